@@ -1,0 +1,371 @@
+#!/usr/bin/env python
+"""Benchmark of the NA1D hot path: fused forward+backward queries/s at the PCF-NAT training shape.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one forward+backward pass of the fused neighbourhood-attention operator over one
+batch of synthetic inputs (seeded N(0,1) stand-ins for log-mel features). Rank 0 prints one JSON
+line. N>1 is launched by torchrun, one rank per GPU; the op has no exchange step, so every rank
+runs the same per-GPU batch (weak scaling) and the only collectives are the timing barrier and the
+max-over-ranks reduction of the elapsed time.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# name -> (batch, heads, T, C, win, dil, backward)
+WORKLOADS = {
+    # BASELINE configs[1]: the shape the metric is quoted on
+    "cfg2_train_B128_H4_L200_D64_w7": dict(B=128, H=4, T=200, C=64, win=7, dil=1, bwd=True),
+    # BASELINE configs[3]: long-utterance forward
+    "cfg4_long_B16_H8_L3000_D64_w15": dict(B=16, H=8, T=3000, C=64, win=15, dil=1, bwd=False),
+    # the shape the reference's own yaml trains (configs/pcf_nat4x4.yaml:16-17,50-53)
+    "real_B512_H16_L150_D16_w27": dict(B=512, H=16, T=150, C=16, win=27, dil=1, bwd=True),
+}
+DEFAULT = "cfg2_train_B128_H4_L200_D64_w7"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def algorithmic_bytes(N, T, C, bwd):
+    fwd = 8 * N * T * C + 4 * N * T          # read q,k,v; write o; write lse
+    back = 16 * N * T * C + 4 * N * T        # read q,k,v,o,dO,lse; write dq,dk,dv
+    return fwd, (back if bwd else 0)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.th.join(timeout=5)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for nm, val in zip(names, r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_host_inputs(w, seed=1):
+    N = w["B"] * w["H"]
+    g = torch.Generator().manual_seed(seed)
+    shape = (N, w["T"], w["C"])
+    return [torch.randn(shape, generator=g).to(torch.bfloat16) for _ in range(4)]  # q, k, v, dO
+
+
+# ------------------------------------------------------------------------------------------ reference arm
+def run_reference(args, w, name):
+    """The reference's CPU implementation of the path (its eager pad/unfold/softmax branch,
+    models/PCF_NATransformer.py:153-174), as restated by the oracle, on all host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import na1d_oracle as orc
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    left = w["win"] - 1 - w["win"] // 2
+    N = w["B"] * w["H"]
+    host = make_host_inputs(w)
+
+    def make_step(n_s):
+        q, k, v, d_o = (x[:n_s].float() for x in host)
+
+        def step():
+            if w["bwd"]:
+                orc.na1d_fused_with_grads(q, k, v, d_o, w["win"], left, w["dil"], 1.0, None, None, w["H"])
+            else:
+                orc.na1d_fused(q, k, v, w["win"], left, w["dil"], 1.0, None, None, w["H"])
+        return step
+
+    # size the per-step sample so that the whole run stays near args.ref_budget seconds
+    probe_n = min(N, 32)
+    probe = make_step(probe_n)
+    probe()
+    t0 = time.perf_counter()
+    probe()
+    per_seq = (time.perf_counter() - t0) / probe_n
+    n_s = int(args.ref_budget / max(1, args.steps + args.warmup) / per_seq)
+    n_s = max(1, min(N, n_s))
+    step = make_step(n_s)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    val = args.steps * n_s * w["T"] / dt
+    line = {
+        "impl": "reference", "metric": "NA1D fwd+bwd queries/sec/GPU" if w["bwd"] else "NA1D fwd queries/sec/GPU",
+        "value": val, "unit": "queries/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "sample": "%d of %d sequences per step" % (n_s, N)},
+        "cpu_baseline": {"value": val, "unit": "queries/s", "cores": cores, "kind": "port",
+                         "sample": "%d of %d sequences x %d steps, fp32 eager oracle" % (n_s, N, args.steps)},
+        "e2e": {"value": val, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------ our arm
+class BufferSet:
+    def __init__(self, w, dev, host):
+        N = w["B"] * w["H"]
+        self.q, self.k, self.v, self.d_o = (x.to(dev) for x in host)
+        e = lambda: torch.empty_like(self.q)
+        self.o, self.dq, self.dk, self.dv = e(), e(), e(), e()
+        self.lse = torch.empty((N, w["T"]), dtype=torch.float32, device=dev)
+        self.delta = torch.empty((N, w["T"]), dtype=torch.float32, device=dev)
+
+
+def run_ours(args, w, name):
+    import torch.distributed as dist
+    from pcf_nat_b200 import _lib, na1d_fused
+    L = _lib.lib()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    N, H, T, C, win, dil = w["B"] * w["H"], w["H"], w["T"], w["C"], w["win"], w["dil"]
+    left = win - 1 - win // 2
+    fwd_b, bwd_b = algorithmic_bytes(N, T, C, w["bwd"])
+    host = make_host_inputs(w, seed=1 + rank)
+    per_set = (9 if w["bwd"] else 4) * N * T * C * 2
+    n_sets = max(4, (3 * L2_BYTES) // per_set + 2)   # the other sets in the rotation exceed L2 several times over
+    sets = [BufferSet(w, dev, host) for _ in range(n_sets)]
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = torch.cuda.Stream(dev)
+
+    def launch_fwd(s, st):
+        rc = L.na1d_fused_forward(P(s.o), P(s.lse), P(s.q), P(s.k), P(s.v), None, None, N, H, T, C, win, left, dil,
+                                  1.0, 0, st)
+        assert rc == 0, rc
+
+    def launch_bwd(s, st):
+        rc = L.na1d_fused_backward(P(s.dq), P(s.dk), P(s.dv), None, P(s.d_o), P(s.q), P(s.k), P(s.v), P(s.o),
+                                   P(s.lse), None, None, P(s.delta), N, H, T, C, win, left, dil, 1.0, 0, st)
+        assert rc == 0, rc
+
+    def run_steps(n, what="both", start=0):
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        for i in range(n):
+            s = sets[(start + i) % n_sets]
+            if what in ("both", "fwd"):
+                launch_fwd(s, st)
+            if w["bwd"] and what in ("both", "bwd"):
+                launch_bwd(s, st)
+
+    def timed(n, what):
+        """Device time of n steps replayed from one CUDA graph, ms, max over ranks."""
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            run_steps(2, what)                      # lazy module load / first-use setup outside capture
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=stream):
+                run_steps(n, what)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0.record(stream)
+            g.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    with torch.cuda.stream(stream):
+        run_steps(args.warmup)
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_total = timed(args.steps, "both")
+    ms_fwd = timed(args.steps, "fwd")
+    ms_bwd = timed(args.steps, "bwd") if w["bwd"] else 0.0
+
+    # ---- end to end through the public torch API with HOST buffers
+    pin = [x.pin_memory() for x in host]
+    n_out = 4 if w["bwd"] else 1
+    host_out = [torch.empty_like(pin[0]).pin_memory() for _ in range(n_out)]
+    e2e_steps = max(3, min(args.steps, 20))
+
+    def e2e_step():
+        q, k, v, d_o = (x.to(dev, non_blocking=True) for x in pin)
+        if w["bwd"]:
+            q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+            o = na1d_fused(q, k, v, win, left, dil, 1.0, None, None, H)
+            o.backward(d_o)
+            outs = (o.detach(), q.grad, k.grad, v.grad)
+        else:
+            outs = (na1d_fused(q, k, v, win, left, dil, 1.0, None, None, H),)
+        for dst, src in zip(host_out, outs):
+            dst.copy_(src, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_e2e = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        queries = N * T
+        # dominant kernel: the fused backward main kernel when there is a backward, else the forward
+        dom_ms = (ms_bwd if w["bwd"] else ms_fwd) / args.steps
+        dom_bytes = bwd_b if w["bwd"] else fwd_b
+        ach = dom_bytes / (dom_ms * 1e-3) / 1e9
+        fam = L.na1d_fused_kernel_family(N, T, C, win, left, dil, 0, 1 if w["bwd"] else 0)
+        line = {
+            "metric": "NA1D fwd+bwd queries/sec/GPU" if w["bwd"] else "NA1D fwd queries/sec/GPU",
+            "value": world * queries * args.steps / (ms_total * 1e-3), "unit": "queries/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": name, "N": N, "T": T, "C": C, "win": win, "dil": dil,
+                       "l2": "rotating %d buffer sets of %.0f MB (> L2 between reuses)" % (n_sets, per_set / 1e6),
+                       "launch": "one CUDA graph of all timed steps", "kernel_family": ["cuda-core", "tcgen05"][fam]},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                         "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "fused backward (delta pre-pass + main)" if w["bwd"] else "fused forward",
+                         "algorithmic_bytes_per_launch": dom_bytes},
+            "roofline_step": {"fwd_us": 1e3 * ms_fwd / args.steps, "bwd_us": 1e3 * ms_bwd / args.steps,
+                              "fwd_frac": fwd_b / (ms_fwd / args.steps * 1e-3) / 1e9 / peak,
+                              "step_frac": (fwd_b + bwd_b) / (ms_total / args.steps * 1e-3) / 1e9 / peak},
+            "e2e": {"value": world * queries * e2e_steps / (ms_e2e * 1e-3), "unit": "queries/s",
+                    "h2d_bytes_per_step": 4 * N * T * C * 2, "d2h_bytes_per_step": n_out * N * T * C * 2,
+                    "steps": e2e_steps},
+            "gpu_launches": args.steps * (3 if w["bwd"] else 1),
+            "clocks": clocks,
+        }
+        line["cpu_baseline"] = cpu_baseline(w) if world == 1 and not args.no_cpu_baseline else None
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(w, budget_s=12.0):
+    """The fp32 oracle timed on the host cores on a bounded sample of the same workload."""
+    from oracle import na1d_oracle as orc
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    left = w["win"] - 1 - w["win"] // 2
+    N = w["B"] * w["H"]
+    n_s = min(N, 128)
+    q, k, v, d_o = (x[:n_s].float() for x in make_host_inputs(w))
+
+    def step():
+        if w["bwd"]:
+            orc.na1d_fused_with_grads(q, k, v, d_o, w["win"], left, w["dil"], 1.0, None, None, w["H"])
+        else:
+            orc.na1d_fused(q, k, v, w["win"], left, w["dil"], 1.0, None, None, w["H"])
+
+    step()
+    t0 = time.perf_counter()
+    n = 0
+    while time.perf_counter() - t0 < budget_s and n < 200:
+        step()
+        n += 1
+    dt = time.perf_counter() - t0
+    return {"value": n * n_s * w["T"] / dt, "unit": "queries/s", "cores": cores, "kind": "port",
+            "sample": "%d of %d sequences x %d passes (%.1f s), fp32 eager oracle" % (n_s, N, n, dt)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT, choices=list(WORKLOADS))
+    ap.add_argument("--ref-budget", type=float, default=90.0, help="seconds of CPU work for --impl reference")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w, args.workload)
+    else:
+        run_ours(args, w, args.workload)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,130 @@
+/*
+ * na1d_b200.h -- C ABI of the B200 (sm_100a) 1-D neighbourhood-attention library.
+ *
+ * All pointers are DEVICE pointers unless a comment says otherwise; all tensors are dense and
+ * row-major.  Every function is asynchronous on `stream` (a cudaStream_t passed as void*, NULL =
+ * legacy default stream), allocates nothing unless stated, and returns 0 (NA1D_OK) or a negative
+ * NA1D_ERR_* code after validating its arguments on the host; no argument error ever reaches
+ * the device.  The library is re-entrant; the caller owns every buffer.
+ *
+ * Geometry shared by all entry points (reference: models/PCF_NATransformer.py:47-56, 153-171):
+ *   N sequences (= batch*heads, head index fastest: n = b*heads + h), T tokens, C channels per
+ *   head (multiple of 8), window `win` with `left` neighbours before the query, dilation `dil`.
+ *   Neighbour kk of query t is key j = t + (kk-left)*dil; keys outside [0,T) read as zero rows.
+ *
+ * Each declaration cites the interface of the reference project (ChenNan1996/PCF-NAT) that it
+ * replaces, as file:line inside that project.
+ */
+#ifndef NA1D_B200_H
+#define NA1D_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element type of the 16-bit tensors */
+#define NA1D_BF16 0 /* replaces the bf16_ana1d module, na1d_tensorcore/nattn.py:12-20 */
+#define NA1D_FP16 1 /* replaces the fp16_ana1d module, na1d_tensorcore/nattn.py:21-29 */
+
+/* status codes */
+#define NA1D_OK 0
+#define NA1D_ERR_NULL_POINTER (-1)   /* a required pointer is NULL */
+#define NA1D_ERR_BAD_SHAPE (-2)      /* N,T,C <= 0, C % 8 != 0, C > 256, or a product overflows int32 */
+#define NA1D_ERR_BAD_WINDOW (-3)     /* win <= 0, win > NA1D_MAX_WINDOW, left outside [0,win), dil <= 0 */
+#define NA1D_ERR_BAD_DTYPE (-4)      /* dtype is neither NA1D_BF16 nor NA1D_FP16 */
+#define NA1D_ERR_BAD_HEADS (-5)      /* heads <= 0 or N % heads != 0 */
+#define NA1D_ERR_MISALIGNED (-6)     /* a 16-bit tensor pointer is not 16-byte aligned */
+#define NA1D_ERR_CUDA (-7)           /* a CUDA runtime/driver call failed; see na1d_last_cuda_error() */
+#define NA1D_ERR_DEVICE_TIMEOUT (-8) /* a bounded wait inside a kernel expired (reported by na1d_check_status) */
+#define NA1D_ERR_TOO_LARGE (-9)      /* problem exceeds a fixed capacity of the entry point */
+
+#define NA1D_MAX_WINDOW 128 /* the reference asserts win <= 80, models/PCF_NATransformer.py:53 */
+
+/* Human-readable text for a status code (host pointer, static storage). */
+const char* na1d_status_string(int status);
+/* cudaError_t value of the most recent failing CUDA call on this host thread (0 if none). */
+int na1d_last_cuda_error(void);
+/* Library version, major*100+minor. */
+int na1d_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Unfused pair: the six entry points of the reference extension, same argument meaning.
+ * `dil` extends them (the reference kernels support dil == 1 only, na1d_tensorcore/nattn.py:130).
+ * ---------------------------------------------------------------------------------------- */
+
+/* attn[n,t,kk] = sum_c q[n,t,c] * k[n,j,c]            attn: (N,T,win) fp32; q,k: (N,T,C) 16-bit.
+ * Replaces torch_ana_qk_forward, na1d_tensorcore/bf16_ana1d.cpp:8-27 (kernels
+ * bf16_ana1d_kernel.cu:42-282; fp16 twin fp16_ana1d.cpp:8-27). */
+int na1d_qk_forward(float* attn, const void* q, const void* k, int64_t N, int64_t T, int64_t C,
+                    int64_t win, int64_t left, int64_t dil, int dtype, void* stream);
+
+/* q_gd[n,t,c] = sum_kk attn_gd[n,t,kk] * k[n,j,c]      q_gd: (N,T,C) 16-bit.
+ * Replaces torch_ana_q_backward, na1d_tensorcore/bf16_ana1d.cpp:29-41 (kernel :285-391). */
+int na1d_q_backward(void* q_gd, const float* attn_gd, const void* k, int64_t N, int64_t T, int64_t C,
+                    int64_t win, int64_t left, int64_t dil, int dtype, void* stream);
+
+/* k_gd[n,j,c] = sum_kk attn_gd[n,t,kk] * q[n,t,c] over all (t,kk) whose neighbour is j.
+ * Replaces torch_ana_k_backward, na1d_tensorcore/bf16_ana1d.cpp:43-55 (kernel :394-492). */
+int na1d_k_backward(void* k_gd, const float* attn_gd, const void* q, int64_t N, int64_t T, int64_t C,
+                    int64_t win, int64_t left, int64_t dil, int dtype, void* stream);
+
+/* result[n,t,c] = sum_kk attn[n,t,kk] * v[n,j,c].
+ * Replaces torch_ana_av_forward, na1d_tensorcore/bf16_ana1d.cpp:57-69. */
+int na1d_av_forward(void* result, const float* attn, const void* v, int64_t N, int64_t T, int64_t C,
+                    int64_t win, int64_t left, int64_t dil, int dtype, void* stream);
+
+/* attn_gd[n,t,kk] = sum_c result_gd[n,t,c] * v[n,j,c].
+ * Replaces torch_ana_a_backward, na1d_tensorcore/bf16_ana1d.cpp:71-90. */
+int na1d_a_backward(float* attn_gd, const void* result_gd, const void* v, int64_t N, int64_t T, int64_t C,
+                    int64_t win, int64_t left, int64_t dil, int dtype, void* stream);
+
+/* v_gd[n,j,c] = sum_kk attn[n,t,kk] * result_gd[n,t,c] over all (t,kk) whose neighbour is j.
+ * Replaces torch_ana_v_backward, na1d_tensorcore/bf16_ana1d.cpp:92-104. */
+int na1d_v_backward(void* v_gd, const float* attn, const void* result_gd, int64_t N, int64_t T, int64_t C,
+                    int64_t win, int64_t left, int64_t dil, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused layer core: everything NAttention.forward does between the head split and the head
+ * merge (models/PCF_NATransformer.py:141-150; MFA twin models/MFA_NATransformer.py:141-150):
+ *   s[kk] = scale * q[t].k[j] + rpb[h,kk] + (masked ? -100 : 0);  p = softmax(s);  o = sum p[kk] v[j]
+ *   masked = j outside [0,T)  or  j >= valid_len[b]  or  t >= valid_len[b]      (:87-116)
+ * The fp32 (N,T,win) tensor of the unfused pair never exists in memory.
+ * ---------------------------------------------------------------------------------------- */
+
+/* o: (N,T,C) 16-bit; lse: (N,T) fp32 = log sum_kk exp(s[kk]) (kept for the backward pass; may be NULL);
+ * rpb: (heads,win) fp32 or NULL; valid_len: (N/heads) int32 or NULL (= no padding). */
+int na1d_fused_forward(void* o, float* lse, const void* q, const void* k, const void* v,
+                       const float* rpb, const int32_t* valid_len, int64_t N, int64_t heads, int64_t T,
+                       int64_t C, int64_t win, int64_t left, int64_t dil, float scale, int dtype,
+                       void* stream);
+
+/* Gradients of na1d_fused_forward. dq,dk,dv: (N,T,C) 16-bit. d_rpb: (heads,win) fp32, ACCUMULATED
+ * into (caller zeroes it), or NULL. delta_ws: caller-provided scratch of N*T fp32 (row sums of
+ * d_o*o, written by a pre-pass and read by the main kernel).
+ * Replaces the autograd chain AV.backward -> softmax backward -> QK.backward,
+ * na1d_tensorcore/nattn.py:46-54 and :69-78. */
+int na1d_fused_backward(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q,
+                        const void* k, const void* v, const void* o, const float* lse, const float* rpb,
+                        const int32_t* valid_len, float* delta_ws, int64_t N, int64_t heads, int64_t T,
+                        int64_t C, int64_t win, int64_t left, int64_t dil, float scale, int dtype,
+                        void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Window index arithmetic as the kernels compute it, for bit-exact checking:
+ * j_out[t,kk] = t + (kk-left)*dil (int32, (T,win)); in_range[t,kk] = 1 if 0 <= j < T else 0.
+ * Restates the implicit pad+unfold indexing of models/PCF_NATransformer.py:158-165.
+ * ---------------------------------------------------------------------------------------- */
+int na1d_window_index(int32_t* j_out, uint8_t* in_range, int64_t T, int64_t win, int64_t left,
+                      int64_t dil, void* stream);
+
+/* Which kernel family the fused entry points would pick for a shape: 0 = CUDA-core kernels,
+ * 1 = tcgen05/TMA kernels. Host-only query, no device work. */
+int na1d_fused_kernel_family(int64_t N, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil,
+                             int dtype, int backward);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NA1D_B200_H */

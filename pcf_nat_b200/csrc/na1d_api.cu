@@ -1,0 +1,139 @@
+// C ABI of the library: argument validation, kernel-family choice, launches. No torch types.
+#include "../../include/na1d_b200.h"
+#include "na1d_internal.h"
+
+#include <atomic>
+#include <climits>
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+std::atomic<int> g_family_override{-1};
+
+int cuda_status(cudaError_t e) {
+    if (e == cudaSuccess) return NA1D_OK;
+    g_last_cuda_error = (int)e;
+    return NA1D_ERR_CUDA;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_geometry(int64_t N, int64_t heads, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil, int dtype,
+                   float scale, na1d::Geometry& g) {
+    if (dtype != NA1D_BF16 && dtype != NA1D_FP16) return NA1D_ERR_BAD_DTYPE;
+    if (N <= 0 || T <= 0 || C <= 0 || C % 8 != 0 || C > 256) return NA1D_ERR_BAD_SHAPE;
+    if (!na1d::simt_supports_channels((int)C)) return NA1D_ERR_BAD_SHAPE;
+    if (win <= 0 || win > NA1D_MAX_WINDOW || left < 0 || left >= win || dil <= 0) return NA1D_ERR_BAD_WINDOW;
+    if (heads <= 0 || N % heads != 0) return NA1D_ERR_BAD_HEADS;
+    // every flat index used by the kernels must fit int32: rows, rows*win, window reach
+    if (N * T > INT_MAX || N * T * win > INT_MAX || T * win > INT_MAX || win * dil > INT_MAX / 2 ||
+        T + win * dil > INT_MAX / 2)
+        return NA1D_ERR_BAD_SHAPE;
+    g.N = (int)N; g.H = (int)heads; g.T = (int)T; g.C = (int)C; g.win = (int)win; g.left = (int)left; g.dil = (int)dil;
+    g.scale = scale;
+    return NA1D_OK;
+}
+
+#define NA1D_REQUIRE_PTR(p) do { if ((p) == nullptr) return NA1D_ERR_NULL_POINTER; } while (0)
+#define NA1D_REQUIRE_ALIGNED(p) do { if (!aligned16(p)) return NA1D_ERR_MISALIGNED; } while (0)
+
+}  // namespace
+
+extern "C" {
+
+const char* na1d_status_string(int status) {
+    switch (status) {
+        case NA1D_OK: return "ok";
+        case NA1D_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case NA1D_ERR_BAD_SHAPE: return "bad shape: need N,T,C > 0, C a supported multiple of 8 (<= 256), sizes within int32";
+        case NA1D_ERR_BAD_WINDOW: return "bad window: need 0 < win <= 128, 0 <= left < win, dil >= 1";
+        case NA1D_ERR_BAD_DTYPE: return "bad dtype: expected NA1D_BF16 or NA1D_FP16";
+        case NA1D_ERR_BAD_HEADS: return "bad heads: need heads > 0 and N divisible by heads";
+        case NA1D_ERR_MISALIGNED: return "a 16-bit tensor pointer is not 16-byte aligned";
+        case NA1D_ERR_CUDA: return "a CUDA call failed (see na1d_last_cuda_error)";
+        case NA1D_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
+        case NA1D_ERR_TOO_LARGE: return "problem exceeds a fixed capacity of this entry point";
+        default: return "unknown status";
+    }
+}
+int na1d_last_cuda_error(void) { return g_last_cuda_error; }
+int na1d_version(void) { return 100; }
+
+int na1d_qk_forward(float* attn, const void* q, const void* k, int64_t N, int64_t T, int64_t C, int64_t win,
+                    int64_t left, int64_t dil, int dtype, void* stream) {
+    NA1D_REQUIRE_PTR(attn); NA1D_REQUIRE_PTR(q); NA1D_REQUIRE_PTR(k);
+    NA1D_REQUIRE_ALIGNED(q); NA1D_REQUIRE_ALIGNED(k);
+    na1d::Geometry g;
+    if (int s = check_geometry(N, 1, T, C, win, left, dil, dtype, 1.f, g)) return s;
+    return cuda_status(na1d::simt_qk(attn, q, k, g, dtype, (cudaStream_t)stream));
+}
+int na1d_a_backward(float* attn_gd, const void* result_gd, const void* v, int64_t N, int64_t T, int64_t C, int64_t win,
+                    int64_t left, int64_t dil, int dtype, void* stream) {
+    return na1d_qk_forward(attn_gd, result_gd, v, N, T, C, win, left, dil, dtype, stream);
+}
+int na1d_q_backward(void* q_gd, const float* attn_gd, const void* k, int64_t N, int64_t T, int64_t C, int64_t win,
+                    int64_t left, int64_t dil, int dtype, void* stream) {
+    NA1D_REQUIRE_PTR(q_gd); NA1D_REQUIRE_PTR(attn_gd); NA1D_REQUIRE_PTR(k);
+    NA1D_REQUIRE_ALIGNED(q_gd); NA1D_REQUIRE_ALIGNED(k);
+    na1d::Geometry g;
+    if (int s = check_geometry(N, 1, T, C, win, left, dil, dtype, 1.f, g)) return s;
+    return cuda_status(na1d::simt_band_x(q_gd, attn_gd, k, g, dtype, (cudaStream_t)stream));
+}
+int na1d_av_forward(void* result, const float* attn, const void* v, int64_t N, int64_t T, int64_t C, int64_t win,
+                    int64_t left, int64_t dil, int dtype, void* stream) {
+    return na1d_q_backward(result, attn, v, N, T, C, win, left, dil, dtype, stream);
+}
+int na1d_k_backward(void* k_gd, const float* attn_gd, const void* q, int64_t N, int64_t T, int64_t C, int64_t win,
+                    int64_t left, int64_t dil, int dtype, void* stream) {
+    NA1D_REQUIRE_PTR(k_gd); NA1D_REQUIRE_PTR(attn_gd); NA1D_REQUIRE_PTR(q);
+    NA1D_REQUIRE_ALIGNED(k_gd); NA1D_REQUIRE_ALIGNED(q);
+    na1d::Geometry g;
+    if (int s = check_geometry(N, 1, T, C, win, left, dil, dtype, 1.f, g)) return s;
+    return cuda_status(na1d::simt_bandT_x(k_gd, attn_gd, q, g, dtype, (cudaStream_t)stream));
+}
+int na1d_v_backward(void* v_gd, const float* attn, const void* result_gd, int64_t N, int64_t T, int64_t C, int64_t win,
+                    int64_t left, int64_t dil, int dtype, void* stream) {
+    return na1d_k_backward(v_gd, attn, result_gd, N, T, C, win, left, dil, dtype, stream);
+}
+
+int na1d_fused_kernel_family(int64_t N, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil, int dtype,
+                             int backward) {
+    (void)N; (void)T; (void)C; (void)win; (void)left; (void)dil; (void)dtype; (void)backward;
+    return 0;
+}
+
+int na1d_fused_forward(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
+                       const int32_t* valid_len, int64_t N, int64_t heads, int64_t T, int64_t C, int64_t win,
+                       int64_t left, int64_t dil, float scale, int dtype, void* stream) {
+    NA1D_REQUIRE_PTR(o); NA1D_REQUIRE_PTR(q); NA1D_REQUIRE_PTR(k); NA1D_REQUIRE_PTR(v);
+    NA1D_REQUIRE_ALIGNED(o); NA1D_REQUIRE_ALIGNED(q); NA1D_REQUIRE_ALIGNED(k); NA1D_REQUIRE_ALIGNED(v);
+    na1d::Geometry g;
+    if (int s = check_geometry(N, heads, T, C, win, left, dil, dtype, scale, g)) return s;
+    return cuda_status(na1d::simt_fused_fwd(o, lse, q, k, v, rpb, valid_len, g, dtype, (cudaStream_t)stream));
+}
+
+int na1d_fused_backward(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
+                        const void* v, const void* o, const float* lse, const float* rpb, const int32_t* valid_len,
+                        float* delta_ws, int64_t N, int64_t heads, int64_t T, int64_t C, int64_t win, int64_t left,
+                        int64_t dil, float scale, int dtype, void* stream) {
+    NA1D_REQUIRE_PTR(dq); NA1D_REQUIRE_PTR(dk); NA1D_REQUIRE_PTR(dv); NA1D_REQUIRE_PTR(d_o); NA1D_REQUIRE_PTR(q);
+    NA1D_REQUIRE_PTR(k); NA1D_REQUIRE_PTR(v); NA1D_REQUIRE_PTR(o); NA1D_REQUIRE_PTR(lse); NA1D_REQUIRE_PTR(delta_ws);
+    NA1D_REQUIRE_ALIGNED(dq); NA1D_REQUIRE_ALIGNED(dk); NA1D_REQUIRE_ALIGNED(dv); NA1D_REQUIRE_ALIGNED(d_o);
+    NA1D_REQUIRE_ALIGNED(q); NA1D_REQUIRE_ALIGNED(k); NA1D_REQUIRE_ALIGNED(v); NA1D_REQUIRE_ALIGNED(o);
+    na1d::Geometry g;
+    if (int s = check_geometry(N, heads, T, C, win, left, dil, dtype, scale, g)) return s;
+    if (d_rpb && heads * win * 4 > 48 * 1024) return NA1D_ERR_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (int s = cuda_status(na1d::simt_delta(delta_ws, d_o, o, g.N * g.T, g.C, dtype, st))) return s;
+    return cuda_status(na1d::simt_fused_bwd(dq, dk, dv, d_rpb, d_o, q, k, v, lse, delta_ws, rpb, valid_len, g, dtype, st));
+}
+
+int na1d_window_index(int32_t* j_out, uint8_t* in_range, int64_t T, int64_t win, int64_t left, int64_t dil,
+                      void* stream) {
+    NA1D_REQUIRE_PTR(j_out); NA1D_REQUIRE_PTR(in_range);
+    na1d::Geometry g;
+    if (int s = check_geometry(1, 1, T, 8, win, left, dil, NA1D_BF16, 1.f, g)) return s;
+    return cuda_status(na1d::window_index(j_out, in_range, g.T, g.win, g.left, g.dil, (cudaStream_t)stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,64 @@
+// Shared device/host helpers for the NA1D kernels (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace na1d {
+
+// Additive logit for a masked neighbour. The reference adds -100 instead of excluding the
+// neighbour (models/PCF_NATransformer.py:98), which keeps fully masked rows finite.
+constexpr float kMaskValue = -100.0f;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// The single definition of the window index arithmetic used by every kernel:
+// neighbour kk of query t is key t + (kk-left)*dil  (pad+unfold of
+// models/PCF_NATransformer.py:158-165 made explicit).
+__host__ __device__ __forceinline__ int neighbour(int t, int kk, int left, int dil) {
+    return t + (kk - left) * dil;
+}
+__host__ __device__ __forceinline__ bool in_range(int j, int T) { return j >= 0 && j < T; }
+
+struct Geometry {
+    int N, H, T, C, win, left, dil;
+    float scale;
+};
+
+// 8 consecutive 16-bit elements (one 16-byte chunk) <-> 8 floats
+template <typename E> struct Cvt;
+template <> struct Cvt<__nv_bfloat16> {
+    static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    }
+    static __device__ __forceinline__ uint4 pack(const float* f) {
+        uint4 u; __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        return u;
+    }
+    static __device__ __forceinline__ uint32_t pack2(float a, float b) {
+        __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t);
+    }
+};
+template <> struct Cvt<__half> {
+    static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
+        const __half2* p = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { float2 t = __half22float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    }
+    static __device__ __forceinline__ uint4 pack(const float* f) {
+        uint4 u; __half2* p = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+        return u;
+    }
+    static __device__ __forceinline__ uint32_t pack2(float a, float b) {
+        __half2 t = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&t);
+    }
+};
+
+}  // namespace na1d

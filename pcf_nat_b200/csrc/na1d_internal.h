@@ -1,0 +1,20 @@
+// Internal C++ interface between the C ABI (na1d_api.cu) and the kernel families.
+#pragma once
+#include "na1d_common.cuh"
+
+namespace na1d {
+
+// ---- CUDA-core family (na1d_simt.cu)
+bool simt_supports_channels(int C);
+cudaError_t simt_qk(float* attn, const void* a, const void* b, const Geometry& gm, int dtype, cudaStream_t st);
+cudaError_t simt_band_x(void* out, const float* band, const void* x, const Geometry& gm, int dtype, cudaStream_t st);
+cudaError_t simt_bandT_x(void* out, const float* band, const void* x, const Geometry& gm, int dtype, cudaStream_t st);
+cudaError_t simt_fused_fwd(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
+                           const int* valid_len, const Geometry& gm, int dtype, cudaStream_t st);
+cudaError_t simt_delta(float* delta, const void* d_o, const void* o, int rows, int C, int dtype, cudaStream_t st);
+cudaError_t simt_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
+                           const void* v, const float* lse, const float* delta, const float* rpb, const int* valid_len,
+                           const Geometry& gm, int dtype, cudaStream_t st);
+cudaError_t window_index(int* j_out, unsigned char* inr, int T, int win, int left, int dil, cudaStream_t st);
+
+}  // namespace na1d

@@ -1,0 +1,188 @@
+"""Torch-facing wrappers over the C ABI: device memory and streams come from torch, the
+arithmetic comes from libna1d_b200.so. CUDA tensors only -- there is no CPU fallback."""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import check
+
+_L = _lib.lib()
+
+
+def _dtype_code(t):
+    if t.dtype == torch.bfloat16:
+        return _lib.NA1D_BF16
+    if t.dtype == torch.float16:
+        return _lib.NA1D_FP16
+    raise TypeError("NA1D kernels take bfloat16 or float16 tensors, got %s" % t.dtype)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("pcf_nat_b200 runs on CUDA devices only (no CPU fallback); got a %s tensor" % t.device)
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _shape3(x):
+    if x.dim() != 3:
+        raise ValueError("expected a (N,T,C) tensor, got shape %s" % (tuple(x.shape),))
+    return x.shape
+
+
+def _band_call(fn_name, out, a, b, N, T, C, win, left, dil, ref):
+    with torch.cuda.device(ref.device):
+        check(getattr(_L, fn_name)(_p(out), _p(a), _p(b), N, T, C, win, left, dil, _dtype_code(ref), _stream(ref)),
+              fn_name)
+    return out
+
+
+# ------------------------------------------------------------------ unfused pair
+def qk_forward(q, k, win, left, dil=1):
+    """attn (N,T,win) fp32 = banded q.k^T (na1d_tensorcore/nattn.py:34-44 forward)."""
+    _need_cuda(q, k)
+    assert q.is_contiguous() and k.is_contiguous() and q.dtype == k.dtype and q.shape == k.shape
+    N, T, C = _shape3(q)
+    attn = torch.empty((N, T, win), dtype=torch.float32, device=q.device)
+    return _band_call("na1d_qk_forward", attn, q, k, N, T, C, win, left, dil, q)
+
+
+def q_backward(attn_gd, k, win, left, dil=1):
+    _need_cuda(attn_gd, k)
+    assert attn_gd.is_contiguous() and k.is_contiguous() and attn_gd.dtype == torch.float32
+    N, T, C = _shape3(k)
+    assert attn_gd.shape == (N, T, win)
+    return _band_call("na1d_q_backward", torch.empty_like(k), attn_gd, k, N, T, C, win, left, dil, k)
+
+
+def k_backward(attn_gd, q, win, left, dil=1):
+    _need_cuda(attn_gd, q)
+    assert attn_gd.is_contiguous() and q.is_contiguous() and attn_gd.dtype == torch.float32
+    N, T, C = _shape3(q)
+    assert attn_gd.shape == (N, T, win)
+    return _band_call("na1d_k_backward", torch.empty_like(q), attn_gd, q, N, T, C, win, left, dil, q)
+
+
+def av_forward(attn, v, win, left, dil=1):
+    _need_cuda(attn, v)
+    assert attn.is_contiguous() and v.is_contiguous() and attn.dtype == torch.float32
+    N, T, C = _shape3(v)
+    assert attn.shape == (N, T, win)
+    return _band_call("na1d_av_forward", torch.empty_like(v), attn, v, N, T, C, win, left, dil, v)
+
+
+def a_backward(result_gd, v, win, left, dil=1):
+    _need_cuda(result_gd, v)
+    assert result_gd.is_contiguous() and v.is_contiguous() and result_gd.dtype == v.dtype
+    N, T, C = _shape3(v)
+    attn_gd = torch.empty((N, T, win), dtype=torch.float32, device=v.device)
+    return _band_call("na1d_a_backward", attn_gd, result_gd, v, N, T, C, win, left, dil, v)
+
+
+def v_backward(attn, result_gd, win, left, dil=1):
+    _need_cuda(attn, result_gd)
+    assert attn.is_contiguous() and result_gd.is_contiguous() and attn.dtype == torch.float32
+    N, T, C = _shape3(result_gd)
+    assert attn.shape == (N, T, win)
+    return _band_call("na1d_v_backward", torch.empty_like(result_gd), attn, result_gd, N, T, C, win, left, dil, result_gd)
+
+
+# ------------------------------------------------------------------ fused layer core
+def _prep_rpb(rpb, heads, win, dev):
+    if rpb is None:
+        return None
+    r = rpb.detach().to(device=dev, dtype=torch.float32).reshape(heads, win).contiguous()
+    return r
+
+
+def _prep_valid(valid_len, batch, dev):
+    if valid_len is None:
+        return None
+    v = torch.as_tensor(valid_len, device=dev).to(torch.int32).reshape(batch).contiguous()
+    return v
+
+
+def fused_forward(q, k, v, win, left, dil=1, scale=1.0, rpb=None, valid_len=None, heads=1, need_lse=True):
+    """(o, lse): o (N,T,C) in q's dtype, lse (N,T) fp32."""
+    _need_cuda(q, k, v)
+    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+    assert q.dtype == k.dtype == v.dtype and q.shape == k.shape == v.shape
+    N, T, C = _shape3(q)
+    o = torch.empty_like(q)
+    lse = torch.empty((N, T), dtype=torch.float32, device=q.device) if need_lse else None
+    r = _prep_rpb(rpb, heads, win, q.device)
+    vl = _prep_valid(valid_len, N // max(heads, 1), q.device)
+    with torch.cuda.device(q.device):
+        check(_L.na1d_fused_forward(_p(o), _p(lse), _p(q), _p(k), _p(v), _p(r), _p(vl), N, heads, T, C, win, left,
+                                    dil, float(scale), _dtype_code(q), _stream(q)), "na1d_fused_forward")
+    return o, lse
+
+
+def fused_backward(d_o, q, k, v, o, lse, win, left, dil=1, scale=1.0, rpb=None, valid_len=None, heads=1,
+                   need_d_rpb=False):
+    """(dq, dk, dv, d_rpb or None)."""
+    _need_cuda(d_o, q, k, v, o, lse)
+    d_o = d_o.contiguous()
+    N, T, C = _shape3(q)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    delta = torch.empty((N, T), dtype=torch.float32, device=q.device)
+    r = _prep_rpb(rpb, heads, win, q.device)
+    vl = _prep_valid(valid_len, N // max(heads, 1), q.device)
+    d_rpb = torch.zeros((heads, win), dtype=torch.float32, device=q.device) if need_d_rpb else None
+    with torch.cuda.device(q.device):
+        check(_L.na1d_fused_backward(_p(dq), _p(dk), _p(dv), _p(d_rpb), _p(d_o), _p(q), _p(k), _p(v), _p(o), _p(lse),
+                                     _p(r), _p(vl), _p(delta), N, heads, T, C, win, left, dil, float(scale),
+                                     _dtype_code(q), _stream(q)), "na1d_fused_backward")
+    return dq, dk, dv, d_rpb
+
+
+class NA1dFusedFunction(torch.autograd.Function):
+    """o = softmax(scale*q.k^T + rpb + mask) . v over each query's window, as one op.
+
+    Fuses models/PCF_NATransformer.py:141-150 (QK -> +bias -> +mask -> softmax -> AV); saves
+    (q,k,v,o,lse) instead of the fp32 (N,T,win) probabilities the unfused pair keeps
+    (na1d_tensorcore/nattn.py:41, :65).
+    """
+
+    @staticmethod
+    def forward(ctx, q, k, v, win_size, left, dilation=1, scale=1.0, rpb=None, valid_len=None, heads=1):
+        o, lse = fused_forward(q, k, v, win_size, left, dilation, scale, rpb, valid_len, heads)
+        ctx.save_for_backward(q, k, v, o, lse, rpb if rpb is not None else torch.empty(0),
+                              valid_len if isinstance(valid_len, torch.Tensor) else torch.empty(0))
+        ctx.cfg = (win_size, left, dilation, scale, heads, rpb is not None,
+                   valid_len if not isinstance(valid_len, torch.Tensor) else "tensor")
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse, rpb, vl_t = ctx.saved_tensors
+        win, left, dil, scale, heads, has_rpb, vl = ctx.cfg
+        valid_len = vl_t if vl == "tensor" else vl
+        need_rpb = has_rpb and ctx.needs_input_grad[7]
+        dq, dk, dv, d_rpb = fused_backward(d_o, q, k, v, o, lse, win, left, dil, scale, rpb if has_rpb else None,
+                                           valid_len, heads, need_d_rpb=need_rpb)
+        if d_rpb is not None:
+            d_rpb = d_rpb.reshape(rpb.shape).to(rpb.dtype)
+        return dq, dk, dv, None, None, None, None, d_rpb, None, None
+
+
+def na1d_fused(q, k, v, win_size, left, dilation=1, scale=1.0, rpb=None, valid_len=None, heads=1):
+    return NA1dFusedFunction.apply(q, k, v, win_size, left, dilation, scale, rpb, valid_len, heads)
+
+
+def window_index(T, win, left, dil=1, device="cuda"):
+    """(j, in_range) exactly as the kernels compute them: int32 (T,win) and bool (T,win)."""
+    dev = torch.device(device)
+    j = torch.empty((T, win), dtype=torch.int32, device=dev)
+    inr = torch.empty((T, win), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        check(_L.na1d_window_index(_p(j), _p(inr), T, win, left, dil, _stream(j)), "na1d_window_index")
+    return j, inr.bool()
