@@ -39,6 +39,7 @@ extern "C" {
 #define NA1D_ERR_CUDA (-7)           /* a CUDA runtime/driver call failed; see na1d_last_cuda_error() */
 #define NA1D_ERR_DEVICE_TIMEOUT (-8) /* a bounded wait inside a kernel expired (reported by na1d_check_status) */
 #define NA1D_ERR_TOO_LARGE (-9)      /* problem exceeds a fixed capacity of the entry point */
+#define NA1D_ERR_UNSUPPORTED (-10)   /* the kernel family forced by na1d_set_kernel_family cannot run this shape */
 
 #define NA1D_MAX_WINDOW 128 /* the reference asserts win <= 80, models/PCF_NATransformer.py:53 */
 
@@ -123,6 +124,14 @@ int na1d_window_index(int32_t* j_out, uint8_t* in_range, int64_t T, int64_t win,
  * 1 = tcgen05/TMA kernels. Host-only query, no device work. */
 int na1d_fused_kernel_family(int64_t N, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil,
                              int dtype, int backward);
+
+/* Force a kernel family for the fused entry points: -1 = automatic (default), 0 = CUDA-core,
+ * 1 = tcgen05/TMA. Process-wide; meant for tests and benchmarks. Returns the previous setting. */
+int na1d_set_kernel_family(int family);
+
+/* Synchronises the device, then returns and clears the device-side status word: 0 = every bounded
+ * wait inside the tcgen05 kernels completed, otherwise NA1D_ERR_DEVICE_TIMEOUT. */
+int na1d_device_status(void);
 
 #ifdef __cplusplus
 }

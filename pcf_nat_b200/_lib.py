@@ -63,6 +63,10 @@ _lib.na1d_window_index.restype = _i32
 _lib.na1d_window_index.argtypes = [_ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]
 _lib.na1d_fused_kernel_family.restype = _i32
 _lib.na1d_fused_kernel_family.argtypes = [_i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32]
+_lib.na1d_set_kernel_family.restype = _i32
+_lib.na1d_set_kernel_family.argtypes = [_i32]
+_lib.na1d_device_status.restype = _i32
+_lib.na1d_device_status.argtypes = []
 
 
 def lib():

@@ -53,6 +53,7 @@ const char* na1d_status_string(int status) {
         case NA1D_ERR_CUDA: return "a CUDA call failed (see na1d_last_cuda_error)";
         case NA1D_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
         case NA1D_ERR_TOO_LARGE: return "problem exceeds a fixed capacity of this entry point";
+        case NA1D_ERR_UNSUPPORTED: return "the forced kernel family does not support this shape";
         default: return "unknown status";
     }
 }
@@ -96,10 +97,30 @@ int na1d_v_backward(void* v_gd, const float* attn, const void* result_gd, int64_
     return na1d_k_backward(v_gd, attn, result_gd, N, T, C, win, left, dil, dtype, stream);
 }
 
+static int pick_family(const na1d::Geometry& g, int backward) {
+    const int forced = g_family_override.load();
+    const bool tc_ok = backward ? false : na1d::tc_fwd_supports(g);
+    if (forced == 0) return 0;
+    if (forced == 1) return tc_ok ? 1 : NA1D_ERR_UNSUPPORTED;
+    return tc_ok ? 1 : 0;
+}
+
 int na1d_fused_kernel_family(int64_t N, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil, int dtype,
                              int backward) {
-    (void)N; (void)T; (void)C; (void)win; (void)left; (void)dil; (void)dtype; (void)backward;
-    return 0;
+    na1d::Geometry g;
+    if (int s = check_geometry(N, 1, T, C, win, left, dil, dtype, 1.f, g)) return s;
+    return pick_family(g, backward);
+}
+
+int na1d_set_kernel_family(int family) {
+    if (family < -1 || family > 1) family = -1;
+    return g_family_override.exchange(family);
+}
+
+int na1d_device_status(void) {
+    const int v = na1d::tc_read_status();
+    if (v < 0) return cuda_status(cudaGetLastError());
+    return v == 0 ? NA1D_OK : NA1D_ERR_DEVICE_TIMEOUT;
 }
 
 int na1d_fused_forward(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
@@ -109,6 +130,9 @@ int na1d_fused_forward(void* o, float* lse, const void* q, const void* k, const 
     NA1D_REQUIRE_ALIGNED(o); NA1D_REQUIRE_ALIGNED(q); NA1D_REQUIRE_ALIGNED(k); NA1D_REQUIRE_ALIGNED(v);
     na1d::Geometry g;
     if (int s = check_geometry(N, heads, T, C, win, left, dil, dtype, scale, g)) return s;
+    const int fam = pick_family(g, 0);
+    if (fam < 0) return fam;
+    if (fam == 1) return cuda_status(na1d::tc_fused_fwd(o, lse, q, k, v, rpb, valid_len, g, dtype, (cudaStream_t)stream));
     return cuda_status(na1d::simt_fused_fwd(o, lse, q, k, v, rpb, valid_len, g, dtype, (cudaStream_t)stream));
 }
 

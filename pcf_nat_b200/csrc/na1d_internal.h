@@ -17,4 +17,10 @@ cudaError_t simt_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const voi
                            const Geometry& gm, int dtype, cudaStream_t st);
 cudaError_t window_index(int* j_out, unsigned char* inr, int T, int win, int left, int dil, cudaStream_t st);
 
+// ---- tcgen05 / TMA family (na1d_tc_fwd.cu)
+bool tc_fwd_supports(const Geometry& gm);
+cudaError_t tc_fused_fwd(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
+                         const int* valid_len, const Geometry& gm, int dtype, cudaStream_t st);
+int tc_read_status();
+
 }  // namespace na1d

@@ -186,3 +186,22 @@ def window_index(T, win, left, dil=1, device="cuda"):
     with torch.cuda.device(dev):
         check(_L.na1d_window_index(_p(j), _p(inr), T, win, left, dil, _stream(j)), "na1d_window_index")
     return j, inr.bool()
+
+
+FAMILY_AUTO, FAMILY_CUDA_CORE, FAMILY_TCGEN05 = -1, 0, 1
+
+
+def set_kernel_family(family):
+    """Force the kernel family of the fused entry points (tests/benchmarks); returns the old setting."""
+    return _L.na1d_set_kernel_family(int(family))
+
+
+def kernel_family(N, T, C, win, left, dil, dtype, backward=False):
+    """0 = CUDA-core kernels, 1 = tcgen05/TMA kernels, negative = status code (forced family unsupported)."""
+    code = _lib.NA1D_BF16 if dtype == torch.bfloat16 else _lib.NA1D_FP16
+    return _L.na1d_fused_kernel_family(N, T, C, win, left, dil, code, 1 if backward else 0)
+
+
+def device_status():
+    """Synchronise and raise if a bounded wait inside a kernel expired."""
+    check(_L.na1d_device_status(), "na1d_device_status")

@@ -21,6 +21,17 @@ def _ops():
     return ops
 
 
+@pytest.fixture(params=["auto", "cuda_core"])
+def family(request):
+    """Runs a test once with the automatic kernel choice (tcgen05 kernels where they apply) and once
+    with the CUDA-core kernels forced, so both families are held to the same oracle."""
+    ops = _ops()
+    old = ops.set_kernel_family(ops.FAMILY_CUDA_CORE if request.param == "cuda_core" else ops.FAMILY_AUTO)
+    yield request.param
+    ops.set_kernel_family(old)
+    ops.device_status()
+
+
 # ------------------------------------------------------------------ index math, bit exact
 @pytest.mark.parametrize("T,win,left,dil", [(1, 3, 1, 1), (5, 9, 4, 1), (200, 7, 3, 1), (200, 8, 3, 1),
                                             (37, 7, 3, 2), (50, 15, 7, 4), (31, 6, 1, 1), (20, 5, 0, 1),
@@ -35,7 +46,7 @@ def test_window_index_bit_exact(T, win, left, dil):
 # ------------------------------------------------------------------ fused forward / backward
 @pytest.mark.parametrize("dtype", DTYPES, ids=["bf16", "fp16"])
 @pytest.mark.parametrize("name", list(CASES))
-def test_fused_forward_matches_oracle_and_reference_vectors(name, dtype):
+def test_fused_forward_matches_oracle_and_reference_vectors(name, dtype, family):
     c = CASES[name]
     win, left = win_left(c["win"])
     (q, k, v, _), (qf, kf, vf, _), rpb = rounded_inputs(name, dtype)
@@ -52,7 +63,7 @@ def test_fused_forward_matches_oracle_and_reference_vectors(name, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["bf16", "fp16"])
 @pytest.mark.parametrize("name", [n for n in CASES if CASES[n]["grads"]])
-def test_fused_backward_matches_oracle(name, dtype):
+def test_fused_backward_matches_oracle(name, dtype, family):
     ops = _ops()
     c = CASES[name]
     win, left = win_left(c["win"])
@@ -94,7 +105,7 @@ EDGE = [(T, win, left, dil, C)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["bf16", "fp16"])
-def test_edge_sweep_forward_backward(dtype):
+def test_edge_sweep_forward_backward(dtype, family):
     ops = _ops()
     for idx, (T, win, left, dil, C) in enumerate(EDGE):
         N, H = 4, 2
@@ -143,7 +154,7 @@ def test_unfused_pair_forward_and_gradients(T, C, win, left, dil, dtype):
 
 
 # ------------------------------------------------------------------ properties at the full benchmark shape
-def test_full_size_training_shape_properties():
+def test_full_size_training_shape_properties(family):
     """BASELINE configs[1]: B=128, heads=4, L=200, head_dim=64, win=7, bf16."""
     ops = _ops()
     N, H, T, C, win, left = 512, 4, 200, 64, 7, 3
@@ -174,7 +185,7 @@ def test_full_size_training_shape_properties():
     assert float((ob.float() - (o.float() + oa.float())).abs().max()) < 6e-2
 
 
-def test_batch_invariance_bitwise():
+def test_batch_invariance_bitwise(family):
     """Row n of a batched call equals the same sequence run alone (the property the reference's
     own ad-hoc script looked at)."""
     ops = _ops()
@@ -188,7 +199,7 @@ def test_batch_invariance_bitwise():
         assert torch.equal(o[n:n + 1], o1) and torch.equal(lse[n:n + 1], lse1)
 
 
-def test_outputs_stay_inside_their_buffers():
+def test_outputs_stay_inside_their_buffers(family):
     """Sentinel margins around every output must survive (stands in for a memory checker)."""
     from pcf_nat_b200 import _lib
     import ctypes
@@ -233,3 +244,35 @@ def test_bad_arguments_raise_without_touching_the_device():
     torch.cuda.synchronize()
     o, _ = ops.fused_forward(q, q, q, 7, 3)
     assert torch.isfinite(o.float()).all()
+
+
+# ------------------------------------------------------------------ tcgen05 family: shapes it must take, and parity there
+TC_SHAPES = [(N, T, C, win, left) for (N, T) in ((3, 200), (2, 128), (1, 129), (2, 1), (1, 1000), (2, 383))
+             for (C, win, left) in ((64, 7, 3), (32, 7, 3), (16, 27, 13), (64, 15, 7), (64, 31, 15), (32, 33, 0),
+                                    (16, 3, 2), (64, 8, 3), (32, 17, 16), (64, 9, 4), (16, 18, 9))]
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["bf16", "fp16"])
+def test_tcgen05_forward_shapes(dtype):
+    ops = _ops()
+    old = ops.set_kernel_family(ops.FAMILY_TCGEN05)
+    try:
+        for idx, (N, T, C, win, left) in enumerate(TC_SHAPES):
+            assert ops.kernel_family(N, T, C, win, left, 1, dtype) == 1, "tcgen05 family should take this shape"
+            H = 1
+            sc = C ** -0.5
+            q, k, v = (randn16((N, T, C), dtype, 500 + 3 * idx + i) for i in range(3))
+            rpb = 0.3 * torch.randn(H, win, generator=torch.Generator().manual_seed(idx))
+            vl = [T] + [max(1, T - 5)] * (N - 1)
+            o, lse = ops.fused_forward(q.cuda(), k.cuda(), v.cuda(), win, left, 1, sc, rpb.cuda(), vl, H)
+            ops.device_status()
+            o_r, lse_r = orc.na1d_fused(q.float(), k.float(), v.float(), win, left, 1, sc, rpb, vl, H, return_lse=True)
+            tag = "N=%d T=%d C=%d win=%d left=%d " % (N, T, C, win, left)
+            assert_close(o, o_r, dtype, tag + "o")
+            assert float((lse.cpu() - lse_r).abs().max()) < 1e-3 * max(1.0, float(lse_r.abs().max())), tag + "lse"
+        # shapes outside the family are refused when it is forced, and taken by the CUDA-core kernels otherwise
+        assert ops.kernel_family(2, 64, 64, 7, 3, 2, dtype) == -10
+        assert ops.kernel_family(2, 64, 24, 7, 3, 1, dtype) == -10
+    finally:
+        ops.set_kernel_family(old)
+    assert ops.kernel_family(2, 64, 64, 7, 3, 2, dtype) == 0
