@@ -99,9 +99,9 @@ int na1d_v_backward(void* v_gd, const float* attn, const void* result_gd, int64_
 
 static int pick_family(const na1d::Geometry& g, int backward) {
     const int forced = g_family_override.load();
-    const bool tc_ok = backward ? false : na1d::tc_fwd_supports(g);
+    const bool tc_ok = backward ? na1d::tc_bwd_supports(g) : na1d::tc_fwd_supports(g);
     if (forced == 0) return 0;
-    if (forced == 1) return tc_ok ? 1 : NA1D_ERR_UNSUPPORTED;
+    if (forced >= 1) return tc_ok ? forced : NA1D_ERR_UNSUPPORTED;
     return tc_ok ? 1 : 0;
 }
 
@@ -113,14 +113,15 @@ int na1d_fused_kernel_family(int64_t N, int64_t T, int64_t C, int64_t win, int64
 }
 
 int na1d_set_kernel_family(int family) {
-    if (family < -1 || family > 1) family = -1;
+    if (family < -1 || family > 2) family = -1;
     return g_family_override.exchange(family);
 }
 
 int na1d_device_status(void) {
     const int v = na1d::tc_read_status();
-    if (v < 0) return cuda_status(cudaGetLastError());
-    return v == 0 ? NA1D_OK : NA1D_ERR_DEVICE_TIMEOUT;
+    const int w = na1d::tc_bwd_read_status();
+    if (v < 0 || w < 0) return cuda_status(cudaGetLastError());
+    return (v == 0 && w == 0) ? NA1D_OK : NA1D_ERR_DEVICE_TIMEOUT;
 }
 
 int na1d_fused_forward(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
@@ -132,7 +133,7 @@ int na1d_fused_forward(void* o, float* lse, const void* q, const void* k, const 
     if (int s = check_geometry(N, heads, T, C, win, left, dil, dtype, scale, g)) return s;
     const int fam = pick_family(g, 0);
     if (fam < 0) return fam;
-    if (fam == 1) return cuda_status(na1d::tc_fused_fwd(o, lse, q, k, v, rpb, valid_len, g, dtype, (cudaStream_t)stream));
+    if (fam >= 1) return cuda_status(na1d::tc_fused_fwd(o, lse, q, k, v, rpb, valid_len, g, dtype, fam == 2, (cudaStream_t)stream));
     return cuda_status(na1d::simt_fused_fwd(o, lse, q, k, v, rpb, valid_len, g, dtype, (cudaStream_t)stream));
 }
 
@@ -148,6 +149,10 @@ int na1d_fused_backward(void* dq, void* dk, void* dv, float* d_rpb, const void* 
     if (int s = check_geometry(N, heads, T, C, win, left, dil, dtype, scale, g)) return s;
     if (d_rpb && heads * win * 4 > 48 * 1024) return NA1D_ERR_TOO_LARGE;
     cudaStream_t st = (cudaStream_t)stream;
+    const int fam = pick_family(g, 1);
+    if (fam < 0) return fam;
+    if (fam >= 1)  // delta is recomputed inside the kernel from P and dP: neither o nor delta_ws is touched
+        return cuda_status(na1d::tc_fused_bwd(dq, dk, dv, d_rpb, d_o, q, k, v, lse, rpb, valid_len, g, dtype, st));
     if (int s = cuda_status(na1d::simt_delta(delta_ws, d_o, o, g.N * g.T, g.C, dtype, st))) return s;
     return cuda_status(na1d::simt_fused_bwd(dq, dk, dv, d_rpb, d_o, q, k, v, lse, delta_ws, rpb, valid_len, g, dtype, st));
 }

@@ -61,12 +61,12 @@ struct alignas(8) FwdMisc {
     float rpb[64];
 };
 
-template <typename E, int C, int WB>
+template <typename E, int C, int WB, bool PT>
 __global__ void __launch_bounds__(128, 2)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, E* __restrict__ o, float* __restrict__ lse,
               const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, int tiles_per_seq, int KT) {
-    constexpr int LW = round_up(WB + 31, 8);  // TMEM columns each warp reads
+    constexpr int LW = round_up(WB + 31, 16);  // TMEM columns each warp reads
     constexpr int kRowBytes = C * 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -97,7 +97,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ptx::tmem_alloc(&misc->tmem_base, kTmemCols);
         ptx::tmem_relinquish();
     }
-    {   // P starts as zeros; only band entries are written later
+    if constexpr (!PT) {   // P starts as zeros; only band entries are written later
         uint4* p4 = reinterpret_cast<uint4*>(sP);
         const int n16 = kTileM * KT * 2 / 16;
         for (int i = tid; i < n16; i += 128) p4[i] = make_uint4(0, 0, 0, 0);
@@ -171,17 +171,43 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             if (kk < win) { const float p = exp2f(s[kk] - mx); s[kk] = p; sum += p; }
         }
         const float inv = 1.f / sum;
-        if (t < T) {
-            // P[r][c], c = r + kk: K-major core matrices (8 rows x 16 bytes), K-adjacent matrices 2048 bytes apart
+        if (t < T && lse) lse[(size_t)n * T + t] = (mx + log2f(sum)) * kLn2;
+        if constexpr (!PT) {
+            if (t < T) {
+                // P[r][c], c = r + kk: K-major core matrices (8 rows x 16 bytes), K-adjacent matrices 2048 bytes apart
 #pragma unroll
-            for (int kk = 0; kk < WB; ++kk) {
-                if (kk < win) {
-                    const int c = r + kk;
-                    E* dst = reinterpret_cast<E*>(sP + (c >> 3) * 2048 + r * 16 + (c & 7) * 2);
-                    *dst = (E)(s[kk] * inv);
+                for (int kk = 0; kk < WB; ++kk) {
+                    if (kk < win) {
+                        const int c = r + kk;
+                        E* dst = reinterpret_cast<E*>(sP + (c >> 3) * 2048 + r * 16 + (c & 7) * 2);
+                        *dst = (E)(s[kk] * inv);
+                    }
                 }
             }
-            if (lse) lse[(size_t)n * T + t] = (mx + log2f(sum)) * kLn2;
+        } else {
+            // P goes to tensor memory over the S columns: rotate the band back to its diagonal position
+            // (right by `lane`), pack pairs of 16-bit values per column, zero everything else in the row.
+#pragma unroll
+            for (int i = 0; i < LW; ++i) s[i] = (i < WB && i < win && t < T) ? s[i] * inv : 0.f;
+#pragma unroll
+            for (int b = 1; b <= 16; b <<= 1) {
+                const bool on = (lane & b) != 0;
+#pragma unroll
+                for (int i = LW - 1; i >= 0; --i) {
+                    const float from = (i >= b) ? s[i - b] : 0.f;
+                    s[i] = on ? from : s[i];
+                }
+            }
+            uint32_t w[LW / 2];
+#pragma unroll
+            for (int c = 0; c < LW / 2; ++c) w[c] = Cvt<E>::pack2(s[2 * c], s[2 * c + 1]);
+            const uint32_t prow = tmem + ((uint32_t)(warp * 32) << 16);
+            const uint32_t zeros[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int ci = 0; ci < KT / 16; ++ci)
+                if (ci < 2 * warp || ci >= 2 * warp + LW / 16) ptx::tmem_st8(prow + ci * 8, zeros);
+#pragma unroll
+            for (int cj = 0; cj < LW / 16; ++cj) ptx::tmem_st8(prow + (2 * warp + cj) * 8, &w[cj * 8]);
+            ptx::tmem_st_wait();
         }
     }
     ptx::fence_proxy_async_smem();
@@ -195,9 +221,13 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             const uint32_t idesc = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);
             const uint32_t pa = ptx::smem_u32(sP), va = ptx::smem_u32(sV);
             for (int ks = 0; ks < KT / 16; ++ks) {
-                const uint64_t ad = ptx::smem_desc(pa + ks * 4096, 2048, 128, ptx::kSwizzleNone);
                 const uint64_t bd = ptx::smem_desc(va + ks * 16 * kRowBytes, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
-                ptx::mma_ss(tmem + kOCol, ad, bd, idesc, ks > 0 ? 1u : 0u);
+                if constexpr (PT) {
+                    ptx::mma_ts(tmem + kOCol, tmem + ks * 8, bd, idesc, ks > 0 ? 1u : 0u);
+                } else {
+                    const uint64_t ad = ptx::smem_desc(pa + ks * 4096, 2048, 128, ptx::kSwizzleNone);
+                    ptx::mma_ss(tmem + kOCol, ad, bd, idesc, ks > 0 ? 1u : 0u);
+                }
             }
         }
         ptx::mma_commit(&misc->bar_o);
@@ -261,12 +291,12 @@ bool tc_fwd_supports(const Geometry& gm) {
     return gm.dil == 1 && (gm.C == 64 || gm.C == 32 || gm.C == 16) && gm.win <= 33;
 }
 
-template <typename E, int C, int WB>
+template <typename E, int C, int WB, bool PT>
 static cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* o, float* lse,
                               const float* rpb, const int* valid_len, const Geometry& gm, int tiles_per_seq, int KT,
                               cudaStream_t st) {
     const int smem = fwd_layout(C, KT).total;
-    auto kern = tc_fwd_kernel<E, C, WB>;
+    auto kern = tc_fwd_kernel<E, C, WB, PT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     kern<<<gm.N * tiles_per_seq, 128, smem, st>>>(mq, mk, mv, (E*)o, lse, rpb, valid_len, gm, tiles_per_seq, KT);
@@ -274,7 +304,7 @@ static cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, cons
 }
 
 cudaError_t tc_fused_fwd(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
-                         const int* valid_len, const Geometry& gm, int dtype, cudaStream_t st) {
+                         const int* valid_len, const Geometry& gm, int dtype, bool p_in_tmem, cudaStream_t st) {
     if (!tc_fwd_supports(gm)) return cudaErrorInvalidValue;
     const int KT = round_up(kTileM + gm.win - 1, 16);
     const int tiles_per_seq = (gm.T + kTileM - 1) / kTileM;
@@ -282,7 +312,9 @@ cudaError_t tc_fused_fwd(void* o, float* lse, const void* q, const void* k, cons
     if (!make_row_tile_map(&mq, q, dtype, gm.N, gm.T, gm.C, kTileM) || !make_row_tile_map(&mk, k, dtype, gm.N, gm.T, gm.C, KT) ||
         !make_row_tile_map(&mv, v, dtype, gm.N, gm.T, gm.C, KT))
         return cudaErrorInvalidValue;
-#define NA1D_TC_FWD(E, C, WB) return launch_fwd<E, C, WB>(mq, mk, mv, o, lse, rpb, valid_len, gm, tiles_per_seq, KT, st)
+#define NA1D_TC_FWD(E, C, WB)                                                                                   \
+    return p_in_tmem ? launch_fwd<E, C, WB, true>(mq, mk, mv, o, lse, rpb, valid_len, gm, tiles_per_seq, KT, st) \
+                     : launch_fwd<E, C, WB, false>(mq, mk, mv, o, lse, rpb, valid_len, gm, tiles_per_seq, KT, st)
 #define NA1D_TC_FWD_W(E, C)                          \
     if (gm.win <= 9) { NA1D_TC_FWD(E, C, 9); }       \
     else if (gm.win <= 17) { NA1D_TC_FWD(E, C, 17); } \

@@ -252,13 +252,14 @@ TC_SHAPES = [(N, T, C, win, left) for (N, T) in ((3, 200), (2, 128), (1, 129), (
                                     (16, 3, 2), (64, 8, 3), (32, 17, 16), (64, 9, 4), (16, 18, 9))]
 
 
+@pytest.mark.parametrize("fam", [1, 2], ids=["p_smem", "p_tmem"])
 @pytest.mark.parametrize("dtype", DTYPES, ids=["bf16", "fp16"])
-def test_tcgen05_forward_shapes(dtype):
+def test_tcgen05_forward_shapes(dtype, fam):
     ops = _ops()
-    old = ops.set_kernel_family(ops.FAMILY_TCGEN05)
+    old = ops.set_kernel_family(fam)
     try:
         for idx, (N, T, C, win, left) in enumerate(TC_SHAPES):
-            assert ops.kernel_family(N, T, C, win, left, 1, dtype) == 1, "tcgen05 family should take this shape"
+            assert ops.kernel_family(N, T, C, win, left, 1, dtype) == fam, "tcgen05 family should take this shape"
             H = 1
             sc = C ** -0.5
             q, k, v = (randn16((N, T, C), dtype, 500 + 3 * idx + i) for i in range(3))
@@ -270,6 +271,18 @@ def test_tcgen05_forward_shapes(dtype):
             tag = "N=%d T=%d C=%d win=%d left=%d " % (N, T, C, win, left)
             assert_close(o, o_r, dtype, tag + "o")
             assert float((lse.cpu() - lse_r).abs().max()) < 1e-3 * max(1.0, float(lse_r.abs().max())), tag + "lse"
+            # backward through the tcgen05 family as well
+            assert ops.kernel_family(N, T, C, win, left, 1, dtype, backward=True) == fam
+            d_o = randn16((N, T, C), dtype, 900 + idx)
+            dq, dk, dv, drpb = ops.fused_backward(d_o.cuda(), q.cuda(), k.cuda(), v.cuda(), o, lse, win, left, 1, sc,
+                                                  rpb.cuda(), vl, H, need_d_rpb=True)
+            ops.device_status()
+            _, dq_r, dk_r, dv_r, drpb_r = orc.na1d_fused_with_grads(q.float(), k.float(), v.float(), d_o.float(), win,
+                                                                    left, 1, sc, rpb, vl, H)
+            assert_close(dq, dq_r, dtype, tag + "dq")
+            assert_close(dk, dk_r, dtype, tag + "dk")
+            assert_close(dv, dv_r, dtype, tag + "dv")
+            assert_close(drpb, drpb_r, dtype, tag + "drpb", factor=2.0)
         # shapes outside the family are refused when it is forced, and taken by the CUDA-core kernels otherwise
         assert ops.kernel_family(2, 64, 64, 7, 3, 2, dtype) == -10
         assert ops.kernel_family(2, 64, 24, 7, 3, 1, dtype) == -10
