@@ -2,52 +2,58 @@
 //
 // Tiling. A tile is a window W of 128 consecutive rows of one sequence; consecutive tiles start
 // `stride = 128-(win-1)` rows apart, so they overlap by win-1 rows. All 128 rows act as queries
-// (their band needs keys [w0-left, w0+127+right], staged as KT = round16(128+win-1) rows of K and V);
-// a key row is "interior" when every query that attends it lies in W, which holds for
-// rows [right, 128-left) of W -- exactly `stride` rows, and these are the rows whose dQ, dK and dV
-// this tile stores. Every (query,key) pair of the band is thus seen with both rows inside one tile:
-// no atomics, no second (key-owned) recomputation pass, deterministic results.
+// (their band needs keys [w0-left, w0+127+right]; K and V are staged as KT = round16(128+win-1) rows
+// starting at w0-left). A key row is "interior" when every query that attends it lies in W, which
+// holds for rows [right, 128-left) of W -- exactly `stride` rows, and these are the rows whose dQ, dK
+// and dV this tile stores. Every (query,key) pair of the
+// band is thus seen with both rows inside one tile: no atomics, no second key-owned recomputation,
+// deterministic results.
 //
 // Per tile (one CTA per SM, 192 threads):
 //   warp 4  : TMA producer -- Q[W], dO[W], K[KT], V[KT] into a 2-stage ring (plain tile loads,
 //             out-of-range rows arrive as zeros = the reference's zero padding).
 //   warp 5  : MMA issuer  -- batch 1: S = Q.K^T, dP = dO.V^T (TMEM, N=KT);
-//                            batch 2: dQ = dS.K (A from TMEM), dV = P^T.dO, dK = dS^T.Q (A from smem).
-//   warps0-3: one thread per query row: reads its band of S and dP from TMEM, recomputes
-//             P = exp(S - lse) from the saved log-sum-exp, delta = sum_k P.dP (equal to dot(dO,O), so
-//             neither O nor a separate delta pass is needed), dS = P(dP - delta); writes dS back to
-//             TMEM as a 16-bit A operand and P, dS transposed to shared memory; later reads
-//             dQ/dK/dV from TMEM and stores the rows this tile owns.
+//                            batch 2: dQ = dS.K, dV = P^T.dO, dK = dS^T.Q.
+//   warps0-3: warp w owns query rows 32w..32w+31 (its TMEM lanes) as two 16-row blocks, read as
+//             accumulator fragments (see na1d_tc_common.cuh). P = exp(S - lse) from the saved
+//             log-sum-exp, delta = sum P.dP over the row (equal to dot(dO,O), so neither O nor a separate
+//             delta pass is needed; two quad shuffles), dS = P(dP - delta). P and dS go to shared memory with
+//             stmatrix as 16-bit row-major [query][key] matrices in 8x8 core-matrix order; the same bytes
+//             serve as the K-major A operand of dQ = dS.K and as the MN-major A operand of
+//             dK = dS^T.Q / dV = P^T.dO, so no transpose is ever materialised. dQ rows map to queries
+//             w0+m, dK/dV rows to keys w0-left+m.
 // Replaces the four backward launches of the reference (na1d_tensorcore/nattn.py:46-54, 69-78) and
 // the eager softmax backward between them.
 #include "na1d_internal.h"
-#include "na1d_ptx.cuh"
+#include "na1d_tc_common.cuh"
 
 namespace na1d {
 
 // Device status word of this translation unit (device symbols are per file without relocatable device code).
 __device__ int g_tc_bwd_status = 0;
 
+#ifdef NA1D_TIMELINE
+// Development aid (not compiled by default): clock64 stamps of CTA 0, [tile][slot].
+__device__ long long g_bwd_timeline[64 * 16];
+#define NA1D_STAMP(slot) do { if (blockIdx.x == 0 && it < 64) g_bwd_timeline[it * 16 + (slot)] = clock64(); } while (0)
+#else
+#define NA1D_STAMP(slot) do { } while (0)
+#endif
+
 namespace {
 
-constexpr int kTileM = 128;
+using tc::kTileM;
+using tc::round_up;
+using tc::RowSwizzle;
+using tc::Fmt;
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr int kColDP = 160, kColDQ = 320, kColDK = 384, kColDV = 448;
-
-template <int C> struct RowSwizzle;
-template <> struct RowSwizzle<64> { static constexpr uint64_t umma = ptx::kSwizzle128B; };
-template <> struct RowSwizzle<32> { static constexpr uint64_t umma = ptx::kSwizzle64B; };
-template <> struct RowSwizzle<16> { static constexpr uint64_t umma = ptx::kSwizzle32B; };
-template <typename E> struct Fmt;
-template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
-template <> struct Fmt<__half> { static constexpr uint32_t v = 0; };
-
-__host__ __device__ constexpr int round_up(int x, int m) { return (x + m - 1) / m * m; }
+constexpr int kBiasPad = 16;  // bias table index = kk + kBiasPad; fragment neighbour indices start at -15
 
 struct BwdSmemLayout {
     int stage_q, stage_do, stage_k, stage_v, stage_bytes;  // offsets inside one stage
-    int pt, dst, misc, total;
+    int ds, p, misc, total;
 };
 __host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT) {
     BwdSmemLayout L;
@@ -56,10 +62,10 @@ __host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT) {
     L.stage_k = L.stage_do + round_up(kTileM * C * 2, 1024);
     L.stage_v = L.stage_k + round_up(KT * C * 2, 1024);
     L.stage_bytes = L.stage_v + round_up(KT * C * 2, 1024);
-    L.pt = 2 * L.stage_bytes;
-    L.dst = L.pt + kTileM * kTileM * 2;
-    L.misc = L.dst + kTileM * kTileM * 2;
-    L.total = L.misc + 1024 + 1024;
+    L.ds = 2 * L.stage_bytes;           // dS [128 queries][KT keys]
+    L.p = L.ds + kTileM * KT * 2;       // P  [128 queries][KT keys]
+    L.misc = L.p + kTileM * KT * 2;
+    L.total = L.misc + 1024 + 1008;     // misc block + slack for the manual 1024-byte alignment
     return L;
 }
 
@@ -68,8 +74,7 @@ struct alignas(8) BwdMisc {
     uint64_t s_ready, p_ready, o_ready, o_free;
     uint32_t tmem_base;
     int abort;
-    float rpb[64];
-    float drpb[64];
+    float bias[kBiasPad + 64];  // log2e * rpb[h][kk] at index kk + kBiasPad, zero elsewhere
 };
 
 template <typename E, int C, int WB>
@@ -79,21 +84,22 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               E* __restrict__ dk, E* __restrict__ dv, float* __restrict__ d_rpb, const float* __restrict__ lse,
               const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, int tiles_per_seq, int stride,
               int KT, int total_tiles) {
-    constexpr int LW = round_up(WB + 31, 16);
+    constexpr int NG = tc::band_groups(WB);  // 8-column groups holding the band of a 16-row block
     constexpr int kRowBytes = C * 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const BwdSmemLayout L = bwd_layout(C, KT);
-    uint8_t* sPT = smem + L.pt;
-    uint8_t* sDST = smem + L.dst;
+    uint8_t* sDS = smem + L.ds;
+    uint8_t* sP = smem + L.p;
     BwdMisc* misc = reinterpret_cast<BwdMisc*>(smem + L.misc);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int win = gm.win, left = gm.left, right = gm.win - 1 - gm.left, T = gm.T;
+    const int lboq = KT * 16;  // bytes between 8-query groups of the dS matrix
     const int stage_tx = (2 * kTileM + 2 * KT) * kRowBytes;
 
     if (tid == 0) {
-        for (int s = 0; s < 2; ++s) { ptx::mbar_init(&misc->full[s], 1); ptx::mbar_init(&misc->empty[s], 1); }
+        for (int s = 0; s < 2; ++s) { ptx::mbar_init(&misc->full[s], 1); ptx::mbar_init(&misc->empty[s], 128); }
         ptx::mbar_init(&misc->s_ready, 1);
         ptx::mbar_init(&misc->p_ready, 128);
         ptx::mbar_init(&misc->o_ready, 1);
@@ -110,11 +116,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ptx::tmem_alloc(&misc->tmem_base, kTmemCols);
         ptx::tmem_relinquish();
     }
-    {   // transposed operands start as zeros; the band positions are rewritten every tile
-        uint4* z = reinterpret_cast<uint4*>(sPT);
-        for (int i = tid; i < 2 * kTileM * kTileM * 2 / 16; i += kThreads) z[i] = make_uint4(0, 0, 0, 0);
+    {   // operand matrices start as zeros; each warp rewrites the slab of its own rows every tile
+        uint4* z = reinterpret_cast<uint4*>(sDS);
+        const int n16 = 2 * kTileM * KT * 2 / 16;
+        for (int i = tid; i < n16; i += kThreads) z[i] = make_uint4(0, 0, 0, 0);
     }
-    if (tid < 64) misc->drpb[tid] = 0.f;
     ptx::fence_proxy_async_smem();
     ptx::tc_fence_before_sync();
     __syncthreads();
@@ -143,8 +149,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc_s = ptx::instr_desc(Fmt<E>::v, 0, 0, kTileM, (uint32_t)KT);
-            const uint32_t idesc_o = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);
-            const uint32_t pt_a = ptx::smem_u32(sPT), dst_a = ptx::smem_u32(sDST);
+            const uint32_t idesc_dq = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);   // A K-major, B MN-major
+            const uint32_t idesc_dkv = ptx::instr_desc(Fmt<E>::v, 1, 1, kTileM, (uint32_t)C);  // A MN-major, B MN-major
+            const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
             int it = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1, k = it >> 1;
@@ -152,192 +159,229 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 const uint32_t qa = st + L.stage_q, doa = st + L.stage_do, ka = st + L.stage_k, va = st + L.stage_v;
                 if (!ptx::mbar_wait(&misc->full[s], k & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 12); *abort_flag = 1; break; }
                 ptx::tc_fence_after_sync();
+                NA1D_STAMP(8);
                 // batch 1: S = Q.K^T -> cols [0,KT), dP = dO.V^T -> cols [160,160+KT)
+                {
+                    const uint64_t dq0 = ptx::smem_desc(qa, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                    const uint64_t dk0 = ptx::smem_desc(ka, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                    const uint64_t dd0 = ptx::smem_desc(doa, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                    const uint64_t dv0 = ptx::smem_desc(va, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
 #pragma unroll
-                for (int ks = 0; ks < C / 16; ++ks) {
-                    const uint64_t ad = ptx::smem_desc(qa + ks * 32, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    const uint64_t bd = ptx::smem_desc(ka + ks * 32, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    ptx::mma_ss(tmem, ad, bd, idesc_s, ks > 0 ? 1u : 0u);
-                }
+                    for (int ks = 0; ks < C / 16; ++ks)
+                        ptx::mma_ss(tmem, tc::desc_advance(dq0, ks * 32), tc::desc_advance(dk0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < C / 16; ++ks) {
-                    const uint64_t ad = ptx::smem_desc(doa + ks * 32, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    const uint64_t bd = ptx::smem_desc(va + ks * 32, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    ptx::mma_ss(tmem + kColDP, ad, bd, idesc_s, ks > 0 ? 1u : 0u);
+                    for (int ks = 0; ks < C / 16; ++ks)
+                        ptx::mma_ss(tmem + kColDP, tc::desc_advance(dd0, ks * 32), tc::desc_advance(dv0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
                 }
                 ptx::mma_commit(&misc->s_ready);
+                NA1D_STAMP(9);
                 // operands from the compute warps, and the previous tile's outputs drained
                 if (!ptx::mbar_wait(&misc->p_ready, it & 1) || !ptx::mbar_wait(&misc->o_free, (it & 1) ^ 1) || *abort_flag) {
                     atomicExch(&g_tc_bwd_status, 13); *abort_flag = 1; break;
                 }
                 ptx::tc_fence_after_sync();
-                // batch 2: dQ = dS.K (A: TMEM cols [0,KT/2), 16-bit pairs), dV = P^T.dO, dK = dS^T.Q
-                for (int ks = 0; ks < KT / 16; ++ks) {
-                    const uint64_t bd = ptx::smem_desc(ka + ks * 16 * kRowBytes, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    ptx::mma_ts(tmem + kColDQ, tmem + ks * 8, bd, idesc_o, ks > 0 ? 1u : 0u);
-                }
+                NA1D_STAMP(10);
+                // batch 2. dS/P matrices: element (q, c) at (q/8)*lboq + (c/8)*128 + (q%8)*16 + (c%8)*2.
+                {
+                    //   dQ = dS.K   : A K-major (M = queries, K = KT keys): K-adjacent core matrices 128 B apart, 8-row groups lboq apart
+                    const uint64_t a_dq = ptx::smem_desc(ds_a, 128, lboq, ptx::kSwizzleNone);
+                    //   dV = P^T.dO, dK = dS^T.Q : the same matrices read MN-major (M = first 128 keys of the K window,
+                    //   K = queries): 8-key groups 128 B apart, 8-query groups lboq apart
+                    const uint64_t a_dv = ptx::smem_desc(p_a, lboq, 128, ptx::kSwizzleNone);
+                    const uint64_t a_dk = ptx::smem_desc(ds_a, lboq, 128, ptx::kSwizzleNone);
+                    const uint64_t b_k = ptx::smem_desc(ka, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
+                    const uint64_t b_do = ptx::smem_desc(doa, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
+                    const uint64_t b_q = ptx::smem_desc(qa, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
+                    const int nks = KT / 16;
+#pragma unroll 1
+                    for (int ks = 0; ks < nks; ++ks)
+                        ptx::mma_ss(tmem + kColDQ, tc::desc_advance(a_dq, ks * 256), tc::desc_advance(b_k, ks * 16 * kRowBytes), idesc_dq, ks > 0 ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < kTileM / 16; ++ks) {
-                    const uint64_t ad = ptx::smem_desc(pt_a + ks * 4096, 2048, 128, ptx::kSwizzleNone);
-                    const uint64_t bd = ptx::smem_desc(doa + ks * 16 * kRowBytes, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    ptx::mma_ss(tmem + kColDV, ad, bd, idesc_o, ks > 0 ? 1u : 0u);
-                }
+                    for (int ks = 0; ks < kTileM / 16; ++ks)
+                        ptx::mma_ss(tmem + kColDV, tc::desc_advance(a_dv, ks * 2 * lboq), tc::desc_advance(b_do, ks * 16 * kRowBytes), idesc_dkv, ks > 0 ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < kTileM / 16; ++ks) {
-                    const uint64_t ad = ptx::smem_desc(dst_a + ks * 4096, 2048, 128, ptx::kSwizzleNone);
-                    const uint64_t bd = ptx::smem_desc(qa + ks * 16 * kRowBytes, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    ptx::mma_ss(tmem + kColDK, ad, bd, idesc_o, ks > 0 ? 1u : 0u);
+                    for (int ks = 0; ks < kTileM / 16; ++ks)
+                        ptx::mma_ss(tmem + kColDK, tc::desc_advance(a_dk, ks * 2 * lboq), tc::desc_advance(b_q, ks * 16 * kRowBytes), idesc_dkv, ks > 0 ? 1u : 0u);
                 }
                 ptx::mma_commit(&misc->o_ready);
-                ptx::mma_commit(&misc->empty[s]);
+                NA1D_STAMP(11);
             }
         }
     } else {
-        // ------------------------------------------------------------ compute warps: one thread per query row
-        const int r = warp * 32 + lane;
+        // ------------------------------------------------------------ compute warps
+        const int r = warp * 32 + lane;                 // row of the 32x32b epilogue loads
+        const int fr = lane >> 2, fc = 2 * (lane & 3);  // fragment row / first column inside an 8x8 block
+        const int fa = fc - fr;                         // neighbour index = 8(n-h) + e + fa
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
         const float sc = gm.scale * kLog2e;
-        float drpb_acc[WB];
-#pragma unroll
-        for (int kk = 0; kk < WB; ++kk) drpb_acc[kk] = 0.f;
+        const float mask2 = kMaskValue * kLog2e;
+        const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
         int it = 0;
         int cached_h = -1;
+        // log-sum-exp of the four fragment rows of a tile; loaded one tile ahead so the DRAM latency is hidden
+        auto load_lse = [&](int tile_, float (&dst)[2][2]) {
+            const int n_ = tile_ / tiles_per_seq;
+            const int w0_ = (tile_ - n_ * tiles_per_seq) * stride - right;
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int t = w0_ + warp * 32 + 16 * b + 8 * hh + fr;
+                    dst[b][hh] = (tile_ < total_tiles && t >= 0 && t < T) ? __ldg(lse + (size_t)n_ * T + t) : 0.f;
+                }
+        };
+        float lse_next[2][2];
+        load_lse(blockIdx.x, lse_next);
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+            if (tid == 0) NA1D_STAMP(0);
             const int n = tile / tiles_per_seq;
             const int w0 = (tile - n * tiles_per_seq) * stride - right;
-            const int t = w0 + r;
             const int h = n % gm.H;
-            const bool valid_q = t >= 0 && t < T;
-            const bool owned = valid_q && r >= right && r < kTileM - left;
             const int vl = valid_len ? __ldg(valid_len + n / gm.H) : T;
-            const float lse2 = valid_q ? __ldg(lse + (size_t)n * T + t) * kLog2e : 0.f;
-            if (h != cached_h) {
-                // rpb row of this head (all compute threads agree on h; sync among the 4 compute warps only)
+            const int jmax = min(T, vl);
+            // the four query rows this thread sees in the fragments: block b, row half hh (lse was fetched one tile ahead)
+            float lse2[2][2];
+            bool vq[2][2], qm[2][2];
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int t = w0 + warp * 32 + 16 * b + 8 * hh + fr;
+                    vq[b][hh] = t >= 0 && t < T;
+                    qm[b][hh] = t >= vl;
+                    lse2[b][hh] = lse_next[b][hh] * kLog2e;
+                }
+            if (rpb && h != cached_h) {
+                // bias table of this head (all compute threads agree on h; barrier among the 4 compute warps only)
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (r < win) misc->rpb[r] = rpb ? __ldg(rpb + h * win + r) : 0.f;
+                if (r < kBiasPad + 64) {
+                    const int kk = r - kBiasPad;
+                    misc->bias[r] = (kk >= 0 && kk < win) ? __ldg(rpb + h * win + kk) * kLog2e : 0.f;
+                }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 cached_h = h;
             }
+            // masks are needed only when the warp's keys or queries touch a sequence end or the padded region
+            const int jlo = w0 - left + warp * 32, jhi = jlo + 16 + 8 * NG + 16;
+            const bool need_mask = jlo < 0 || jhi > jmax || (w0 + warp * 32 + 32 > vl);
+            if (tid == 0) NA1D_STAMP(1);
             if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 14); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
-            float s[LW], d[LW];
+            if (tid == 0) NA1D_STAMP(2);
+
+            float s[2][4 * NG], d[2][4 * NG];
 #pragma unroll
-            for (int c = 0; c < LW; c += 8) ptx::tmem_ld8(lane_base + warp * 32 + c, &s[c]);
-#pragma unroll
-            for (int c = 0; c < LW; c += 8) ptx::tmem_ld8(lane_base + kColDP + warp * 32 + c, &d[c]);
+            for (int b = 0; b < 2; ++b) {
+                const uint32_t a = lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b);
+                tc::ld_frag<NG>(a, s[b]);
+                tc::ld_frag<NG>(a + kColDP, d[b]);
+            }
             ptx::tmem_ld_wait();
+            if (tid == 0) NA1D_STAMP(3);
+            float delta[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
-            for (int b = 16; b >= 1; b >>= 1) {
-                const bool on = (lane & b) != 0;
+            for (int b = 0; b < 2; ++b)
 #pragma unroll
-                for (int i = 0; i < WB + b - 1; ++i) { s[i] = on ? s[i + b] : s[i]; d[i] = on ? d[i + b] : d[i]; }
-            }
-            // P, delta, dS on the band
-            float delta = 0.f;
+                for (int g = 0; g < NG; ++g)
 #pragma unroll
-            for (int kk = 0; kk < WB; ++kk) {
-                if (kk < win) {
-                    const int j = neighbour(t, kk, left, 1);
-                    const bool masked = (j < 0) | (j >= T) | (j >= vl) | (t >= vl);
-                    const float x = fmaf(s[kk], sc, (misc->rpb[kk] + (masked ? kMaskValue : 0.f)) * kLog2e) - lse2;
-                    const float p = valid_q ? exp2f(x) : 0.f;
-                    s[kk] = p;
-                    delta = fmaf(p, d[kk], delta);
-                } else {
-                    s[kk] = 0.f; d[kk] = 0.f;
-                }
-            }
+                    for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
-            for (int kk = 0; kk < WB; ++kk) {
-                const float ds = s[kk] * (d[kk] - delta);
-                if (owned) drpb_acc[kk] += ds;
-                d[kk] = ds * gm.scale;
-            }
-            // transposed operands: row m = key index inside W, column r = this query
+                        for (int e = 0; e < 2; ++e) {
+                            const int idx = 4 * g + 2 * hh + e;
+                            const int kk = 8 * (g - hh) + e + fa;
+                            const bool inband = (unsigned)kk < (unsigned)win;
+                            float bias = 0.f;
+                            if (rpb) bias = misc->bias[kk + kBiasPad];
+                            if (need_mask) {
+                                const int j = w0 - left + warp * 32 + 16 * b + 8 * g + fc + e;
+                                if (j < 0 || j >= jmax || qm[b][hh]) bias += mask2;
+                            }
+                            const float x = fmaf(s[b][idx], sc, bias) - lse2[b][hh];
+                            const float p = (inband && vq[b][hh]) ? tc::fast_exp2(x) : 0.f;
+                            s[b][idx] = p;
+                            delta[b][hh] = fmaf(p, d[b][idx], delta[b][hh]);
+                        }
 #pragma unroll
-            for (int kk = 0; kk < WB; ++kk) {
-                if (kk < win) {
-                    const int m = r + kk - left;
-                    if (m >= 0 && m < kTileM) {
-                        const int off = (r >> 3) * 2048 + m * 16 + (r & 7) * 2;
-                        *reinterpret_cast<E*>(sPT + off) = (E)s[kk];
-                        *reinterpret_cast<E*>(sDST + off) = (E)d[kk];
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) delta[b][hh] = tc::quad_sum(delta[b][hh]);
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                uint32_t pk_p[2 * NG], pk_d[2 * NG];
+#pragma unroll
+                for (int g = 0; g < NG; ++g)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const int idx = 4 * g + 2 * hh;
+                        const float ds0 = s[b][idx] * (d[b][idx] - delta[b][hh]);
+                        const float ds1 = s[b][idx + 1] * (d[b][idx + 1] - delta[b][hh]);
+                        pk_d[2 * g + hh] = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
+                        pk_p[2 * g + hh] = Cvt<E>::pack2(s[b][idx], s[b][idx + 1]);
                     }
-                }
+                // core matrix of the block's first row / first column: row group 4w+2b, column group 4w+2b
+                const uint32_t blk = (uint32_t)(4 * warp + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * warp + 2 * b) * 128u;
+                tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d, lane);
+                tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
             }
-            // dS as a 16-bit A operand in TMEM over the S columns: rotate the band back to its diagonal
-#pragma unroll
-            for (int i = WB; i < LW; ++i) d[i] = 0.f;
-#pragma unroll
-            for (int b = 1; b <= 16; b <<= 1) {
-                const bool on = (lane & b) != 0;
-#pragma unroll
-                for (int i = LW - 1; i >= 0; --i) {
-                    const float from = (i >= b) ? d[i - b] : 0.f;
-                    d[i] = on ? from : d[i];
-                }
-            }
-            {
-                uint32_t w[LW / 2];
-#pragma unroll
-                for (int c = 0; c < LW / 2; ++c) w[c] = Cvt<E>::pack2(d[2 * c], d[2 * c + 1]);
-                const uint32_t zeros[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                for (int ci = 0; ci < KT / 16; ++ci)
-                    if (ci < 2 * warp || ci >= 2 * warp + LW / 16) ptx::tmem_st8(lane_base + ci * 8, zeros);
-#pragma unroll
-                for (int cj = 0; cj < LW / 16; ++cj) ptx::tmem_st8(lane_base + (2 * warp + cj) * 8, &w[cj * 8]);
-                ptx::tmem_st_wait();
-            }
+            if (tid == 0) NA1D_STAMP(4);
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&misc->p_ready);
+            load_lse(tile + gridDim.x, lse_next);
+            if (tid == 0) NA1D_STAMP(5);
+            if (d_rpb) {
+                // d_rpb[h][kk] += dS over the query rows this tile owns: thread r reads the band of row r back
+                // from the dS operand (16-bit, scaled), the warp reduces, one atomic per warp and neighbour
+                __syncwarp();
+                const bool own = r >= right && r < kTileM - left && (w0 + r) >= 0 && (w0 + r) < T;
+                const float inv_scale = 1.f / gm.scale;
+                const uint8_t* row = sDS + (r >> 3) * lboq + (r & 7) * 16;
+#pragma unroll
+                for (int kk = 0; kk < WB; ++kk) {
+                    if (kk < win) {
+                        const int col = r + kk;
+                        float x = own ? (float)*reinterpret_cast<const E*>(row + (col >> 3) * 128 + (col & 7) * 2) * inv_scale : 0.f;
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+                        if (lane == 0 && x != 0.f) atomicAdd(d_rpb + h * win + kk, x);
+                    }
+                }
+            }
 
-            // epilogue: dQ, dK, dV rows owned by this tile
+            // epilogue (one thread per accumulator row m): dQ row m is query w0+m, dK/dV row m is key w0-left+m
             if (!ptx::mbar_wait(&misc->o_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 15); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
-            const size_t row_off = ((size_t)n * T + (valid_q ? t : 0)) * C;
+            if (tid == 0) NA1D_STAMP(6);
             {
+                // rows of this warp: accumulator row m = 32w + i; dQ row m is query w0+m, dK/dV row m is key w0-left+m
+                const int m0 = warp * 32;
+                uint8_t* stage = smem + (it & 1) * L.stage_bytes + L.stage_q + m0 * kRowBytes;  // the tile's own Q buffer, now idle
+                auto own_q = [&](int i) { const int m = m0 + i, t = w0 + m; return m >= right && m < kTileM - left && t >= 0 && t < T; };
+                auto own_k = [&](int i) { const int m = m0 + i, t = w0 - left + m; return m >= win - 1 && t >= 0 && t < T; };
+                // row pointers may lie before the tensor for rows that are not stored; only offsets of stored rows are dereferenced
+                E* q_row0 = dq + ((ptrdiff_t)n * T + (w0 + m0)) * C;
+                E* k_row0 = dk + ((ptrdiff_t)n * T + (w0 - left + m0)) * C;
+                E* v_row0 = dv + ((ptrdiff_t)n * T + (w0 - left + m0)) * C;
                 float acc[C];
 #pragma unroll
                 for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + kColDQ + c, &acc[c]);
                 ptx::tmem_ld_wait();
-                if (owned) {
-                    uint4* dst = reinterpret_cast<uint4*>(dq + row_off);
-#pragma unroll
-                    for (int c = 0; c < C / 8; ++c) dst[c] = Cvt<E>::pack(&acc[c * 8]);
-                }
+                tc::store_rows_coalesced<E, C>(stage, acc, q_row0, lane, own_q);
 #pragma unroll
                 for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + kColDK + c, &acc[c]);
                 ptx::tmem_ld_wait();
-                if (owned) {
-                    uint4* dst = reinterpret_cast<uint4*>(dk + row_off);
-#pragma unroll
-                    for (int c = 0; c < C / 8; ++c) dst[c] = Cvt<E>::pack(&acc[c * 8]);
-                }
+                tc::store_rows_coalesced<E, C>(stage, acc, k_row0, lane, own_k);
 #pragma unroll
                 for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + kColDV + c, &acc[c]);
                 ptx::tmem_ld_wait();
                 ptx::tc_fence_before_sync();
                 ptx::mbar_arrive(&misc->o_free);
-                if (owned) {
-                    uint4* dst = reinterpret_cast<uint4*>(dv + row_off);
-#pragma unroll
-                    for (int c = 0; c < C / 8; ++c) dst[c] = Cvt<E>::pack(&acc[c * 8]);
-                }
+                tc::store_rows_coalesced<E, C>(stage, acc, v_row0, lane, own_k);
+                // the staging reads are done: the producer may refill this stage
+                __syncwarp();
+                ptx::mbar_arrive(&misc->empty[it & 1]);
             }
-            // d_rpb changes head when the sequence changes: flush per tile (cheap: win shared atomics per warp)
-            if (d_rpb) {
-#pragma unroll
-                for (int kk = 0; kk < WB; ++kk) {
-                    if (kk < win) {
-                        float x = drpb_acc[kk];
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
-                        if (lane == 0 && x != 0.f) atomicAdd(d_rpb + h * win + kk, x);
-                    }
-                    drpb_acc[kk] = 0.f;
-                }
-            }
+            if (tid == 0) NA1D_STAMP(7);
         }
     }
     ptx::tc_fence_before_sync();
@@ -365,10 +409,8 @@ cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUte
 
 }  // namespace
 
-bool make_row_tile_map(CUtensorMap* map, const void* base, int dtype, int N, int T, int C, int box_rows);
-
 bool tc_bwd_supports(const Geometry& gm) {
-    return gm.dil == 1 && (gm.C == 64 || gm.C == 32 || gm.C == 16) && gm.win <= 33 && gm.H * gm.win <= 1 << 20;
+    return gm.dil == 1 && (gm.C == 64 || gm.C == 32 || gm.C == 16) && gm.win <= 33;
 }
 
 int device_sm_count() {
@@ -390,6 +432,12 @@ int tc_bwd_read_status() {
     if (v != 0) cudaMemcpyToSymbol(g_tc_bwd_status, &zero, sizeof(int));
     return v;
 }
+
+#ifdef NA1D_TIMELINE
+extern "C" int na1d_debug_bwd_timeline(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_bwd_timeline, sizeof(long long) * 64 * 16);
+}
+#endif
 
 cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
                          const void* v, const float* lse, const float* rpb, const int* valid_len, const Geometry& gm, int dtype,
