@@ -101,7 +101,7 @@ static int pick_family(const na1d::Geometry& g, int backward) {
     const int forced = g_family_override.load();
     const bool tc_ok = backward ? na1d::tc_bwd_supports(g) : na1d::tc_fwd_supports(g);
     if (forced == 0) return 0;
-    if (forced >= 1) return tc_ok ? forced : NA1D_ERR_UNSUPPORTED;
+    if (forced == 1) return tc_ok ? 1 : NA1D_ERR_UNSUPPORTED;
     return tc_ok ? 1 : 0;
 }
 
@@ -113,7 +113,7 @@ int na1d_fused_kernel_family(int64_t N, int64_t T, int64_t C, int64_t win, int64
 }
 
 int na1d_set_kernel_family(int family) {
-    if (family < -1 || family > 2) family = -1;
+    if (family < -1 || family > 1) family = -1;
     return g_family_override.exchange(family);
 }
 
@@ -133,7 +133,7 @@ int na1d_fused_forward(void* o, float* lse, const void* q, const void* k, const 
     if (int s = check_geometry(N, heads, T, C, win, left, dil, dtype, scale, g)) return s;
     const int fam = pick_family(g, 0);
     if (fam < 0) return fam;
-    if (fam >= 1) return cuda_status(na1d::tc_fused_fwd(o, lse, q, k, v, rpb, valid_len, g, dtype, fam == 2, (cudaStream_t)stream));
+    if (fam == 1) return cuda_status(na1d::tc_fused_fwd(o, lse, q, k, v, rpb, valid_len, g, dtype, (cudaStream_t)stream));
     return cuda_status(na1d::simt_fused_fwd(o, lse, q, k, v, rpb, valid_len, g, dtype, (cudaStream_t)stream));
 }
 
@@ -151,7 +151,7 @@ int na1d_fused_backward(void* dq, void* dk, void* dv, float* d_rpb, const void* 
     cudaStream_t st = (cudaStream_t)stream;
     const int fam = pick_family(g, 1);
     if (fam < 0) return fam;
-    if (fam >= 1)  // delta is recomputed inside the kernel from P and dP: neither o nor delta_ws is touched
+    if (fam == 1)  // delta is recomputed inside the kernel from P and dP: neither o nor delta_ws is touched
         return cuda_status(na1d::tc_fused_bwd(dq, dk, dv, d_rpb, d_o, q, k, v, lse, rpb, valid_len, g, dtype, st));
     if (int s = cuda_status(na1d::simt_delta(delta_ws, d_o, o, g.N * g.T, g.C, dtype, st))) return s;
     return cuda_status(na1d::simt_fused_bwd(dq, dk, dv, d_rpb, d_o, q, k, v, lse, delta_ws, rpb, valid_len, g, dtype, st));

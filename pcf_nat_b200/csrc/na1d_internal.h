@@ -20,7 +20,7 @@ cudaError_t window_index(int* j_out, unsigned char* inr, int T, int win, int lef
 // ---- tcgen05 / TMA family (na1d_tc_fwd.cu)
 bool tc_fwd_supports(const Geometry& gm);
 cudaError_t tc_fused_fwd(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
-                         const int* valid_len, const Geometry& gm, int dtype, bool p_in_tmem, cudaStream_t st);
+                         const int* valid_len, const Geometry& gm, int dtype, cudaStream_t st);
 int tc_read_status();
 int tc_bwd_read_status();
 bool tc_bwd_supports(const Geometry& gm);

@@ -413,18 +413,6 @@ bool tc_bwd_supports(const Geometry& gm) {
     return gm.dil == 1 && (gm.C == 64 || gm.C == 32 || gm.C == 16) && gm.win <= 33;
 }
 
-int device_sm_count() {
-    static int cached[64] = {0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int n = 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
-    }
-    return cached[dev];
-}
-
 // Reads and clears the backward kernels' status word (synchronises the device).
 int tc_bwd_read_status() {
     int v = 0, zero = 0;

@@ -252,10 +252,10 @@ TC_SHAPES = [(N, T, C, win, left) for (N, T) in ((3, 200), (2, 128), (1, 129), (
                                     (16, 3, 2), (64, 8, 3), (32, 17, 16), (64, 9, 4), (16, 18, 9))]
 
 
-@pytest.mark.parametrize("fam", [1, 2], ids=["p_smem", "p_tmem"])
 @pytest.mark.parametrize("dtype", DTYPES, ids=["bf16", "fp16"])
-def test_tcgen05_forward_shapes(dtype, fam):
+def test_tcgen05_forward_backward_shapes(dtype):
     ops = _ops()
+    fam = ops.FAMILY_TCGEN05
     old = ops.set_kernel_family(fam)
     try:
         for idx, (N, T, C, win, left) in enumerate(TC_SHAPES):
