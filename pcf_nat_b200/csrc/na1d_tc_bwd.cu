@@ -9,19 +9,23 @@
 // band is thus seen with both rows inside one tile: no atomics, no second key-owned recomputation,
 // deterministic results.
 //
-// Per tile (one CTA per SM, 192 threads):
-//   warp 4  : TMA producer -- Q[W], dO[W], K[KT], V[KT] into a 2-stage ring (plain tile loads,
+// Per tile (one CTA per SM, 320 threads):
+//   warp 8  : TMA producer -- Q[W], dO[W], K[KT], V[KT] into a 2-stage ring (plain tile loads,
 //             out-of-range rows arrive as zeros = the reference's zero padding).
-//   warp 5  : MMA issuer  -- batch 1: S = Q.K^T, dP = dO.V^T (TMEM, N=KT);
+//   warp 9  : MMA issuer  -- batch 1: S = Q.K^T, dP = dO.V^T (TMEM, N=KT);
 //                            batch 2: dQ = dS.K, dV = P^T.dO, dK = dS^T.Q.
-//   warps0-3: warp w owns query rows 32w..32w+31 (its TMEM lanes) as two 16-row blocks, read as
+//             Batch 1 of the NEXT tile is issued before batch 2 of the current one, so the compute warps
+//             work on tile i+1 while the tensor pipe finishes tile i.
+//   warps0-3: compute. Warp w owns query rows 32w..32w+31 (its TMEM lanes) as two 16-row blocks, read as
 //             accumulator fragments (see na1d_tc_common.cuh). P = exp(S - lse) from the saved
 //             log-sum-exp, delta = sum P.dP over the row (equal to dot(dO,O), so neither O nor a separate
 //             delta pass is needed; two quad shuffles), dS = P(dP - delta). P and dS go to shared memory with
 //             stmatrix as 16-bit row-major [query][key] matrices in 8x8 core-matrix order; the same bytes
 //             serve as the K-major A operand of dQ = dS.K and as the MN-major A operand of
-//             dK = dS^T.Q / dV = P^T.dO, so no transpose is ever materialised. dQ rows map to queries
-//             w0+m, dK/dV rows to keys w0-left+m.
+//             dK = dS^T.Q / dV = P^T.dO, so no transpose is ever materialised.
+//   warps4-7: epilogue. Read dQ/dK/dV from TMEM (row m of dQ is query w0+m, row m of dK/dV is key
+//             w0-left+m), round to 16 bits, stage the `stride` owned rows in the tile's idle Q/dO/K buffers
+//             in the TMA swizzle and issue three TMA tile stores (rows >= T are clipped by the tensor map).
 // Replaces the four backward launches of the reference (na1d_tensorcore/nattn.py:46-54, 69-78) and
 // the eager softmax backward between them.
 #include "na1d_internal.h"
@@ -46,14 +50,16 @@ using tc::kTileM;
 using tc::round_up;
 using tc::RowSwizzle;
 using tc::Fmt;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr int kTmemCols = 512;
 constexpr int kColDP = 160, kColDQ = 320, kColDK = 384, kColDV = 448;
 constexpr int kBiasPad = 16;  // bias table index = kk + kBiasPad; fragment neighbour indices start at -15
 
 struct BwdSmemLayout {
     int stage_q, stage_do, stage_k, stage_v, stage_bytes;  // offsets inside one stage
-    int ds, p, misc, total;
+    int ds, p, out, misc, total;
+    bool own_out;  // a dedicated 128-row staging buffer for the outputs fits next to everything else
 };
 __host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT) {
     BwdSmemLayout L;
@@ -64,14 +70,16 @@ __host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT) {
     L.stage_bytes = L.stage_v + round_up(KT * C * 2, 1024);
     L.ds = 2 * L.stage_bytes;           // dS [128 queries][KT keys]
     L.p = L.ds + kTileM * KT * 2;       // P  [128 queries][KT keys]
-    L.misc = L.p + kTileM * KT * 2;
+    L.out = L.p + kTileM * KT * 2;
+    L.own_out = L.out + round_up(kTileM * C * 2, 1024) + 1024 + 1008 <= 227 * 1024;
+    L.misc = L.out + (L.own_out ? round_up(kTileM * C * 2, 1024) : 0);
     L.total = L.misc + 1024 + 1008;     // misc block + slack for the manual 1024-byte alignment
     return L;
 }
 
 struct alignas(8) BwdMisc {
     uint64_t full[2], empty[2];
-    uint64_t s_ready, p_ready, o_ready, o_free;
+    uint64_t s_ready, s_free, p_ready, o_ready, o_free;
     uint32_t tmem_base;
     int abort;
     float bias[kBiasPad + 64];  // log2e * rpb[h][kk] at index kk + kBiasPad, zero elsewhere
@@ -80,8 +88,9 @@ struct alignas(8) BwdMisc {
 template <typename E, int C, int WB>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-              const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, E* __restrict__ dq,
-              E* __restrict__ dk, E* __restrict__ dv, float* __restrict__ d_rpb, const float* __restrict__ lse,
+              const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+              const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk,
+              const __grid_constant__ CUtensorMap tm_dv, float* __restrict__ d_rpb, const float* __restrict__ lse,
               const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, int tiles_per_seq, int stride,
               int KT, int total_tiles) {
     constexpr int NG = tc::band_groups(WB);  // 8-column groups holding the band of a 16-row block
@@ -99,8 +108,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int stage_tx = (2 * kTileM + 2 * KT) * kRowBytes;
 
     if (tid == 0) {
-        for (int s = 0; s < 2; ++s) { ptx::mbar_init(&misc->full[s], 1); ptx::mbar_init(&misc->empty[s], 128); }
+        for (int s = 0; s < 2; ++s) { ptx::mbar_init(&misc->full[s], 1); ptx::mbar_init(&misc->empty[s], 1); }
         ptx::mbar_init(&misc->s_ready, 1);
+        ptx::mbar_init(&misc->s_free, 128);
         ptx::mbar_init(&misc->p_ready, 128);
         ptx::mbar_init(&misc->o_ready, 1);
         ptx::mbar_init(&misc->o_free, 128);
@@ -110,6 +120,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ptx::prefetch_tensormap(&tm_do);
         ptx::prefetch_tensormap(&tm_k);
         ptx::prefetch_tensormap(&tm_v);
+        ptx::prefetch_tensormap(&tm_dq);
+        ptx::prefetch_tensormap(&tm_dk);
+        ptx::prefetch_tensormap(&tm_dv);
     }
     if (warp == 0) {
         __syncwarp();
@@ -128,7 +141,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const uint32_t tmem = misc->tmem_base;
     volatile int* abort_flag = &misc->abort;
 
-    if (warp == 4) {
+    if (warp == kProducerWarp) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             int it = 0;
@@ -145,40 +158,49 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 ptx::tma_load_3d(st + L.stage_v, &tm_v, &misc->full[s], 0, w0 - left, n);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc_s = ptx::instr_desc(Fmt<E>::v, 0, 0, kTileM, (uint32_t)KT);
             const uint32_t idesc_dq = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);   // A K-major, B MN-major
             const uint32_t idesc_dkv = ptx::instr_desc(Fmt<E>::v, 1, 1, kTileM, (uint32_t)C);  // A MN-major, B MN-major
             const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
-            int it = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-                const int s = it & 1, k = it >> 1;
+            const int nks = KT / 16;
+            // batch 1 of tile `jt`: S = Q.K^T -> cols [0,KT), dP = dO.V^T -> cols [160,160+KT)
+            auto batch1 = [&](int jt) -> bool {
+                const int s = jt & 1, k = jt >> 1;
+                if (!ptx::mbar_wait(&misc->full[s], k & 1)) return false;
+                ptx::tc_fence_after_sync();
                 const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
-                const uint32_t qa = st + L.stage_q, doa = st + L.stage_do, ka = st + L.stage_k, va = st + L.stage_v;
-                if (!ptx::mbar_wait(&misc->full[s], k & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 12); *abort_flag = 1; break; }
+                const uint64_t dq0 = ptx::smem_desc(st + L.stage_q, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                const uint64_t dk0 = ptx::smem_desc(st + L.stage_k, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                const uint64_t dd0 = ptx::smem_desc(st + L.stage_do, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                const uint64_t dv0 = ptx::smem_desc(st + L.stage_v, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+#pragma unroll
+                for (int ks = 0; ks < C / 16; ++ks)
+                    ptx::mma_ss(tmem, tc::desc_advance(dq0, ks * 32), tc::desc_advance(dk0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
+#pragma unroll
+                for (int ks = 0; ks < C / 16; ++ks)
+                    ptx::mma_ss(tmem + kColDP, tc::desc_advance(dd0, ks * 32), tc::desc_advance(dv0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
+                ptx::mma_commit(&misc->s_ready);
+                return true;
+            };
+            int it = 0;
+            bool ok = blockIdx.x < total_tiles ? batch1(0) : true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+                const int s = it & 1;
+                const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
+                const uint32_t qa = st + L.stage_q, doa = st + L.stage_do, ka = st + L.stage_k;
+                // S/dP of this tile are in the compute warps' registers: the next tile's batch 1 may overwrite them
+                if (!ptx::mbar_wait(&misc->s_free, it & 1) || *abort_flag) { ok = false; break; }
                 ptx::tc_fence_after_sync();
                 NA1D_STAMP(8);
-                // batch 1: S = Q.K^T -> cols [0,KT), dP = dO.V^T -> cols [160,160+KT)
-                {
-                    const uint64_t dq0 = ptx::smem_desc(qa, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    const uint64_t dk0 = ptx::smem_desc(ka, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    const uint64_t dd0 = ptx::smem_desc(doa, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    const uint64_t dv0 = ptx::smem_desc(va, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-#pragma unroll
-                    for (int ks = 0; ks < C / 16; ++ks)
-                        ptx::mma_ss(tmem, tc::desc_advance(dq0, ks * 32), tc::desc_advance(dk0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
-#pragma unroll
-                    for (int ks = 0; ks < C / 16; ++ks)
-                        ptx::mma_ss(tmem + kColDP, tc::desc_advance(dd0, ks * 32), tc::desc_advance(dv0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
-                }
-                ptx::mma_commit(&misc->s_ready);
+                if (tile + gridDim.x < total_tiles && !batch1(it + 1)) { ok = false; break; }
                 NA1D_STAMP(9);
-                // operands from the compute warps, and the previous tile's outputs drained
-                if (!ptx::mbar_wait(&misc->p_ready, it & 1) || !ptx::mbar_wait(&misc->o_free, (it & 1) ^ 1) || *abort_flag) {
-                    atomicExch(&g_tc_bwd_status, 13); *abort_flag = 1; break;
-                }
+                // the compute warps have written this tile's operands
+                if (!ptx::mbar_wait(&misc->p_ready, it & 1) || *abort_flag) { ok = false; break; }
+                // the epilogue warps have drained the previous tile's outputs
+                if (!ptx::mbar_wait(&misc->o_free, (it & 1) ^ 1) || *abort_flag) { ok = false; break; }
                 ptx::tc_fence_after_sync();
                 NA1D_STAMP(10);
                 // batch 2. dS/P matrices: element (q, c) at (q/8)*lboq + (c/8)*128 + (q%8)*16 + (c%8)*2.
@@ -192,7 +214,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     const uint64_t b_k = ptx::smem_desc(ka, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
                     const uint64_t b_do = ptx::smem_desc(doa, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
                     const uint64_t b_q = ptx::smem_desc(qa, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    const int nks = KT / 16;
 #pragma unroll 1
                     for (int ks = 0; ks < nks; ++ks)
                         ptx::mma_ss(tmem + kColDQ, tc::desc_advance(a_dq, ks * 256), tc::desc_advance(b_k, ks * 16 * kRowBytes), idesc_dq, ks > 0 ? 1u : 0u);
@@ -204,10 +225,12 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                         ptx::mma_ss(tmem + kColDK, tc::desc_advance(a_dk, ks * 2 * lboq), tc::desc_advance(b_q, ks * 16 * kRowBytes), idesc_dkv, ks > 0 ? 1u : 0u);
                 }
                 ptx::mma_commit(&misc->o_ready);
+                if (L.own_out) ptx::mma_commit(&misc->empty[s]);  // the stage is free once batch 2 has read it
                 NA1D_STAMP(11);
             }
+            if (!ok) { atomicExch(&g_tc_bwd_status, 12); *abort_flag = 1; }
         }
-    } else {
+    } else if (warp < 4) {
         // ------------------------------------------------------------ compute warps
         const int r = warp * 32 + lane;                 // row of the 32x32b epilogue loads
         const int fr = lane >> 2, fc = 2 * (lane & 3);  // fragment row / first column inside an 8x8 block
@@ -277,6 +300,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 tc::ld_frag<NG>(a + kColDP, d[b]);
             }
             ptx::tmem_ld_wait();
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(&misc->s_free);
             if (tid == 0) NA1D_STAMP(3);
             float delta[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
@@ -305,6 +330,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             for (int b = 0; b < 2; ++b)
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) delta[b][hh] = tc::quad_sum(delta[b][hh]);
+            // batch 2 of the previous tile must have finished reading the operand matrices before they are rewritten
+            if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
                 uint32_t pk_p[2 * NG], pk_d[2 * NG];
@@ -348,41 +375,99 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 }
             }
 
-            // epilogue (one thread per accumulator row m): dQ row m is query w0+m, dK/dV row m is key w0-left+m
+        }
+    } else if (warp < 8) {
+        // ------------------------------------------------------------ epilogue warps (TMEM lanes 32(warp-4)..)
+        const int ew = warp - 4;
+        const int r = ew * 32 + lane;  // accumulator row m
+        const uint32_t lane_base = tmem + ((uint32_t)(ew * 32) << 16);
+        constexpr int CH = C / 8;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+            const int n = tile / tiles_per_seq;
+            const int ti = tile - n * tiles_per_seq;
+            uint8_t* st = smem + (it & 1) * L.stage_bytes;
             if (!ptx::mbar_wait(&misc->o_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 15); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
-            if (tid == 0) NA1D_STAMP(6);
-            {
-                // rows of this warp: accumulator row m = 32w + i; dQ row m is query w0+m, dK/dV row m is key w0-left+m
-                const int m0 = warp * 32;
-                uint8_t* stage = smem + (it & 1) * L.stage_bytes + L.stage_q + m0 * kRowBytes;  // the tile's own Q buffer, now idle
-                auto own_q = [&](int i) { const int m = m0 + i, t = w0 + m; return m >= right && m < kTileM - left && t >= 0 && t < T; };
-                auto own_k = [&](int i) { const int m = m0 + i, t = w0 - left + m; return m >= win - 1 && t >= 0 && t < T; };
-                // row pointers may lie before the tensor for rows that are not stored; only offsets of stored rows are dereferenced
-                E* q_row0 = dq + ((ptrdiff_t)n * T + (w0 + m0)) * C;
-                E* k_row0 = dk + ((ptrdiff_t)n * T + (w0 - left + m0)) * C;
-                E* v_row0 = dv + ((ptrdiff_t)n * T + (w0 - left + m0)) * C;
+            if (tid == 128) NA1D_STAMP(6);
+            // owned rows: dQ rows [right, right+stride), dK/dV rows [win-1, 128); both land on global rows
+            // [ti*stride, (ti+1)*stride) and are staged from row 0 of the (now idle) Q / dO / K buffers
+            auto stage_rows = [&](uint8_t* buf, const float* acc, int m_first) {
+                const int ms = r - m_first;  // staging row
+                if (ms >= 0 && ms < stride) {
+                    const int swz = (C == 64) ? (ms & 7) : (C == 32) ? ((ms >> 1) & 3) : ((ms >> 2) & 1);
+#pragma unroll
+                    for (int c = 0; c < CH; ++c)
+                        *reinterpret_cast<uint4*>(buf + ms * kRowBytes + ((c ^ swz) * 16)) = Cvt<E>::pack(acc + c * 8);
+                }
+            };
+            if (L.own_out) {
+                // drain all three accumulators to 16-bit registers first so the MMA warp can reuse them, then
+                // one staging buffer, three rounds: stage -> TMA store -> wait until the store has read it
+                uint8_t* buf = smem + L.out;
+                uint4 pk[3][CH];
+#pragma unroll
+                for (int which = 0; which < 3; ++which) {
+                    const uint32_t col = which == 0 ? kColDQ : which == 1 ? kColDK : kColDV;
+                    float acc[C];
+#pragma unroll
+                    for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + col + c, &acc[c]);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) pk[which][c] = Cvt<E>::pack(acc + c * 8);
+                }
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(&misc->o_free);
+#pragma unroll
+                for (int which = 0; which < 3; ++which) {
+                    if (which > 0) asm volatile("bar.sync 2, 128;" ::: "memory");  // previous store has read the buffer
+                    const int ms = r - (which == 0 ? right : win - 1);
+                    if (ms >= 0 && ms < stride) {
+                        const int swz = (C == 64) ? (ms & 7) : (C == 32) ? ((ms >> 1) & 3) : ((ms >> 2) & 1);
+#pragma unroll
+                        for (int c = 0; c < CH; ++c) *reinterpret_cast<uint4*>(buf + ms * kRowBytes + ((c ^ swz) * 16)) = pk[which][c];
+                    }
+                    ptx::fence_proxy_async_smem();
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                    if (tid == 128) {
+                        ptx::tma_store_3d(which == 0 ? &tm_dq : which == 1 ? &tm_dk : &tm_dv, buf, 0, ti * stride, n);
+                        ptx::tma_store_commit();
+                        ptx::tma_store_wait_read();
+                    }
+                }
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (tid == 128) NA1D_STAMP(7);
+            } else {
+                // no room for a staging buffer: use the tile's idle Q / dO / K buffers and release the stage afterwards
                 float acc[C];
 #pragma unroll
                 for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + kColDQ + c, &acc[c]);
                 ptx::tmem_ld_wait();
-                tc::store_rows_coalesced<E, C>(stage, acc, q_row0, lane, own_q);
+                stage_rows(st + L.stage_q, acc, right);
 #pragma unroll
                 for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + kColDK + c, &acc[c]);
                 ptx::tmem_ld_wait();
-                tc::store_rows_coalesced<E, C>(stage, acc, k_row0, lane, own_k);
+                stage_rows(st + L.stage_do, acc, win - 1);
 #pragma unroll
                 for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + kColDV + c, &acc[c]);
                 ptx::tmem_ld_wait();
                 ptx::tc_fence_before_sync();
                 ptx::mbar_arrive(&misc->o_free);
-                tc::store_rows_coalesced<E, C>(stage, acc, v_row0, lane, own_k);
-                // the staging reads are done: the producer may refill this stage
-                __syncwarp();
-                ptx::mbar_arrive(&misc->empty[it & 1]);
+                stage_rows(st + L.stage_k, acc, win - 1);
+                ptx::fence_proxy_async_smem();
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (tid == 128) {
+                    ptx::tma_store_3d(&tm_dq, st + L.stage_q, 0, ti * stride, n);
+                    ptx::tma_store_3d(&tm_dk, st + L.stage_do, 0, ti * stride, n);
+                    ptx::tma_store_3d(&tm_dv, st + L.stage_k, 0, ti * stride, n);
+                    ptx::tma_store_commit();
+                    ptx::tma_store_wait_read();
+                    ptx::mbar_arrive(&misc->empty[it & 1]);  // the producer may refill this stage
+                    NA1D_STAMP(7);
+                }
             }
-            if (tid == 0) NA1D_STAMP(7);
         }
+        if (tid == 128) ptx::tma_store_wait_all();
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
@@ -393,8 +478,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 }
 
 template <typename E, int C, int WB>
-cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUtensorMap& mk, const CUtensorMap& mv, void* dq,
-                       void* dk, void* dv, float* d_rpb, const float* lse, const float* rpb, const int* valid_len,
+cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUtensorMap& mk, const CUtensorMap& mv,
+                       const CUtensorMap& mdq, const CUtensorMap& mdk, const CUtensorMap& mdv, float* d_rpb, const float* lse, const float* rpb, const int* valid_len,
                        const Geometry& gm, int tiles_per_seq, int stride, int KT, int sm_count, cudaStream_t st) {
     const int smem = bwd_layout(C, KT).total;
     auto kern = tc_bwd_kernel<E, C, WB>;
@@ -402,7 +487,7 @@ cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUte
     if (e != cudaSuccess) return e;
     const int total = gm.N * tiles_per_seq;
     const int grid = total < sm_count ? total : sm_count;
-    kern<<<grid, kThreads, smem, st>>>(mq, mdo, mk, mv, (E*)dq, (E*)dk, (E*)dv, d_rpb, lse, rpb, valid_len, gm, tiles_per_seq,
+    kern<<<grid, kThreads, smem, st>>>(mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm, tiles_per_seq,
                                        stride, KT, total);
     return cudaGetLastError();
 }
@@ -434,13 +519,16 @@ cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void*
     const int KT = round_up(kTileM + gm.win - 1, 16);
     const int stride = kTileM - (gm.win - 1);
     const int tiles_per_seq = (gm.T + stride - 1) / stride;
-    CUtensorMap mq, mdo, mk, mv;
+    CUtensorMap mq, mdo, mk, mv, mdq, mdk, mdv;
+    if (!make_row_tile_map(&mdq, dq, dtype, gm.N, gm.T, gm.C, stride) || !make_row_tile_map(&mdk, dk, dtype, gm.N, gm.T, gm.C, stride) ||
+        !make_row_tile_map(&mdv, dv, dtype, gm.N, gm.T, gm.C, stride))
+        return cudaErrorInvalidValue;
     if (!make_row_tile_map(&mq, q, dtype, gm.N, gm.T, gm.C, kTileM) || !make_row_tile_map(&mdo, d_o, dtype, gm.N, gm.T, gm.C, kTileM) ||
         !make_row_tile_map(&mk, k, dtype, gm.N, gm.T, gm.C, KT) || !make_row_tile_map(&mv, v, dtype, gm.N, gm.T, gm.C, KT))
         return cudaErrorInvalidValue;
     const int sms = device_sm_count();
 #define NA1D_TC_BWD(E, C, WB) \
-    return launch_bwd<E, C, WB>(mq, mdo, mk, mv, dq, dk, dv, d_rpb, lse, rpb, valid_len, gm, tiles_per_seq, stride, KT, sms, st)
+    return launch_bwd<E, C, WB>(mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm, tiles_per_seq, stride, KT, sms, st)
 #define NA1D_TC_BWD_W(E, C)                          \
     if (gm.win <= 9) { NA1D_TC_BWD(E, C, 9); }       \
     else if (gm.win <= 17) { NA1D_TC_BWD(E, C, 17); } \
