@@ -112,6 +112,36 @@ int na1d_fused_backward(void* dq, void* dk, void* dv, float* d_rpb, const void* 
                         int64_t C, int64_t win, int64_t left, int64_t dil, float scale, int dtype,
                         void* stream);
 
+/* Backward pass for callers that must not allocate device memory and have no spare buffer to lend.
+ * (No counterpart in the reference project: its Python layer allocates every tensor with torch.)
+ *
+ * Who needs it: a host that drives this library from a place where device allocation is forbidden or
+ * simply unavailable -- a serving or training loop whose memory pool is frozen after start-up, a thread
+ * that is between cudaStreamBeginCapture and cudaStreamEndCapture, or a plain C/C++ runtime that hands
+ * a plug-in fixed input/output buffers and no allocator handle. na1d_fused_backward asks such a caller
+ * for an N*T-float workspace (delta_ws) it cannot produce. This variant takes the same inputs and
+ * outputs but keeps that workspace inside the library, in a fixed device array.
+ *
+ * Same results as na1d_fused_backward with the CUDA-core kernels (it always runs those: they are the
+ * backward kernels that use the workspace). Limits and rules:
+ *   - N*T <= NA1D_STATIC_SCRATCH_ROWS, otherwise NA1D_ERR_TOO_LARGE is returned and nothing is launched.
+ *     The array (NA1D_STATIC_SCRATCH_ROWS floats = 4 MiB) exists once per GPU that loads the library and
+ *     stays resident until the process exits.
+ *   - It calls no cudaMalloc/cudaFree and no allocating library routine, on any call.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current). Make that first call outside any stream capture.
+ *   - All calls on one device share the array. Every call overwrites the part it uses before reading
+ *     it, so nothing has to be cleared between calls -- but two calls whose kernels can overlap on the
+ *     GPU (different streams, no dependency) would race on it; order them on one stream or with events.
+ *   - d_rpb, when given, is accumulated into exactly as in na1d_fused_backward (the caller zeroes it).
+ */
+#define NA1D_STATIC_SCRATCH_ROWS (1 << 20)
+int na1d_fused_backward_static(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q,
+                               const void* k, const void* v, const void* o, const float* lse,
+                               const float* rpb, const int32_t* valid_len, int64_t N, int64_t heads,
+                               int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil, float scale,
+                               int dtype, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Window index arithmetic as the kernels compute it, for bit-exact checking:
  * j_out[t,kk] = t + (kk-left)*dil (int32, (T,win)); in_range[t,kk] = 1 if 0 <= j < T else 0.

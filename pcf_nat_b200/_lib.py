@@ -59,6 +59,8 @@ _lib.na1d_fused_forward.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                                     _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _i32, _ptr]
 _lib.na1d_fused_backward.restype = _i32
 _lib.na1d_fused_backward.argtypes = [_ptr] * 13 + [_i64] * 7 + [_f32, _i32, _ptr]
+_lib.na1d_fused_backward_static.restype = _i32
+_lib.na1d_fused_backward_static.argtypes = [_ptr] * 12 + [_i64] * 7 + [_f32, _i32, _ptr]
 _lib.na1d_window_index.restype = _i32
 _lib.na1d_window_index.argtypes = [_ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]
 _lib.na1d_fused_kernel_family.restype = _i32

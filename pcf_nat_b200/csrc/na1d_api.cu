@@ -4,6 +4,7 @@
 
 #include <atomic>
 #include <climits>
+#include <mutex>
 
 namespace {
 
@@ -52,7 +53,7 @@ const char* na1d_status_string(int status) {
         case NA1D_ERR_MISALIGNED: return "a 16-bit tensor pointer is not 16-byte aligned";
         case NA1D_ERR_CUDA: return "a CUDA call failed (see na1d_last_cuda_error)";
         case NA1D_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
-        case NA1D_ERR_TOO_LARGE: return "problem exceeds a fixed capacity of this entry point";
+        case NA1D_ERR_TOO_LARGE: return "problem exceeds a fixed capacity of this entry point (e.g. N*T above NA1D_STATIC_SCRATCH_ROWS)";
         case NA1D_ERR_UNSUPPORTED: return "the forced kernel family does not support this shape";
         default: return "unknown status";
     }
@@ -163,6 +164,57 @@ int na1d_window_index(int32_t* j_out, uint8_t* in_range, int64_t T, int64_t win,
     na1d::Geometry g;
     if (int s = check_geometry(1, 1, T, 8, win, left, dil, NA1D_BF16, 1.f, g)) return s;
     return cuda_status(na1d::window_index(j_out, in_range, g.T, g.win, g.left, g.dil, (cudaStream_t)stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward pass without a caller-provided workspace (see the header for who needs this and why).
+// The delta workspace of the CUDA-core backward lives in this file-scope device array. In host code
+// the name below is only a handle for the runtime; the address a kernel can use is obtained once per
+// device with cudaGetSymbolAddress and cached.
+static __device__ __align__(256) float g_static_delta[NA1D_STATIC_SCRATCH_ROWS];
+
+namespace {
+std::mutex g_static_mutex;
+float* g_static_delta_addr[64] = {nullptr};
+
+// Device address of g_static_delta on the current device; looked up on the first call per device.
+int static_delta_address(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_status(e);
+    if (dev < 0 || dev >= 64) return NA1D_ERR_TOO_LARGE;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_delta_addr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_delta);  // needs `dev` current, which it is
+        if (e != cudaSuccess) return cuda_status(e);
+        if (p == nullptr) return NA1D_ERR_CUDA;
+        g_static_delta_addr[dev] = static_cast<float*>(p);
+    }
+    *out = g_static_delta_addr[dev];
+    return NA1D_OK;
+}
+}  // namespace
+
+int na1d_fused_backward_static(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
+                               const void* v, const void* o, const float* lse, const float* rpb, const int32_t* valid_len,
+                               int64_t N, int64_t heads, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil,
+                               float scale, int dtype, void* stream) {
+    NA1D_REQUIRE_PTR(dq); NA1D_REQUIRE_PTR(dk); NA1D_REQUIRE_PTR(dv); NA1D_REQUIRE_PTR(d_o); NA1D_REQUIRE_PTR(q);
+    NA1D_REQUIRE_PTR(k); NA1D_REQUIRE_PTR(v); NA1D_REQUIRE_PTR(o); NA1D_REQUIRE_PTR(lse);
+    NA1D_REQUIRE_ALIGNED(dq); NA1D_REQUIRE_ALIGNED(dk); NA1D_REQUIRE_ALIGNED(dv); NA1D_REQUIRE_ALIGNED(d_o);
+    NA1D_REQUIRE_ALIGNED(q); NA1D_REQUIRE_ALIGNED(k); NA1D_REQUIRE_ALIGNED(v); NA1D_REQUIRE_ALIGNED(o);
+    na1d::Geometry g;
+    if (int s = check_geometry(N, heads, T, C, win, left, dil, dtype, scale, g)) return s;
+    if (N * T > (int64_t)NA1D_STATIC_SCRATCH_ROWS) return NA1D_ERR_TOO_LARGE;  // the fixed workspace holds N*T floats
+    if (d_rpb && heads * win * 4 > 48 * 1024) return NA1D_ERR_TOO_LARGE;
+    float* delta = nullptr;
+    if (int s = static_delta_address(&delta)) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    // The pre-pass writes delta[0 .. N*T) completely before the main kernel reads it, on the same stream:
+    // leftovers of earlier calls are never observed.
+    if (int s = cuda_status(na1d::simt_delta(delta, d_o, o, g.N * g.T, g.C, dtype, st))) return s;
+    return cuda_status(na1d::simt_fused_bwd(dq, dk, dv, d_rpb, d_o, q, k, v, lse, delta, rpb, valid_len, g, dtype, st));
 }
 
 }  // extern "C"
