@@ -44,6 +44,14 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor in the
+// stream is still running. grid_dependency_wait() blocks until the predecessor has completed and its memory
+// is visible: nothing produced by an earlier kernel may be read, and nothing global written, before it.
+// grid_launch_dependents() lets the successor's CTAs be scheduled as soon as SM resources free up.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ------------------------------------------------------------------ TMA (tiled, 3-D tensors (C, T, N))
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
     asm volatile(

@@ -140,6 +140,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     ptx::tc_fence_after_sync();
     const uint32_t tmem = misc->tmem_base;
     volatile int* abort_flag = &misc->abort;
+    // Everything above touched only this CTA's shared and tensor memory. From here on global memory written by
+    // earlier kernels is read and outputs are written: wait for the predecessor, and let the successor start its
+    // own set-up as this grid drains.
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
 
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------ TMA producer
@@ -487,9 +492,18 @@ cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUte
     if (e != cudaSuccess) return e;
     const int total = gm.N * tiles_per_seq;
     const int grid = total < sm_count ? total : sm_count;
-    kern<<<grid, kThreads, smem, st>>>(mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm, tiles_per_seq,
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm, tiles_per_seq,
                                        stride, KT, total);
-    return cudaGetLastError();
 }
 
 }  // namespace

@@ -105,6 +105,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     ptx::tc_fence_after_sync();
     const uint32_t tmem = misc->tmem_base;
     volatile int* abort_flag = &misc->abort;
+    // Everything above touched only this CTA's shared and tensor memory. From here on global memory written by
+    // earlier kernels is read and outputs are written: wait for the predecessor, and let the successor start its
+    // own set-up as this grid drains.
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
 
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer
@@ -319,8 +324,17 @@ cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     const int per_sm = (2 * (smem + 1024) <= 227 * 1024) ? 2 : 1;
     const int slots = sm_count * per_sm;
     const int grid = total < slots ? total : slots;
-    kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, mo, lse, rpb, valid_len, gm, tiles_per_seq, KT, total);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mo, lse, rpb, valid_len, gm, tiles_per_seq, KT, total);
 }
 
 }  // namespace
