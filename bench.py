@@ -33,6 +33,9 @@ WORKLOADS = {
     "real_B512_H16_L150_D16_w27": dict(B=512, H=16, T=150, C=16, win=27, dil=1, bwd=True),
 }
 DEFAULT = "cfg2_train_B128_H4_L200_D64_w7"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from one ncu --set full capture of this
+# same command (profiles/tcgen05_fused_cfg2_train.md). Writes still resident in L2 when the kernel ends are not in it.
+NCU_TRAFFIC = {"cfg2_train_B128_H4_L200_D64_w7": 52.93e6 + 5.94e6}
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -305,8 +308,8 @@ def run_ours(args, w, name):
                        "l2": "rotating %d buffer sets of %.0f MB (> L2 between reuses)" % (n_sets, per_set / 1e6),
                        "launch": "one CUDA graph of all timed steps", "kernel_family": ["cuda-core", "tcgen05"][fam]},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                         "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "fused backward (delta pre-pass + main)" if w["bwd"] else "fused forward",
+                         "traffic": NCU_TRAFFIC.get(name), "peak_kind": peak_kind,
+                         "kernel": ("fused backward" if w["bwd"] else "fused forward") + (" (tcgen05)" if fam == 1 else " (cuda-core)"),
                          "algorithmic_bytes_per_launch": dom_bytes},
             "roofline_step": {"fwd_us": 1e3 * ms_fwd / args.steps, "bwd_us": 1e3 * ms_bwd / args.steps,
                               "fwd_frac": fwd_b / (ms_fwd / args.steps * 1e-3) / 1e9 / peak,
