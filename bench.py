@@ -188,6 +188,7 @@ def run_ours(args, w, name):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    from pcf_nat_b200 import parallel
 
     N, H, T, C, win, dil = w["B"] * w["H"], w["H"], w["T"], w["C"], w["win"], w["dil"]
     left = win - 1 - win // 2
@@ -238,11 +239,7 @@ def run_ours(args, w, name):
             if world > 1:
                 dist.barrier()
             ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+        return parallel.max_over_ranks(ms, dev)
 
     with torch.cuda.stream(stream):
         run_steps(args.warmup)
@@ -285,10 +282,7 @@ def run_ours(args, w, name):
     e1.record()
     torch.cuda.synchronize()
     ms_e2e = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_e2e = float(t.item())
+    ms_e2e = parallel.max_over_ranks(ms_e2e, dev)
     clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
@@ -321,9 +315,70 @@ def run_ours(args, w, name):
             "clocks": clocks,
         }
         line["cpu_baseline"] = cpu_baseline(w) if world == 1 and not args.no_cpu_baseline else None
+        line["reference_cuda"] = reference_cuda_baseline(w, dev, host) if world == 1 else None
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def reference_cuda_baseline(w, dev, host, iters=30):
+    """The reference's own sm_80-style CUDA kernels (oracle/_ref, compiled unmodified for sm_100a) on this GPU:
+    the six launches of one forward+backward, alone and inside the unfused chain the model executes
+    (QK -> +mask -> softmax -> AV, and its backward; models/PCF_NATransformer.py:141-150). Reported beside
+    the product's number, never part of it. Only shapes the reference launches as one tile per sequence."""
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    so = os.path.join(ref_dir, "libref_ana1d_bf16.so")
+    N, T, C, win = w["B"] * w["H"], w["T"], w["C"], w["win"]
+    if not os.path.exists(so) or w["dil"] != 1 or T > 256 or not w["bwd"]:
+        return None
+    lib = ctypes.CDLL(so)
+    for nm in ("ref_ana_qk_forward", "ref_ana_band_x", "ref_ana_bandT_x"):
+        getattr(lib, nm).argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 5
+        getattr(lib, nm).restype = ctypes.c_int
+    left = win - 1 - win // 2
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    q, k, v, d_o = (x.to(dev) for x in host)
+    attn = torch.empty(N, T, win, dtype=torch.float32, device=dev)
+    attn_gd = torch.empty_like(attn)
+    out, q_gd, k_gd, v_gd = (torch.empty_like(q) for _ in range(4))
+    j = torch.arange(T, device=dev).unsqueeze(1) + torch.arange(win, device=dev).unsqueeze(0) - left
+    mask = torch.where((j < 0) | (j >= T), -100.0, 0.0).unsqueeze(0)
+    torch.cuda.synchronize()
+
+    def kernels_only():
+        lib.ref_ana_qk_forward(P(attn), P(q), P(k), N, T, C, win, left)
+        lib.ref_ana_band_x(P(out), P(attn), P(v), N, T, C, win, left)
+        lib.ref_ana_qk_forward(P(attn_gd), P(d_o), P(v), N, T, C, win, left)
+        lib.ref_ana_bandT_x(P(v_gd), P(attn), P(d_o), N, T, C, win, left)
+        lib.ref_ana_band_x(P(q_gd), P(attn_gd), P(k), N, T, C, win, left)
+        lib.ref_ana_bandT_x(P(k_gd), P(attn_gd), P(q), N, T, C, win, left)
+
+    def chain():
+        lib.ref_ana_qk_forward(P(attn), P(q), P(k), N, T, C, win, left)
+        p = torch.softmax(attn + mask, -1)
+        lib.ref_ana_band_x(P(out), P(p), P(v), N, T, C, win, left)
+        lib.ref_ana_qk_forward(P(attn_gd), P(d_o), P(v), N, T, C, win, left)
+        lib.ref_ana_bandT_x(P(v_gd), P(p), P(d_o), N, T, C, win, left)
+        ds = (p * (attn_gd - (p * attn_gd).sum(-1, keepdim=True))).contiguous()
+        lib.ref_ana_band_x(P(q_gd), P(ds), P(k), N, T, C, win, left)
+        lib.ref_ana_bandT_x(P(k_gd), P(ds), P(q), N, T, C, win, left)
+
+    res = {}
+    with torch.cuda.stream(torch.cuda.default_stream(dev)):   # the reference launches on the legacy default stream
+        for name, fn in (("kernels_only", kernels_only), ("unfused_chain", chain)):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            us = 1e3 * e0.elapsed_time(e1) / iters
+            res[name] = {"us_per_step": us, "queries_per_s": N * T / (us * 1e-6)}
+    res["note"] = "reference na1d_tensorcore bf16 kernels compiled for sm_100a, same GPU, same shape, single buffer set (L2-warm)"
+    return res
 
 
 def cpu_baseline(w, budget_s=12.0):
