@@ -52,6 +52,7 @@ using tc::RowSwizzle;
 using tc::Fmt;
 constexpr int kThreads = 320;
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kQ = 0, kDO = 1, kK = 2, kV = 3;  // buffers of a stage
 constexpr int kTmemCols = 512;
 constexpr int kColDP = 160, kColDQ = 320, kColDK = 384, kColDV = 448;
 constexpr int kBiasPad = 16;  // bias table index = kk + kBiasPad; fragment neighbour indices start at -15
@@ -78,7 +79,8 @@ __host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT) {
 }
 
 struct alignas(8) BwdMisc {
-    uint64_t full[2], empty[2];
+    // ring barriers per stage and per buffer (kQ, kDO, kK, kV): each buffer is refilled as soon as its last reader retires
+    uint64_t full[2][4], empty[2][4];
     uint64_t s_ready, s_free, p_ready, o_ready, o_free;
     uint32_t tmem_base;
     int abort;
@@ -105,10 +107,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int win = gm.win, left = gm.left, right = gm.win - 1 - gm.left, T = gm.T;
     const int lboq = KT * 16;  // bytes between 8-query groups of the dS matrix
-    const int stage_tx = (2 * kTileM + 2 * KT) * kRowBytes;
 
     if (tid == 0) {
-        for (int s = 0; s < 2; ++s) { ptx::mbar_init(&misc->full[s], 1); ptx::mbar_init(&misc->empty[s], 1); }
+        for (int s = 0; s < 2; ++s)
+            for (int b = 0; b < 4; ++b) { ptx::mbar_init(&misc->full[s][b], 1); ptx::mbar_init(&misc->empty[s][b], 1); }
         ptx::mbar_init(&misc->s_ready, 1);
         ptx::mbar_init(&misc->s_free, 128);
         ptx::mbar_init(&misc->p_ready, 128);
@@ -152,15 +154,23 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             int it = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1, k = it >> 1;
-                if (!ptx::mbar_wait(&misc->empty[s], (k & 1) ^ 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 11); *abort_flag = 1; break; }
                 const int n = tile / tiles_per_seq;
                 const int w0 = (tile - n * tiles_per_seq) * stride - right;
                 uint8_t* st = smem + s * L.stage_bytes;
-                ptx::mbar_expect_tx(&misc->full[s], (uint32_t)stage_tx);
-                ptx::tma_load_3d(st + L.stage_q, &tm_q, &misc->full[s], 0, w0, n);
-                ptx::tma_load_3d(st + L.stage_do, &tm_do, &misc->full[s], 0, w0, n);
-                ptx::tma_load_3d(st + L.stage_k, &tm_k, &misc->full[s], 0, w0 - left, n);
-                ptx::tma_load_3d(st + L.stage_v, &tm_v, &misc->full[s], 0, w0 - left, n);
+                // buffers in the order in which the previous user of this stage releases them: V after batch 1, then K
+                // (dQ = dS.K is issued first in batch 2), dO (dV), Q (dK)
+                bool ok = true;
+                auto refill = [&](int buf, uint8_t* dst, const CUtensorMap* map, int rows, int row0) {
+                    if (!ok) return;
+                    if (!ptx::mbar_wait(&misc->empty[s][buf], (k & 1) ^ 1) || *abort_flag) { ok = false; return; }
+                    ptx::mbar_expect_tx(&misc->full[s][buf], (uint32_t)(rows * kRowBytes));
+                    ptx::tma_load_3d(dst, map, &misc->full[s][buf], 0, row0, n);
+                };
+                refill(kV, st + L.stage_v, &tm_v, KT, w0 - left);
+                refill(kK, st + L.stage_k, &tm_k, KT, w0 - left);
+                refill(kDO, st + L.stage_do, &tm_do, kTileM, w0);
+                refill(kQ, st + L.stage_q, &tm_q, kTileM, w0);
+                if (!ok) { atomicExch(&g_tc_bwd_status, 11); *abort_flag = 1; break; }
             }
         }
     } else if (warp == kMmaWarp) {
@@ -174,19 +184,25 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             // batch 1 of tile `jt`: S = Q.K^T -> cols [0,KT), dP = dO.V^T -> cols [160,160+KT)
             auto batch1 = [&](int jt) -> bool {
                 const int s = jt & 1, k = jt >> 1;
-                if (!ptx::mbar_wait(&misc->full[s], k & 1)) return false;
-                ptx::tc_fence_after_sync();
                 const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
                 const uint64_t dq0 = ptx::smem_desc(st + L.stage_q, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
                 const uint64_t dk0 = ptx::smem_desc(st + L.stage_k, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
                 const uint64_t dd0 = ptx::smem_desc(st + L.stage_do, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
                 const uint64_t dv0 = ptx::smem_desc(st + L.stage_v, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-#pragma unroll
-                for (int ks = 0; ks < C / 16; ++ks)
-                    ptx::mma_ss(tmem, tc::desc_advance(dq0, ks * 32), tc::desc_advance(dk0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
+                // dP = dO.V^T first: V and dO are the buffers that arrive first
+                if (!ptx::mbar_wait(&misc->full[s][kV], k & 1) || !ptx::mbar_wait(&misc->full[s][kDO], k & 1)) return false;
+                ptx::tc_fence_after_sync();
+                { const int it = jt - 1; NA1D_STAMP(12); }
 #pragma unroll
                 for (int ks = 0; ks < C / 16; ++ks)
                     ptx::mma_ss(tmem + kColDP, tc::desc_advance(dd0, ks * 32), tc::desc_advance(dv0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
+                ptx::mma_commit(&misc->empty[s][kV]);  // nothing else reads V
+                if (!ptx::mbar_wait(&misc->full[s][kK], k & 1) || !ptx::mbar_wait(&misc->full[s][kQ], k & 1)) return false;
+                ptx::tc_fence_after_sync();
+                { const int it = jt - 1; NA1D_STAMP(13); }
+#pragma unroll
+                for (int ks = 0; ks < C / 16; ++ks)
+                    ptx::mma_ss(tmem, tc::desc_advance(dq0, ks * 32), tc::desc_advance(dk0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
                 ptx::mma_commit(&misc->s_ready);
                 return true;
             };
@@ -222,15 +238,17 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll 1
                     for (int ks = 0; ks < nks; ++ks)
                         ptx::mma_ss(tmem + kColDQ, tc::desc_advance(a_dq, ks * 256), tc::desc_advance(b_k, ks * 16 * kRowBytes), idesc_dq, ks > 0 ? 1u : 0u);
+                    if (L.own_out) ptx::mma_commit(&misc->empty[s][kK]);   // K is free once dQ has been accumulated
 #pragma unroll
                     for (int ks = 0; ks < kTileM / 16; ++ks)
                         ptx::mma_ss(tmem + kColDV, tc::desc_advance(a_dv, ks * 2 * lboq), tc::desc_advance(b_do, ks * 16 * kRowBytes), idesc_dkv, ks > 0 ? 1u : 0u);
+                    if (L.own_out) ptx::mma_commit(&misc->empty[s][kDO]);  // dO after dV
 #pragma unroll
                     for (int ks = 0; ks < kTileM / 16; ++ks)
                         ptx::mma_ss(tmem + kColDK, tc::desc_advance(a_dk, ks * 2 * lboq), tc::desc_advance(b_q, ks * 16 * kRowBytes), idesc_dkv, ks > 0 ? 1u : 0u);
+                    if (L.own_out) ptx::mma_commit(&misc->empty[s][kQ]);   // Q after dK
                 }
                 ptx::mma_commit(&misc->o_ready);
-                if (L.own_out) ptx::mma_commit(&misc->empty[s]);  // the stage is free once batch 2 has read it
                 NA1D_STAMP(11);
             }
             if (!ok) { atomicExch(&g_tc_bwd_status, 12); *abort_flag = 1; }
@@ -467,7 +485,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     ptx::tma_store_3d(&tm_dv, st + L.stage_k, 0, ti * stride, n);
                     ptx::tma_store_commit();
                     ptx::tma_store_wait_read();
-                    ptx::mbar_arrive(&misc->empty[it & 1]);  // the producer may refill this stage
+                    // the staging used the tile's Q, dO and K buffers: only now may the producer refill them
+                    ptx::mbar_arrive(&misc->empty[it & 1][kQ]);
+                    ptx::mbar_arrive(&misc->empty[it & 1][kDO]);
+                    ptx::mbar_arrive(&misc->empty[it & 1][kK]);
                     NA1D_STAMP(7);
                 }
             }
@@ -499,7 +520,7 @@ cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUte
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm, tiles_per_seq,

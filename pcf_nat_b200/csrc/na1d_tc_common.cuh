@@ -100,6 +100,17 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+__device__ __forceinline__ float fast_log2(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Descriptor for the next K step: only the 14-bit start-address field (16-byte units) moves.
 __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
 
@@ -142,5 +153,6 @@ __device__ __forceinline__ float quad_max(float x) {
 // Tensor map over a dense (N, T, C) 16-bit tensor viewed as dims (C, T, N), box (C, rows, 1).
 bool make_row_tile_map(CUtensorMap* map, const void* base, int dtype, int N, int T, int C, int box_rows);
 int device_sm_count();
+bool pdl_enabled();
 
 }  // namespace na1d

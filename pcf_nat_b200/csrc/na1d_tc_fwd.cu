@@ -25,10 +25,14 @@ namespace na1d {
 __device__ int g_tc_status = 0;
 
 #ifdef NA1D_TIMELINE
+__device__ unsigned long long g_fwd_cta_times[512 * 4];  // per CTA: start, after set-up, first S ready, end (globaltimer ns)
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define NA1D_CTA_TIME(slot) do { if (threadIdx.x == 0 && blockIdx.x < 512) g_fwd_cta_times[blockIdx.x * 4 + (slot)] = gtime(); } while (0)
 __device__ long long g_fwd_timeline[64 * 16];
 #define NA1D_FSTAMP(slot) do { if (blockIdx.x == 0 && it < 64) g_fwd_timeline[it * 16 + (slot)] = clock64(); } while (0)
 #else
 #define NA1D_FSTAMP(slot) do { } while (0)
+#define NA1D_CTA_TIME(slot) do { } while (0)
 #endif
 
 namespace {
@@ -58,7 +62,7 @@ __host__ __device__ inline FwdSmemLayout fwd_layout(int C, int KT) {
 
 struct alignas(8) FwdMisc {
     uint64_t full[2], empty[2];
-    uint64_t s_ready, p_ready, o_ready, o_free;
+    uint64_t s_ready, p_ready, o_ready, o_free, o_staged;
     uint32_t tmem_base;
     int abort;
     float bias[kBiasPad + 64];
@@ -73,6 +77,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     constexpr int NG = tc::band_groups(WB);
     constexpr int kRowBytes = C * 2;
     constexpr int CH = C / 8;
+    NA1D_CTA_TIME(0);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const FwdSmemLayout L = fwd_layout(C, KT);
@@ -88,6 +93,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ptx::mbar_init(&misc->p_ready, 128);
         ptx::mbar_init(&misc->o_ready, 1);
         ptx::mbar_init(&misc->o_free, 128);
+        ptx::mbar_init(&misc->o_staged, 128);
         misc->abort = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tm_q);
@@ -110,6 +116,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     // own set-up as this grid drains.
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
+    NA1D_CTA_TIME(1);
 
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer
@@ -126,6 +133,20 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 ptx::tma_load_3d(st + L.stage_k, &tm_k, &misc->full[s], 0, t0 - left, n);
                 ptx::tma_load_3d(st + L.stage_v, &tm_v, &misc->full[s], 0, t0 - left, n);
             }
+        } else if (lane == 1) {
+            // ---------------------------------------------------------- output store thread: waits until the softmax warps
+            // have staged a tile's O, issues the TMA store, and frees the stage once the store has read shared memory
+            int it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+                if (!ptx::mbar_wait(&misc->o_staged, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 6); *abort_flag = 1; break; }
+                const int n = tile / tiles_per_seq;
+                const int t0 = (tile - n * tiles_per_seq) * kTileM;
+                ptx::tma_store_3d(&tm_o, smem + (it & 1) * L.stage_bytes + L.stage_q, 0, t0, n);
+                ptx::tma_store_commit();
+                ptx::tma_store_wait_read();
+                ptx::mbar_arrive(&misc->empty[it & 1]);
+            }
+            ptx::tma_store_wait_all();
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------ MMA issuer
@@ -195,6 +216,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 4); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
             if (tid == 0) NA1D_FSTAMP(1);
+            if (it == 0) NA1D_CTA_TIME(2);
 
             float s[2][4 * NG];
 #pragma unroll
@@ -226,6 +248,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                             s[b][idx] = x;
                             mx[b][hh] = fmaxf(mx[b][hh], x);
                         }
+            if (tid == 0) NA1D_FSTAMP(12);
             float sum[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
             for (int b = 0; b < 2; ++b)
@@ -250,26 +273,32 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 for (int hh = 0; hh < 2; ++hh) {
                     sum[b][hh] = tc::quad_sum(sum[b][hh]);
                     const int t = t0 + warp * 32 + 16 * b + 8 * hh + fr;
-                    if (lse && (lane & 3) == 0 && t < T) lse[(size_t)n * T + t] = (mx[b][hh] + log2f(sum[b][hh])) * kLn2;
-                    sum[b][hh] = 1.f / sum[b][hh];
+                    if (lse && (lane & 3) == 0 && t < T) lse[(size_t)n * T + t] = (mx[b][hh] + tc::fast_log2(sum[b][hh])) * kLn2;
+                    sum[b][hh] = tc::fast_rcp(sum[b][hh]);
                 }
-            // P over the S columns: zero the whole row range first, then the band blocks
+            if (tid == 0) NA1D_FSTAMP(13);
+            // P over the S columns. Per 16-lane block the band occupies NGP 8-key groups starting at the block's own
+            // first row; every other 16-key chunk of the row range is zeroed. The two sets are disjoint, so one wait.
             {
-                const uint32_t zeros[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                for (int c = 0; c < KT / 2; c += 8) ptx::tmem_st8(lane_base + c, zeros);
-                ptx::tmem_st_wait();
+                constexpr int NGP = NG + (NG & 1);  // band groups padded to whole 16-key chunks
+                const uint32_t zeros[4] = {0, 0, 0, 0};
 #pragma unroll
                 for (int b = 0; b < 2; ++b) {
-                    uint32_t pk[2 * NG];
+                    const uint32_t blk = lane_base + ((uint32_t)(16 * b) << 16);
+                    const int c0 = 2 * warp + b;  // first band chunk (16 keys = 8 packed columns) of this block
+                    for (int ci = 0; ci < KT / 16; ++ci)
+                        if (ci < c0 || ci >= c0 + NGP / 2) tc::st_pack2(blk + ci * 8, zeros);
+                    uint32_t pk[2 * NGP];
 #pragma unroll
-                    for (int g = 0; g < NG; ++g)
+                    for (int g = 0; g < NGP; ++g)
 #pragma unroll
                         for (int hh = 0; hh < 2; ++hh)
-                            pk[2 * g + hh] = Cvt<E>::pack2(s[b][4 * g + 2 * hh] * sum[b][hh], s[b][4 * g + 2 * hh + 1] * sum[b][hh]);
-                    tc::st_pack<NG>(lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(16 * warp + 8 * b), pk);
+                            pk[2 * g + hh] = g < NG ? Cvt<E>::pack2(s[b][4 * g + 2 * hh] * sum[b][hh], s[b][4 * g + 2 * hh + 1] * sum[b][hh]) : 0u;
+                    tc::st_pack<NGP>(blk + c0 * 8, pk);
                 }
                 ptx::tmem_st_wait();
             }
+            if (tid == 0) NA1D_FSTAMP(15);
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&misc->p_ready);
             if (tid == 0) NA1D_FSTAMP(3);
@@ -284,6 +313,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
                 for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + kOCol + c, &acc[c]);
                 ptx::tmem_ld_wait();
+                if (tid == 0) NA1D_FSTAMP(6);
                 ptx::tc_fence_before_sync();
                 ptx::mbar_arrive(&misc->o_free);
                 // row r, 16-byte chunk c at r*rowbytes + ((c ^ swz(r)) * 16): the TMA swizzle of this row size
@@ -292,20 +322,15 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 for (int c = 0; c < CH; ++c)
                     *reinterpret_cast<uint4*>(sO + r * kRowBytes + ((c ^ swz) * 16)) = Cvt<E>::pack(&acc[c * 8]);
                 ptx::fence_proxy_async_smem();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (tid == 0) {
-                    ptx::tma_store_3d(&tm_o, sO, 0, t0, n);
-                    ptx::tma_store_commit();
-                    ptx::tma_store_wait_read();
-                    ptx::mbar_arrive(&misc->empty[it & 1]);
-                }
+                if (tid == 0) NA1D_FSTAMP(7);
+                ptx::mbar_arrive(&misc->o_staged);  // the store thread takes it from here
             }
             if (tid == 0) NA1D_FSTAMP(5);
         }
-        if (tid == 0) ptx::tma_store_wait_all();
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
+    NA1D_CTA_TIME(3);
     if (warp == 0) {
         __syncwarp();
         ptx::tmem_dealloc(tmem, kTmemCols);
@@ -331,7 +356,7 @@ cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mo, lse, rpb, valid_len, gm, tiles_per_seq, KT, total);
@@ -340,6 +365,9 @@ cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
 }  // namespace
 
 #ifdef NA1D_TIMELINE
+extern "C" int na1d_debug_fwd_cta_times(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_fwd_cta_times, sizeof(unsigned long long) * 512 * 4);
+}
 extern "C" int na1d_debug_fwd_timeline(long long* out) {
     return (int)cudaMemcpyFromSymbol(out, g_fwd_timeline, sizeof(long long) * 64 * 16);
 }

@@ -1,6 +1,7 @@
 // Host-side helpers shared by the tcgen05 kernels: TMA tensor maps and device properties.
 #include "na1d_internal.h"
 #include "na1d_tc_common.cuh"
+#include <cstdlib>
 
 namespace na1d {
 namespace {
@@ -37,6 +38,12 @@ bool make_row_tile_map(CUtensorMap* map, const void* base, int dtype, int N, int
     const CUtensorMapDataType dt = dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     return fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Programmatic dependent launch can be switched off with NA1D_PDL=0 in the environment (read once).
+bool pdl_enabled() {
+    static const bool on = []() { const char* e = getenv("NA1D_PDL"); return !(e && e[0] == '0'); }();
+    return on;
 }
 
 int device_sm_count() {
