@@ -520,7 +520,7 @@ cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUte
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    attr[0].val.programmaticStreamSerializationAllowed = (pdl_mode() == 1 || pdl_mode() == 3) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm, tiles_per_seq,

@@ -154,5 +154,6 @@ __device__ __forceinline__ float quad_max(float x) {
 bool make_row_tile_map(CUtensorMap* map, const void* base, int dtype, int N, int T, int C, int box_rows);
 int device_sm_count();
 bool pdl_enabled();
+int pdl_mode();
 
 }  // namespace na1d

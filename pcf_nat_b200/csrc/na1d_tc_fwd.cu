@@ -356,7 +356,7 @@ cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    attr[0].val.programmaticStreamSerializationAllowed = (pdl_mode() == 1 || pdl_mode() == 2) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mo, lse, rpb, valid_len, gm, tiles_per_seq, KT, total);
