@@ -39,6 +39,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
     return false;
 }
 
+// Bounded wait for threads that are not on the critical path (epilogue, producer): a few quick polls, then polls
+// spaced by nanosleep so that idle warps do not take issue slots and shared-memory bandwidth from the working ones.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 18)) {
+    for (uint32_t i = 0; i < 8; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < limit; ++i) {
+        __nanosleep(64);
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    return false;
+}
+
 // ------------------------------------------------------------------ proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

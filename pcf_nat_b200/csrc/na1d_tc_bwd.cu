@@ -9,11 +9,11 @@
 // band is thus seen with both rows inside one tile: no atomics, no second key-owned recomputation,
 // deterministic results.
 //
-// Per tile (one CTA per SM, 320 threads):
+// Per tile (one CTA per SM, 384 threads):
 //   warp 8  : TMA producer -- Q[W], dO[W], K[KT], V[KT] into a 2-stage ring (plain tile loads,
 //             out-of-range rows arrive as zeros = the reference's zero padding).
-//   warp 9  : MMA issuer  -- batch 1: S = Q.K^T, dP = dO.V^T (TMEM, N=KT);
-//                            batch 2: dQ = dS.K, dV = P^T.dO, dK = dS^T.Q.
+//   warps 9-11: MMA issuers -- batch 1: S = Q.K^T, dP = dO.V^T (TMEM, N=KT);
+//                            batch 2: dQ = dS.K, dV = P^T.dO, dK = dS^T.Q. One warp per accumulator chain.
 //             Batch 1 of the NEXT tile is issued before batch 2 of the current one, so the compute warps
 //             work on tile i+1 while the tensor pipe finishes tile i.
 //   warps0-3: compute. Warp w owns query rows 32w..32w+31 (its TMEM lanes) as two 16-row blocks, read as
@@ -50,8 +50,8 @@ using tc::kTileM;
 using tc::round_up;
 using tc::RowSwizzle;
 using tc::Fmt;
-constexpr int kThreads = 320;
-constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kThreads = 384;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;  // warps 9, 10, 11 issue MMAs
 constexpr int kQ = 0, kDO = 1, kK = 2, kV = 3;  // buffers of a stage
 constexpr int kTmemCols = 512;
 constexpr int kColDP = 160, kColDQ = 320, kColDK = 384, kColDV = 448;
@@ -111,10 +111,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     if (tid == 0) {
         for (int s = 0; s < 2; ++s)
             for (int b = 0; b < 4; ++b) { ptx::mbar_init(&misc->full[s][b], 1); ptx::mbar_init(&misc->empty[s][b], 1); }
-        ptx::mbar_init(&misc->s_ready, 1);
+        ptx::mbar_init(&misc->s_ready, 2);   // S chain and dP chain
         ptx::mbar_init(&misc->s_free, 128);
         ptx::mbar_init(&misc->p_ready, 128);
-        ptx::mbar_init(&misc->o_ready, 1);
+        ptx::mbar_init(&misc->o_ready, 3);   // dQ, dV, dK chains
         ptx::mbar_init(&misc->o_free, 128);
         misc->abort = 0;
         ptx::fence_mbar_init();
@@ -162,7 +162,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 bool ok = true;
                 auto refill = [&](int buf, uint8_t* dst, const CUtensorMap* map, int rows, int row0) {
                     if (!ok) return;
-                    if (!ptx::mbar_wait(&misc->empty[s][buf], (k & 1) ^ 1) || *abort_flag) { ok = false; return; }
+                    if (!ptx::mbar_wait_relaxed(&misc->empty[s][buf], (k & 1) ^ 1) || *abort_flag) { ok = false; return; }
                     ptx::mbar_expect_tx(&misc->full[s][buf], (uint32_t)(rows * kRowBytes));
                     ptx::tma_load_3d(dst, map, &misc->full[s][buf], 0, row0, n);
                 };
@@ -173,37 +173,42 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 if (!ok) { atomicExch(&g_tc_bwd_status, 11); *abort_flag = 1; break; }
             }
         }
-    } else if (warp == kMmaWarp) {
-        // ------------------------------------------------------------ MMA issuer
+    } else if (warp >= kMmaWarp) {
+        // ------------------------------------------------------------ MMA issuers
+        // One tcgen05.mma costs its issuing thread about 120 cycles whatever its size (measured), far more than the
+        // tensor pipe needs for these small shapes, but issuers in different warps overlap. Three warps therefore issue
+        // the MMAs of the three independent accumulator chains:  role 0: S and dQ,  role 1: dP and dV,  role 2: dK.
+        const int role = warp - kMmaWarp;
         if (lane == 0) {
             const uint32_t idesc_s = ptx::instr_desc(Fmt<E>::v, 0, 0, kTileM, (uint32_t)KT);
             const uint32_t idesc_dq = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);   // A K-major, B MN-major
             const uint32_t idesc_dkv = ptx::instr_desc(Fmt<E>::v, 1, 1, kTileM, (uint32_t)C);  // A MN-major, B MN-major
             const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
             const int nks = KT / 16;
-            // batch 1 of tile `jt`: S = Q.K^T -> cols [0,KT), dP = dO.V^T -> cols [160,160+KT)
+            // this role's part of batch 1 of tile `jt`: S = Q.K^T -> cols [0,KT) (role 0), dP = dO.V^T -> cols [160,160+KT) (role 1)
             auto batch1 = [&](int jt) -> bool {
                 const int s = jt & 1, k = jt >> 1;
                 const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
-                const uint64_t dq0 = ptx::smem_desc(st + L.stage_q, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                const uint64_t dk0 = ptx::smem_desc(st + L.stage_k, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                const uint64_t dd0 = ptx::smem_desc(st + L.stage_do, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                const uint64_t dv0 = ptx::smem_desc(st + L.stage_v, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                // dP = dO.V^T first: V and dO are the buffers that arrive first
-                if (!ptx::mbar_wait(&misc->full[s][kV], k & 1) || !ptx::mbar_wait(&misc->full[s][kDO], k & 1)) return false;
-                ptx::tc_fence_after_sync();
-                { const int it = jt - 1; NA1D_STAMP(12); }
+                if (role == 0) {
+                    if (!ptx::mbar_wait(&misc->full[s][kK], k & 1) || !ptx::mbar_wait(&misc->full[s][kQ], k & 1)) return false;
+                    ptx::tc_fence_after_sync();
+                    const uint64_t dq0 = ptx::smem_desc(st + L.stage_q, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                    const uint64_t dk0 = ptx::smem_desc(st + L.stage_k, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
 #pragma unroll
-                for (int ks = 0; ks < C / 16; ++ks)
-                    ptx::mma_ss(tmem + kColDP, tc::desc_advance(dd0, ks * 32), tc::desc_advance(dv0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
-                ptx::mma_commit(&misc->empty[s][kV]);  // nothing else reads V
-                if (!ptx::mbar_wait(&misc->full[s][kK], k & 1) || !ptx::mbar_wait(&misc->full[s][kQ], k & 1)) return false;
-                ptx::tc_fence_after_sync();
-                { const int it = jt - 1; NA1D_STAMP(13); }
+                    for (int ks = 0; ks < C / 16; ++ks)
+                        ptx::mma_ss(tmem, tc::desc_advance(dq0, ks * 32), tc::desc_advance(dk0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
+                    ptx::mma_commit(&misc->s_ready);
+                } else if (role == 1) {
+                    if (!ptx::mbar_wait(&misc->full[s][kV], k & 1) || !ptx::mbar_wait(&misc->full[s][kDO], k & 1)) return false;
+                    ptx::tc_fence_after_sync();
+                    const uint64_t dd0 = ptx::smem_desc(st + L.stage_do, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                    const uint64_t dv0 = ptx::smem_desc(st + L.stage_v, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
 #pragma unroll
-                for (int ks = 0; ks < C / 16; ++ks)
-                    ptx::mma_ss(tmem, tc::desc_advance(dq0, ks * 32), tc::desc_advance(dk0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
-                ptx::mma_commit(&misc->s_ready);
+                    for (int ks = 0; ks < C / 16; ++ks)
+                        ptx::mma_ss(tmem + kColDP, tc::desc_advance(dd0, ks * 32), tc::desc_advance(dv0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
+                    ptx::mma_commit(&misc->empty[s][kV]);  // nothing else reads V
+                    ptx::mma_commit(&misc->s_ready);
+                }
                 return true;
             };
             int it = 0;
@@ -211,45 +216,40 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1;
                 const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
-                const uint32_t qa = st + L.stage_q, doa = st + L.stage_do, ka = st + L.stage_k;
                 // S/dP of this tile are in the compute warps' registers: the next tile's batch 1 may overwrite them
-                if (!ptx::mbar_wait(&misc->s_free, it & 1) || *abort_flag) { ok = false; break; }
+                if (role < 2) {
+                    if (!ptx::mbar_wait(&misc->s_free, it & 1) || *abort_flag) { ok = false; break; }
+                    ptx::tc_fence_after_sync();
+                    if (role == 0) NA1D_STAMP(8);
+                    if (tile + gridDim.x < total_tiles && !batch1(it + 1)) { ok = false; break; }
+                    if (role == 0) NA1D_STAMP(9);
+                }
+                // the compute warps have written this tile's operands; the epilogue warps have drained the previous outputs
+                if (!ptx::mbar_wait(&misc->p_ready, it & 1) || !ptx::mbar_wait(&misc->o_free, (it & 1) ^ 1) || *abort_flag) { ok = false; break; }
                 ptx::tc_fence_after_sync();
-                NA1D_STAMP(8);
-                if (tile + gridDim.x < total_tiles && !batch1(it + 1)) { ok = false; break; }
-                NA1D_STAMP(9);
-                // the compute warps have written this tile's operands
-                if (!ptx::mbar_wait(&misc->p_ready, it & 1) || *abort_flag) { ok = false; break; }
-                // the epilogue warps have drained the previous tile's outputs
-                if (!ptx::mbar_wait(&misc->o_free, (it & 1) ^ 1) || *abort_flag) { ok = false; break; }
-                ptx::tc_fence_after_sync();
-                NA1D_STAMP(10);
+                if (role == 0) NA1D_STAMP(10);
                 // batch 2. dS/P matrices: element (q, c) at (q/8)*lboq + (c/8)*128 + (q%8)*16 + (c%8)*2.
-                {
-                    //   dQ = dS.K   : A K-major (M = queries, K = KT keys): K-adjacent core matrices 128 B apart, 8-row groups lboq apart
+                if (role == 0) {
+                    //   dQ = dS.K : A K-major (M = queries, K = KT keys): K-adjacent core matrices 128 B apart, 8-row groups lboq apart
                     const uint64_t a_dq = ptx::smem_desc(ds_a, 128, lboq, ptx::kSwizzleNone);
-                    //   dV = P^T.dO, dK = dS^T.Q : the same matrices read MN-major (M = first 128 keys of the K window,
-                    //   K = queries): 8-key groups 128 B apart, 8-query groups lboq apart
-                    const uint64_t a_dv = ptx::smem_desc(p_a, lboq, 128, ptx::kSwizzleNone);
-                    const uint64_t a_dk = ptx::smem_desc(ds_a, lboq, 128, ptx::kSwizzleNone);
-                    const uint64_t b_k = ptx::smem_desc(ka, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    const uint64_t b_do = ptx::smem_desc(doa, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    const uint64_t b_q = ptx::smem_desc(qa, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
+                    const uint64_t b_k = ptx::smem_desc(st + L.stage_k, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
 #pragma unroll 1
                     for (int ks = 0; ks < nks; ++ks)
                         ptx::mma_ss(tmem + kColDQ, tc::desc_advance(a_dq, ks * 256), tc::desc_advance(b_k, ks * 16 * kRowBytes), idesc_dq, ks > 0 ? 1u : 0u);
-                    if (L.own_out) ptx::mma_commit(&misc->empty[s][kK]);   // K is free once dQ has been accumulated
+                    if (L.own_out) ptx::mma_commit(&misc->empty[s][kK]);   // K was read by S (long done) and dQ
+                } else {
+                    //   dV = P^T.dO (role 1), dK = dS^T.Q (role 2): the same matrices read MN-major (M = first 128 keys of the K
+                    //   window, K = queries): 8-key groups 128 B apart, 8-query groups lboq apart
+                    const uint64_t a_t = ptx::smem_desc(role == 1 ? p_a : ds_a, lboq, 128, ptx::kSwizzleNone);
+                    const uint64_t b_t = ptx::smem_desc(st + (role == 1 ? L.stage_do : L.stage_q), 0, 8 * kRowBytes, RowSwizzle<C>::umma);
+                    const uint32_t dcol = tmem + (role == 1 ? kColDV : kColDK);
 #pragma unroll
                     for (int ks = 0; ks < kTileM / 16; ++ks)
-                        ptx::mma_ss(tmem + kColDV, tc::desc_advance(a_dv, ks * 2 * lboq), tc::desc_advance(b_do, ks * 16 * kRowBytes), idesc_dkv, ks > 0 ? 1u : 0u);
-                    if (L.own_out) ptx::mma_commit(&misc->empty[s][kDO]);  // dO after dV
-#pragma unroll
-                    for (int ks = 0; ks < kTileM / 16; ++ks)
-                        ptx::mma_ss(tmem + kColDK, tc::desc_advance(a_dk, ks * 2 * lboq), tc::desc_advance(b_q, ks * 16 * kRowBytes), idesc_dkv, ks > 0 ? 1u : 0u);
-                    if (L.own_out) ptx::mma_commit(&misc->empty[s][kQ]);   // Q after dK
+                        ptx::mma_ss(dcol, tc::desc_advance(a_t, ks * 2 * lboq), tc::desc_advance(b_t, ks * 16 * kRowBytes), idesc_dkv, ks > 0 ? 1u : 0u);
+                    if (L.own_out) ptx::mma_commit(&misc->empty[s][role == 1 ? kDO : kQ]);  // dO: dP and dV done; Q: S and dK done
                 }
                 ptx::mma_commit(&misc->o_ready);
-                NA1D_STAMP(11);
+                if (role == 0) NA1D_STAMP(11);
             }
             if (!ok) { atomicExch(&g_tc_bwd_status, 12); *abort_flag = 1; }
         }
@@ -410,7 +410,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             const int n = tile / tiles_per_seq;
             const int ti = tile - n * tiles_per_seq;
             uint8_t* st = smem + (it & 1) * L.stage_bytes;
-            if (!ptx::mbar_wait(&misc->o_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 15); *abort_flag = 1; break; }
+            if (!ptx::mbar_wait_relaxed(&misc->o_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 15); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
             if (tid == 128) NA1D_STAMP(6);
             // owned rows: dQ rows [right, right+stride), dK/dV rows [win-1, 128); both land on global rows

@@ -124,7 +124,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             int it = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1, k = it >> 1;
-                if (!ptx::mbar_wait(&misc->empty[s], (k & 1) ^ 1) || *abort_flag) { atomicExch(&g_tc_status, 1); *abort_flag = 1; break; }
+                if (!ptx::mbar_wait_relaxed(&misc->empty[s], (k & 1) ^ 1) || *abort_flag) { atomicExch(&g_tc_status, 1); *abort_flag = 1; break; }
                 const int n = tile / tiles_per_seq;
                 const int t0 = (tile - n * tiles_per_seq) * kTileM;
                 uint8_t* st = smem + s * L.stage_bytes;
@@ -138,7 +138,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             // have staged a tile's O, issues the TMA store, and frees the stage once the store has read shared memory
             int it = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-                if (!ptx::mbar_wait(&misc->o_staged, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 6); *abort_flag = 1; break; }
+                if (!ptx::mbar_wait_relaxed(&misc->o_staged, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 6); *abort_flag = 1; break; }
                 const int n = tile / tiles_per_seq;
                 const int t0 = (tile - n * tiles_per_seq) * kTileM;
                 ptx::tma_store_3d(&tm_o, smem + (it & 1) * L.stage_bytes + L.stage_q, 0, t0, n);
