@@ -81,7 +81,8 @@ __host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT) {
 struct alignas(8) BwdMisc {
     // ring barriers per stage and per buffer (kQ, kDO, kK, kV): each buffer is refilled as soon as its last reader retires
     uint64_t full[2][4], empty[2][4];
-    uint64_t s_ready, s_free, p_ready, o_ready, o_free;
+    uint64_t s_ready, s_free, p_ready, o_ready;
+    uint64_t o_free[3];  // per accumulator (dQ, dV, dK): its MMA chain restarts as soon as the epilogue has drained it
     uint32_t tmem_base;
     int abort;
     float bias[kBiasPad + 64];  // log2e * rpb[h][kk] at index kk + kBiasPad, zero elsewhere
@@ -115,7 +116,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ptx::mbar_init(&misc->s_free, 128);
         ptx::mbar_init(&misc->p_ready, 128);
         ptx::mbar_init(&misc->o_ready, 3);   // dQ, dV, dK chains
-        ptx::mbar_init(&misc->o_free, 128);
+        for (int i = 0; i < 3; ++i) ptx::mbar_init(&misc->o_free[i], 128);
         misc->abort = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tm_q);
@@ -225,7 +226,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     if (role == 0) NA1D_STAMP(9);
                 }
                 // the compute warps have written this tile's operands; the epilogue warps have drained the previous outputs
-                if (!ptx::mbar_wait(&misc->p_ready, it & 1) || !ptx::mbar_wait(&misc->o_free, (it & 1) ^ 1) || *abort_flag) { ok = false; break; }
+                if (!ptx::mbar_wait(&misc->p_ready, it & 1) || !ptx::mbar_wait(&misc->o_free[role], (it & 1) ^ 1) || *abort_flag) { ok = false; break; }
                 ptx::tc_fence_after_sync();
                 if (role == 0) NA1D_STAMP(10);
                 // batch 2. dS/P matrices: element (q, c) at (q/8)*lboq + (c/8)*128 + (q%8)*16 + (c%8)*2.
@@ -430,17 +431,17 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 uint8_t* buf = smem + L.out;
                 uint4 pk[3][CH];
 #pragma unroll
-                for (int which = 0; which < 3; ++which) {
-                    const uint32_t col = which == 0 ? kColDQ : which == 1 ? kColDK : kColDV;
+                for (int which = 0; which < 3; ++which) {  // 0: dQ, 1: dV, 2: dK = the MMA roles
+                    const uint32_t col = which == 0 ? kColDQ : which == 1 ? kColDV : kColDK;
                     float acc[C];
 #pragma unroll
                     for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + col + c, &acc[c]);
                     ptx::tmem_ld_wait();
+                    ptx::tc_fence_before_sync();
+                    ptx::mbar_arrive(&misc->o_free[which]);
 #pragma unroll
                     for (int c = 0; c < CH; ++c) pk[which][c] = Cvt<E>::pack(acc + c * 8);
                 }
-                ptx::tc_fence_before_sync();
-                ptx::mbar_arrive(&misc->o_free);
 #pragma unroll
                 for (int which = 0; which < 3; ++which) {
                     if (which > 0) asm volatile("bar.sync 2, 128;" ::: "memory");  // previous store has read the buffer
@@ -453,7 +454,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     ptx::fence_proxy_async_smem();
                     asm volatile("bar.sync 2, 128;" ::: "memory");
                     if (tid == 128) {
-                        ptx::tma_store_3d(which == 0 ? &tm_dq : which == 1 ? &tm_dk : &tm_dv, buf, 0, ti * stride, n);
+                        ptx::tma_store_3d(which == 0 ? &tm_dq : which == 1 ? &tm_dv : &tm_dk, buf, 0, ti * stride, n);
                         ptx::tma_store_commit();
                         ptx::tma_store_wait_read();
                     }
@@ -475,7 +476,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + kColDV + c, &acc[c]);
                 ptx::tmem_ld_wait();
                 ptx::tc_fence_before_sync();
-                ptx::mbar_arrive(&misc->o_free);
+                for (int i = 0; i < 3; ++i) ptx::mbar_arrive(&misc->o_free[i]);
                 stage_rows(st + L.stage_k, acc, win - 1);
                 ptx::fence_proxy_async_smem();
                 asm volatile("bar.sync 2, 128;" ::: "memory");

@@ -6,9 +6,11 @@
 //             into a 2-stage ring. Plain (non-multicast) tile loads; rows outside [0,T) arrive as
 //             zeros, which is the reference's zero padding of K and V
 //             (na1d_tensorcore/bf16_ana1d_kernel.cu:99-112).
-//   warp 5  : MMA issuer  -- S = Q.K^T (C/16 steps, M=128, N=KT) into TMEM columns [0,KT);
+//   warps 5,6: MMA issuers -- S = Q.K^T (C/16 steps, M=128, N=KT) into TMEM columns [0,KT);
 //             O = P.V (KT/16 steps, N=C) with P read from TMEM and V as an MN-major operand straight
-//             from the TMA tile.
+//             from the TMA tile. A tcgen05.mma costs its issuing thread ~120 cycles whatever its size, so
+//             the key steps of P.V are split between two issuers with an accumulator each (even / odd
+//             steps); the epilogue adds the two.
 //   warps0-3: softmax on the band only. Warp w owns rows 32w..32w+31 as two 16-row accumulator
 //             fragments (see na1d_tc_common.cuh): scale, + rpb, + (-100) mask, row max / sum with two
 //             quad shuffles each, normalise, round to 16 bits -- the reference rounds probabilities to
@@ -41,9 +43,11 @@ using tc::kTileM;
 using tc::round_up;
 using tc::RowSwizzle;
 using tc::Fmt;
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;  // 4 softmax warps, producer/store warp, two MMA issuer warps
 constexpr int kTmemCols = 256;
-constexpr int kOCol = 192;   // O accumulator; S (fp32) and then P (16-bit pairs) use [0, KT), KT <= 160
+constexpr int kOCol = 192;   // O accumulator of the even key steps; S (fp32) and then P (16-bit pairs) use [0, KT), KT <= 160
+constexpr int kOColB = 96;   // O accumulator of the odd key steps: inside the S columns, which are dead once softmax has read
+                             // them (P only needs the packed columns [0, KT/2 <= 80))
 constexpr int kBiasPad = 16;
 
 struct FwdSmemLayout {
@@ -76,7 +80,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               int total_tiles) {
     constexpr int NG = tc::band_groups(WB);
     constexpr int kRowBytes = C * 2;
-    constexpr int CH = C / 8;
     NA1D_CTA_TIME(0);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -91,7 +94,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         for (int s = 0; s < 2; ++s) { ptx::mbar_init(&misc->full[s], 1); ptx::mbar_init(&misc->empty[s], 1); }
         ptx::mbar_init(&misc->s_ready, 1);
         ptx::mbar_init(&misc->p_ready, 128);
-        ptx::mbar_init(&misc->o_ready, 1);
+        ptx::mbar_init(&misc->o_ready, 2);  // one commit per MMA issuer
         ptx::mbar_init(&misc->o_free, 128);
         ptx::mbar_init(&misc->o_staged, 128);
         misc->abort = 0;
@@ -149,7 +152,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             ptx::tma_store_wait_all();
         }
     } else if (warp == 5) {
-        // ------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------ MMA issuer A: S, and the even key steps of P.V
         if (lane == 0) {
             const uint32_t idesc_s = ptx::instr_desc(Fmt<E>::v, 0, 0, kTileM, (uint32_t)KT);
             const uint32_t idesc_o = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);
@@ -158,7 +161,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1, k = it >> 1;
                 const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
-                if (!ptx::mbar_wait(&misc->full[s], k & 1) || *abort_flag) { atomicExch(&g_tc_status, 2); *abort_flag = 1; break; }
+                // S overwrites the columns that held the previous tile's P and odd-step accumulator: both must be drained
+                if (!ptx::mbar_wait(&misc->full[s], k & 1) || !ptx::mbar_wait(&misc->o_free, (it & 1) ^ 1) || *abort_flag) {
+                    atomicExch(&g_tc_status, 2); *abort_flag = 1; break;
+                }
                 ptx::tc_fence_after_sync();
                 NA1D_FSTAMP(8);
                 {
@@ -170,19 +176,37 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 }
                 ptx::mma_commit(&misc->s_ready);
                 NA1D_FSTAMP(9);
-                if (!ptx::mbar_wait(&misc->p_ready, it & 1) || !ptx::mbar_wait(&misc->o_free, (it & 1) ^ 1) || *abort_flag) {
-                    atomicExch(&g_tc_status, 3); *abort_flag = 1; break;
-                }
+                if (!ptx::mbar_wait(&misc->p_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 3); *abort_flag = 1; break; }
                 ptx::tc_fence_after_sync();
                 NA1D_FSTAMP(10);
                 {
                     const uint64_t b0 = ptx::smem_desc(st + L.stage_v, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
 #pragma unroll 1
-                    for (int ks = 0; ks < nks; ++ks)
+                    for (int ks = 0; ks < nks; ks += 2)
                         ptx::mma_ts(tmem + kOCol, tmem + ks * 8, tc::desc_advance(b0, ks * 16 * kRowBytes), idesc_o, ks > 0 ? 1u : 0u);
                 }
                 ptx::mma_commit(&misc->o_ready);
                 NA1D_FSTAMP(11);
+            }
+        }
+    } else if (warp == 6) {
+        // ------------------------------------------------------------ MMA issuer B: the odd key steps of P.V
+        if (lane == 0) {
+            const uint32_t idesc_o = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);
+            const int nks = KT / 16;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+                const int s = it & 1, k = it >> 1;
+                const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
+                if (!ptx::mbar_wait(&misc->full[s], k & 1) || !ptx::mbar_wait(&misc->p_ready, it & 1) || *abort_flag) {
+                    atomicExch(&g_tc_status, 7); *abort_flag = 1; break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint64_t b0 = ptx::smem_desc(st + L.stage_v, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
+#pragma unroll 1
+                for (int ks = 1; ks < nks; ks += 2)
+                    ptx::mma_ts(tmem + kOColB, tmem + ks * 8, tc::desc_advance(b0, ks * 16 * kRowBytes), idesc_o, ks > 1 ? 1u : 0u);
+                ptx::mma_commit(&misc->o_ready);
             }
         }
     } else {
@@ -309,18 +333,29 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             if (tid == 0) NA1D_FSTAMP(4);
             {
                 uint8_t* sO = smem + (it & 1) * L.stage_bytes + L.stage_q;
-                float acc[C];
-#pragma unroll
-                for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + kOCol + c, &acc[c]);
-                ptx::tmem_ld_wait();
-                if (tid == 0) NA1D_FSTAMP(6);
-                ptx::tc_fence_before_sync();
-                ptx::mbar_arrive(&misc->o_free);
                 // row r, 16-byte chunk c at r*rowbytes + ((c ^ swz(r)) * 16): the TMA swizzle of this row size
                 const int swz = (C == 64) ? (r & 7) : (C == 32) ? ((r >> 1) & 3) : ((r >> 2) & 1);
+                constexpr int HALF = C >= 32 ? C / 2 : C;  // columns per round (two rounds keep the register count down)
 #pragma unroll
-                for (int c = 0; c < CH; ++c)
-                    *reinterpret_cast<uint4*>(sO + r * kRowBytes + ((c ^ swz) * 16)) = Cvt<E>::pack(&acc[c * 8]);
+                for (int c0 = 0; c0 < C; c0 += HALF) {
+                    float acc[HALF], accb[HALF];
+#pragma unroll
+                    for (int c = 0; c < HALF; c += 8) {
+                        ptx::tmem_ld8(lane_base + kOCol + c0 + c, &acc[c]);
+                        ptx::tmem_ld8(lane_base + kOColB + c0 + c, &accb[c]);
+                    }
+                    ptx::tmem_ld_wait();
+                    if (c0 + HALF >= C) {
+                        if (tid == 0) NA1D_FSTAMP(6);
+                        ptx::tc_fence_before_sync();
+                        ptx::mbar_arrive(&misc->o_free);
+                    }
+#pragma unroll
+                    for (int c = 0; c < HALF; ++c) acc[c] += accb[c];
+#pragma unroll
+                    for (int c = 0; c < HALF / 8; ++c)
+                        *reinterpret_cast<uint4*>(sO + r * kRowBytes + (((c0 / 8 + c) ^ swz) * 16)) = Cvt<E>::pack(&acc[c * 8]);
+                }
                 ptx::fence_proxy_async_smem();
                 if (tid == 0) NA1D_FSTAMP(7);
                 ptx::mbar_arrive(&misc->o_staged);  // the store thread takes it from here
