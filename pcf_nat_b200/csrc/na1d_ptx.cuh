@@ -34,6 +34,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: returns false when the limit expires (the caller records an error and unwinds).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 20)) {
+    // rolled on purpose: unrolled polls of the many wait sites would bloat the kernels past the instruction cache
+#pragma unroll 1
     for (uint32_t i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
@@ -42,8 +44,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
 // Bounded wait for threads that are not on the critical path (epilogue, producer): a few quick polls, then polls
 // spaced by nanosleep so that idle warps do not take issue slots and shared-memory bandwidth from the working ones.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 18)) {
+#pragma unroll 1
     for (uint32_t i = 0; i < 8; ++i)
         if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
     for (uint32_t i = 0; i < limit; ++i) {
         __nanosleep(64);
         if (mbar_try_wait(bar, parity)) return true;

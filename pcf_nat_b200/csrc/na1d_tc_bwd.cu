@@ -1,6 +1,8 @@
 // Fused NA1D backward on the Blackwell tensor path (sm_100a): persistent, warp-specialised.
 //
-// Tiling. A tile is a window W of 128 consecutive rows of one sequence; consecutive tiles start
+// Tiling. Rows are tiled over the FLATTENED (sequence, token) axis, so tiles are full whatever T is; a neighbour that
+// falls outside the query's own sequence is the reference's zero-padded row and is excluded per element.
+// A tile is a window W of 128 consecutive flattened rows; consecutive tiles start
 // `stride = 128-(win-1)` rows apart, so they overlap by win-1 rows. All 128 rows act as queries
 // (their band needs keys [w0-left, w0+127+right]; K and V are staged as KT = round16(128+win-1) rows
 // starting at w0-left). A key row is "interior" when every query that attends it lies in W, which
@@ -29,6 +31,7 @@
 // Replaces the four backward launches of the reference (na1d_tensorcore/nattn.py:46-54, 69-78) and
 // the eager softmax backward between them.
 #include "na1d_internal.h"
+#include <type_traits>
 #include "na1d_tc_common.cuh"
 
 namespace na1d {
@@ -62,7 +65,8 @@ struct BwdSmemLayout {
     int ds, p, out, misc, total;
     bool own_out;  // a dedicated 128-row staging buffer for the outputs fits next to everything else
 };
-__host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT) {
+constexpr int kBiasRowB = 16 + 48;  // per-head table: log2e * rpb[h][kk] at index kk + 16, kk in [-16, 48)
+__host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT, int bias_heads) {
     BwdSmemLayout L;
     L.stage_q = 0;
     L.stage_do = L.stage_q + round_up(kTileM * C * 2, 1024);
@@ -72,10 +76,18 @@ __host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT) {
     L.ds = 2 * L.stage_bytes;           // dS [128 queries][KT keys]
     L.p = L.ds + kTileM * KT * 2;       // P  [128 queries][KT keys]
     L.out = L.p + kTileM * KT * 2;
-    L.own_out = L.out + round_up(kTileM * C * 2, 1024) + 1024 + 1008 <= 227 * 1024;
+    const int tail = 512 + round_up(bias_heads * kBiasRowB * 4, 256) + 1008;  // misc block, bias table, alignment slack
+    L.own_out = L.out + round_up(kTileM * C * 2, 1024) + tail <= 227 * 1024;
     L.misc = L.out + (L.own_out ? round_up(kTileM * C * 2, 1024) : 0);
-    L.total = L.misc + 1024 + 1008;     // misc block + slack for the manual 1024-byte alignment
+    L.total = L.misc + tail;
     return L;
+}
+
+// Bias gradient of neighbours outside the query's own sequence (rare: only padded query rows next to a sequence end have
+// a non-zero probability there). Not inlined, to keep the many call sites of the unrolled loops small.
+__device__ __noinline__ void bias_grad_outside(float* dst, float g0, float g1) {
+    if (g0 != 0.f) atomicAdd(dst, g0);
+    if (g1 != 0.f) atomicAdd(dst + 1, g1);
 }
 
 struct alignas(8) BwdMisc {
@@ -85,25 +97,26 @@ struct alignas(8) BwdMisc {
     uint64_t o_free[3];  // per accumulator (dQ, dV, dK): its MMA chain restarts as soon as the epilogue has drained it
     uint32_t tmem_base;
     int abort;
-    float bias[kBiasPad + 64];  // log2e * rpb[h][kk] at index kk + kBiasPad, zero elsewhere
 };
 
-template <typename E, int C, int WB>
+template <typename E, int C, int WB, bool OWN_OUT>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk,
               const __grid_constant__ CUtensorMap tm_dv, float* __restrict__ d_rpb, const float* __restrict__ lse,
-              const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, int tiles_per_seq, int stride,
-              int KT, int total_tiles) {
+              const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, int stride, int KT,
+              int total_tiles) {
     constexpr int NG = tc::band_groups(WB);  // 8-column groups holding the band of a 16-row block
     constexpr int kRowBytes = C * 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const BwdSmemLayout L = bwd_layout(C, KT);
+    const BwdSmemLayout L = bwd_layout(C, KT, rpb ? gm.H : 0);
     uint8_t* sDS = smem + L.ds;
     uint8_t* sP = smem + L.p;
     BwdMisc* misc = reinterpret_cast<BwdMisc*>(smem + L.misc);
+    float* bias_tab = reinterpret_cast<float*>(smem + L.misc + 512);
+    const int rows_total = gm.N * gm.T;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int win = gm.win, left = gm.left, right = gm.win - 1 - gm.left, T = gm.T;
@@ -155,8 +168,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             int it = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1, k = it >> 1;
-                const int n = tile / tiles_per_seq;
-                const int w0 = (tile - n * tiles_per_seq) * stride - right;
+                const int g0 = tile * stride - right;  // first flattened row of the window
                 uint8_t* st = smem + s * L.stage_bytes;
                 // buffers in the order in which the previous user of this stage releases them: V after batch 1, then K
                 // (dQ = dS.K is issued first in batch 2), dO (dV), Q (dK)
@@ -165,12 +177,12 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     if (!ok) return;
                     if (!ptx::mbar_wait_relaxed(&misc->empty[s][buf], (k & 1) ^ 1) || *abort_flag) { ok = false; return; }
                     ptx::mbar_expect_tx(&misc->full[s][buf], (uint32_t)(rows * kRowBytes));
-                    ptx::tma_load_3d(dst, map, &misc->full[s][buf], 0, row0, n);
+                    ptx::tma_load_3d(dst, map, &misc->full[s][buf], 0, row0, 0);
                 };
-                refill(kV, st + L.stage_v, &tm_v, KT, w0 - left);
-                refill(kK, st + L.stage_k, &tm_k, KT, w0 - left);
-                refill(kDO, st + L.stage_do, &tm_do, kTileM, w0);
-                refill(kQ, st + L.stage_q, &tm_q, kTileM, w0);
+                refill(kV, st + L.stage_v, &tm_v, KT, g0 - left);
+                refill(kK, st + L.stage_k, &tm_k, KT, g0 - left);
+                refill(kDO, st + L.stage_do, &tm_do, kTileM, g0);
+                refill(kQ, st + L.stage_q, &tm_q, kTileM, g0);
                 if (!ok) { atomicExch(&g_tc_bwd_status, 11); *abort_flag = 1; break; }
             }
         }
@@ -237,17 +249,17 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll 1
                     for (int ks = 0; ks < nks; ++ks)
                         ptx::mma_ss(tmem + kColDQ, tc::desc_advance(a_dq, ks * 256), tc::desc_advance(b_k, ks * 16 * kRowBytes), idesc_dq, ks > 0 ? 1u : 0u);
-                    if (L.own_out) ptx::mma_commit(&misc->empty[s][kK]);   // K was read by S (long done) and dQ
+                    if constexpr (OWN_OUT) ptx::mma_commit(&misc->empty[s][kK]);   // K was read by S (long done) and dQ
                 } else {
                     //   dV = P^T.dO (role 1), dK = dS^T.Q (role 2): the same matrices read MN-major (M = first 128 keys of the K
                     //   window, K = queries): 8-key groups 128 B apart, 8-query groups lboq apart
                     const uint64_t a_t = ptx::smem_desc(role == 1 ? p_a : ds_a, lboq, 128, ptx::kSwizzleNone);
                     const uint64_t b_t = ptx::smem_desc(st + (role == 1 ? L.stage_do : L.stage_q), 0, 8 * kRowBytes, RowSwizzle<C>::umma);
                     const uint32_t dcol = tmem + (role == 1 ? kColDV : kColDK);
-#pragma unroll
+#pragma unroll 1
                     for (int ks = 0; ks < kTileM / 16; ++ks)
                         ptx::mma_ss(dcol, tc::desc_advance(a_t, ks * 2 * lboq), tc::desc_advance(b_t, ks * 16 * kRowBytes), idesc_dkv, ks > 0 ? 1u : 0u);
-                    if (L.own_out) ptx::mma_commit(&misc->empty[s][role == 1 ? kDO : kQ]);  // dO: dP and dV done; Q: S and dK done
+                    if constexpr (OWN_OUT) ptx::mma_commit(&misc->empty[s][role == 1 ? kDO : kQ]);  // dO: dP and dV done; Q: S and dK done
                 }
                 ptx::mma_commit(&misc->o_ready);
                 if (role == 0) NA1D_STAMP(11);
@@ -262,55 +274,62 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
         const float sc = gm.scale * kLog2e;
         const float mask2 = kMaskValue * kLog2e;
+        const float inv_T = 1.f / (float)T, inv_H = 1.f / (float)gm.H;
         const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
+        if (rpb) {
+            // bias table of every head, once per CTA (barrier among the 4 compute warps only)
+            for (int i = r; i < gm.H * kBiasRowB; i += 128) {
+                const int hh_ = i / kBiasRowB, kk = i - hh_ * kBiasRowB - kBiasPad;
+                bias_tab[i] = (kk >= 0 && kk < win) ? __ldg(rpb + hh_ * win + kk) * kLog2e : 0.f;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         int it = 0;
-        int cached_h = -1;
         // log-sum-exp of the four fragment rows of a tile; loaded one tile ahead so the DRAM latency is hidden
         auto load_lse = [&](int tile_, float (&dst)[2][2]) {
-            const int n_ = tile_ / tiles_per_seq;
-            const int w0_ = (tile_ - n_ * tiles_per_seq) * stride - right;
+            const int g0_ = tile_ * stride - right;
 #pragma unroll
             for (int b = 0; b < 2; ++b)
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
-                    const int t = w0_ + warp * 32 + 16 * b + 8 * hh + fr;
-                    dst[b][hh] = (tile_ < total_tiles && t >= 0 && t < T) ? __ldg(lse + (size_t)n_ * T + t) : 0.f;
+                    const int gq = g0_ + warp * 32 + 16 * b + 8 * hh + fr;
+                    dst[b][hh] = (tile_ < total_tiles && gq >= 0 && gq < rows_total) ? __ldg(lse + gq) : 0.f;
                 }
         };
         float lse_next[2][2];
         load_lse(blockIdx.x, lse_next);
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+        tc::RowCursor cur;  // row tile * stride = g0 + right
+        cur.init(blockIdx.x * stride, T, gm.H, gridDim.x * stride);
+        const int batch = gm.N / gm.H;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it, cur.advance()) {
             if (tid == 0) NA1D_STAMP(0);
-            const int n = tile / tiles_per_seq;
-            const int w0 = (tile - n * tiles_per_seq) * stride - right;
-            const int h = n % gm.H;
-            const int vl = valid_len ? __ldg(valid_len + n / gm.H) : T;
-            const int jmax = min(T, vl);
+            const int g0 = tile * stride - right;
             // the four query rows this thread sees in the fragments: block b, row half hh (lse was fetched one tile ahead)
+            // The four rows this thread sees in the fragments (local rows 32 warp + fr + 8k; lse was fetched one tile ahead):
+            //   jb  : key index inside the row's own sequence of neighbour kk is jb + (kk - fa); outside [0, T) it is the
+            //         reference's zero-padded K/V row
+            //   vle : keys >= vle are masked (0 when the query itself is padding);  -1 marks a row outside the tensor
             float lse2[2][2];
-            bool vq[2][2], qm[2][2];
+            int jb[2][2], vle[2][2], hrow[2][2];
+            bool need_mask = false;
+            {
+                int tq, hq, bq;
+                cur.row_at(warp * 32 + fr - right, inv_T, inv_H, tq, hq, bq);
 #pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const int t = w0 + warp * 32 + 16 * b + 8 * hh + fr;
-                    vq[b][hh] = t >= 0 && t < T;
-                    qm[b][hh] = t >= vl;
-                    lse2[b][hh] = lse_next[b][hh] * kLog2e;
+                for (int k = 0; k < 4; ++k) {
+                    const int gq = g0 + warp * 32 + fr + 8 * k;
+                    const bool live = gq >= 0 && gq < rows_total;
+                    const int vlr = !live ? 0 : valid_len ? min(T, __ldg(valid_len + min(max(bq, 0), batch - 1))) : T;
+                    hrow[k >> 1][k & 1] = hq;
+                    jb[k >> 1][k & 1] = tq - left + fa;
+                    vle[k >> 1][k & 1] = !live ? -1 : tq >= vlr ? 0 : vlr;
+                    need_mask |= tq < left || tq + right >= vlr;
+                    lse2[k >> 1][k & 1] = lse_next[k >> 1][k & 1] * kLog2e;
+                    tc::row_step8(T, gm.H, tq, hq, bq);
                 }
-            if (rpb && h != cached_h) {
-                // bias table of this head (all compute threads agree on h; barrier among the 4 compute warps only)
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (r < kBiasPad + 64) {
-                    const int kk = r - kBiasPad;
-                    misc->bias[r] = (kk >= 0 && kk < win) ? __ldg(rpb + h * win + kk) * kLog2e : 0.f;
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                cached_h = h;
             }
-            // masks are needed only when the warp's keys or queries touch a sequence end or the padded region
-            const int jlo = w0 - left + warp * 32, jhi = jlo + 16 + 8 * NG + 16;
-            const bool need_mask = jlo < 0 || jhi > jmax || (w0 + warp * 32 + 32 > vl);
+            // masks are needed only when one of the warp's rows touches a sequence end or a padded region
+            need_mask = __any_sync(0xffffffffu, need_mask);
             if (tid == 0) NA1D_STAMP(1);
             if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 14); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
@@ -328,34 +347,45 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             ptx::mbar_arrive(&misc->s_free);
             if (tid == 0) NA1D_STAMP(3);
             float delta[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+            // two straight-line copies of the element loop, with and without masks
+            auto elements = [&](auto masked_tag) {
+                constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
-            for (int b = 0; b < 2; ++b)
+                for (int b = 0; b < 2; ++b)
 #pragma unroll
-                for (int g = 0; g < NG; ++g)
+                    for (int g = 0; g < NG; ++g)
 #pragma unroll
-                    for (int hh = 0; hh < 2; ++hh)
+                        for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int idx = 4 * g + 2 * hh + e;
-                            const int kk = 8 * (g - hh) + e + fa;
-                            const bool inband = (unsigned)kk < (unsigned)win;
-                            float bias = 0.f;
-                            if (rpb) bias = misc->bias[kk + kBiasPad];
-                            if (need_mask) {
-                                const int j = w0 - left + warp * 32 + 16 * b + 8 * g + fc + e;
-                                if (j < 0 || j >= jmax || qm[b][hh]) bias += mask2;
+                            for (int e = 0; e < 2; ++e) {
+                                const int idx = 4 * g + 2 * hh + e;
+                                const int kc = 8 * (g - hh) + e, kk = kc + fa;
+                                bool on = (unsigned)kk < (unsigned)win;
+                                float bias = 0.f;
+                                if (rpb) bias = bias_tab[hrow[b][hh] * kBiasRowB + kBiasPad + kk];
+                                float dot = s[b][idx], dpv = d[b][idx];
+                                if constexpr (kMasked) {
+                                    const unsigned j = (unsigned)(jb[b][hh] + kc);
+                                    if (j >= (unsigned)T) { dot = 0.f; dpv = 0.f; }  // the reference's zero-padded K/V row
+                                    if ((int)j >= vle[b][hh] || (int)j < 0) bias += mask2;
+                                    on = on && vle[b][hh] >= 0;
+                                }
+                                const float x = fmaf(dot, sc, bias) - lse2[b][hh];
+                                const float p = on ? tc::fast_exp2(x) : 0.f;
+                                s[b][idx] = p;
+                                d[b][idx] = dpv;
+                                delta[b][hh] = fmaf(p, dpv, delta[b][hh]);
                             }
-                            const float x = fmaf(s[b][idx], sc, bias) - lse2[b][hh];
-                            const float p = (inband && vq[b][hh]) ? tc::fast_exp2(x) : 0.f;
-                            s[b][idx] = p;
-                            delta[b][hh] = fmaf(p, d[b][idx], delta[b][hh]);
-                        }
+            };
+            if (need_mask) elements(std::true_type{}); else elements(std::false_type{});
+            if (tid == 0) NA1D_STAMP(12);
 #pragma unroll
             for (int b = 0; b < 2; ++b)
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) delta[b][hh] = tc::quad_sum(delta[b][hh]);
             // batch 2 of the previous tile must have finished reading the operand matrices before they are rewritten
             if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
+            if (tid == 0) NA1D_STAMP(13);
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
                 uint32_t pk_p[2 * NG], pk_d[2 * NG];
@@ -364,10 +394,25 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) {
                         const int idx = 4 * g + 2 * hh;
-                        const float ds0 = s[b][idx] * (d[b][idx] - delta[b][hh]);
-                        const float ds1 = s[b][idx + 1] * (d[b][idx + 1] - delta[b][hh]);
+                        float ds0 = s[b][idx] * (d[b][idx] - delta[b][hh]);
+                        float ds1 = s[b][idx + 1] * (d[b][idx + 1] - delta[b][hh]);
+                        float p0 = s[b][idx], p1 = s[b][idx + 1];
+                        if (need_mask) {
+                            // a neighbour outside the query's sequence is a zero K/V row in the reference: its logit still has a
+                            // bias gradient, but it must not reach the other sequence's dK/dV nor this query's dQ
+                            const int kc = 8 * (g - hh), kk0 = kc + fa;
+                            const int j0 = jb[b][hh] + kc;
+                            const int row = warp * 32 + 16 * b + 8 * hh + fr;
+                            const bool own = d_rpb && row >= right && row < kTileM - left;
+                            const bool out0 = (unsigned)j0 >= (unsigned)T, out1 = (unsigned)(j0 + 1) >= (unsigned)T;
+                            if (out0 | out1) {
+                                if (own) bias_grad_outside(d_rpb + hrow[b][hh] * win + kk0, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
+                                if (out0) { ds0 = 0.f; p0 = 0.f; }
+                                if (out1) { ds1 = 0.f; p1 = 0.f; }
+                            }
+                        }
                         pk_d[2 * g + hh] = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
-                        pk_p[2 * g + hh] = Cvt<E>::pack2(s[b][idx], s[b][idx + 1]);
+                        pk_p[2 * g + hh] = Cvt<E>::pack2(p0, p1);
                     }
                 // core matrix of the block's first row / first column: row group 4w+2b, column group 4w+2b
                 const uint32_t blk = (uint32_t)(4 * warp + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * warp + 2 * b) * 128u;
@@ -384,17 +429,32 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 // d_rpb[h][kk] += dS over the query rows this tile owns: thread r reads the band of row r back
                 // from the dS operand (16-bit, scaled), the warp reduces, one atomic per warp and neighbour
                 __syncwarp();
-                const bool own = r >= right && r < kTileM - left && (w0 + r) >= 0 && (w0 + r) < T;
+                const int gr = g0 + r;
+                const bool own = r >= right && r < kTileM - left && gr >= 0 && gr < rows_total;
+                int hr = 0;
+                if (own) {
+                    int tr, br;
+                    cur.row_at(r - right, inv_T, inv_H, tr, hr, br);
+                }
+                const int h_hi = __reduce_max_sync(0xffffffffu, own ? hr : -1);
+                const int h0 = __reduce_min_sync(0xffffffffu, own ? hr : 0x7fffffff);
+                const bool one_head = h_hi == h0;  // all owned rows of the warp belong to sequences of one head
                 const float inv_scale = 1.f / gm.scale;
                 const uint8_t* row = sDS + (r >> 3) * lboq + (r & 7) * 16;
-#pragma unroll
-                for (int kk = 0; kk < WB; ++kk) {
-                    if (kk < win) {
+#pragma unroll 1
+                for (int kk = 0; kk < win; ++kk) {
+                    {
                         const int col = r + kk;
                         float x = own ? (float)*reinterpret_cast<const E*>(row + (col >> 3) * 128 + (col & 7) * 2) * inv_scale : 0.f;
+                        if (h_hi < 0) {
+                            // no owned row in this warp
+                        } else if (one_head) {
 #pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
-                        if (lane == 0 && x != 0.f) atomicAdd(d_rpb + h * win + kk, x);
+                            for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+                            if (lane == 0 && x != 0.f) atomicAdd(d_rpb + h0 * win + kk, x);
+                        } else if (x != 0.f) {
+                            atomicAdd(d_rpb + hr * win + kk, x);  // the warp's rows belong to sequences of different heads
+                        }
                     }
                 }
             }
@@ -408,14 +468,13 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         constexpr int CH = C / 8;
         int it = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-            const int n = tile / tiles_per_seq;
-            const int ti = tile - n * tiles_per_seq;
+            const int out_row = tile * stride;  // first flattened row this tile stores (dQ, dK and dV alike)
             uint8_t* st = smem + (it & 1) * L.stage_bytes;
             if (!ptx::mbar_wait_relaxed(&misc->o_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 15); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
             if (tid == 128) NA1D_STAMP(6);
             // owned rows: dQ rows [right, right+stride), dK/dV rows [win-1, 128); both land on global rows
-            // [ti*stride, (ti+1)*stride) and are staged from row 0 of the (now idle) Q / dO / K buffers
+            // [out_row, out_row+stride) and are staged from row 0 of the (now idle) Q / dO / K buffers
             auto stage_rows = [&](uint8_t* buf, const float* acc, int m_first) {
                 const int ms = r - m_first;  // staging row
                 if (ms >= 0 && ms < stride) {
@@ -425,7 +484,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                         *reinterpret_cast<uint4*>(buf + ms * kRowBytes + ((c ^ swz) * 16)) = Cvt<E>::pack(acc + c * 8);
                 }
             };
-            if (L.own_out) {
+            if constexpr (OWN_OUT) {
                 // drain all three accumulators to 16-bit registers first so the MMA warp can reuse them, then
                 // one staging buffer, three rounds: stage -> TMA store -> wait until the store has read it
                 uint8_t* buf = smem + L.out;
@@ -454,7 +513,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     ptx::fence_proxy_async_smem();
                     asm volatile("bar.sync 2, 128;" ::: "memory");
                     if (tid == 128) {
-                        ptx::tma_store_3d(which == 0 ? &tm_dq : which == 1 ? &tm_dv : &tm_dk, buf, 0, ti * stride, n);
+                        ptx::tma_store_3d(which == 0 ? &tm_dq : which == 1 ? &tm_dv : &tm_dk, buf, 0, out_row, 0);
                         ptx::tma_store_commit();
                         ptx::tma_store_wait_read();
                     }
@@ -481,9 +540,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 ptx::fence_proxy_async_smem();
                 asm volatile("bar.sync 2, 128;" ::: "memory");
                 if (tid == 128) {
-                    ptx::tma_store_3d(&tm_dq, st + L.stage_q, 0, ti * stride, n);
-                    ptx::tma_store_3d(&tm_dk, st + L.stage_do, 0, ti * stride, n);
-                    ptx::tma_store_3d(&tm_dv, st + L.stage_k, 0, ti * stride, n);
+                    ptx::tma_store_3d(&tm_dq, st + L.stage_q, 0, out_row, 0);
+                    ptx::tma_store_3d(&tm_dk, st + L.stage_do, 0, out_row, 0);
+                    ptx::tma_store_3d(&tm_dv, st + L.stage_k, 0, out_row, 0);
                     ptx::tma_store_commit();
                     ptx::tma_store_wait_read();
                     // the staging used the tile's Q, dO and K buffers: only now may the producer refill them
@@ -507,12 +566,17 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 template <typename E, int C, int WB>
 cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUtensorMap& mk, const CUtensorMap& mv,
                        const CUtensorMap& mdq, const CUtensorMap& mdk, const CUtensorMap& mdv, float* d_rpb, const float* lse, const float* rpb, const int* valid_len,
-                       const Geometry& gm, int tiles_per_seq, int stride, int KT, int sm_count, cudaStream_t st) {
-    const int smem = bwd_layout(C, KT).total;
-    auto kern = tc_bwd_kernel<E, C, WB>;
+                       const Geometry& gm, int stride, int KT, int sm_count, cudaStream_t st) {
+    const BwdSmemLayout L = bwd_layout(C, KT, rpb ? gm.H : 0);
+    const int smem = L.total;
+    // only 64-channel rows can be too large for the dedicated output staging buffer
+    if constexpr (C != 64) {
+        if (!L.own_out) return cudaErrorInvalidValue;
+    }
+    auto kern = (C == 64 && !L.own_out) ? tc_bwd_kernel<E, C, WB, C != 64> : tc_bwd_kernel<E, C, WB, true>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    const int total = gm.N * tiles_per_seq;
+    const int total = (gm.N * gm.T + stride - 1) / stride;
     const int grid = total < sm_count ? total : sm_count;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
@@ -524,14 +588,14 @@ cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUte
     attr[0].val.programmaticStreamSerializationAllowed = (pdl_mode() == 1 || pdl_mode() == 3) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm, tiles_per_seq,
+    return cudaLaunchKernelEx(&cfg, kern, mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm,
                                        stride, KT, total);
 }
 
 }  // namespace
 
 bool tc_bwd_supports(const Geometry& gm) {
-    return gm.dil == 1 && (gm.C == 64 || gm.C == 32 || gm.C == 16) && gm.win <= 33;
+    return gm.dil == 1 && (gm.C == 64 || gm.C == 32 || gm.C == 16) && gm.win <= 33 && gm.H <= 32 && gm.T >= 32 && gm.T < (1 << 21);
 }
 
 // Reads and clears the backward kernels' status word (synchronises the device).
@@ -554,17 +618,17 @@ cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void*
     if (!tc_bwd_supports(gm)) return cudaErrorInvalidValue;
     const int KT = round_up(kTileM + gm.win - 1, 16);
     const int stride = kTileM - (gm.win - 1);
-    const int tiles_per_seq = (gm.T + stride - 1) / stride;
+    const int rows = gm.N * gm.T;  // the tensors are tiled as one (N*T, C) matrix
     CUtensorMap mq, mdo, mk, mv, mdq, mdk, mdv;
-    if (!make_row_tile_map(&mdq, dq, dtype, gm.N, gm.T, gm.C, stride) || !make_row_tile_map(&mdk, dk, dtype, gm.N, gm.T, gm.C, stride) ||
-        !make_row_tile_map(&mdv, dv, dtype, gm.N, gm.T, gm.C, stride))
+    if (!make_row_tile_map(&mdq, dq, dtype, 1, rows, gm.C, stride) || !make_row_tile_map(&mdk, dk, dtype, 1, rows, gm.C, stride) ||
+        !make_row_tile_map(&mdv, dv, dtype, 1, rows, gm.C, stride))
         return cudaErrorInvalidValue;
-    if (!make_row_tile_map(&mq, q, dtype, gm.N, gm.T, gm.C, kTileM) || !make_row_tile_map(&mdo, d_o, dtype, gm.N, gm.T, gm.C, kTileM) ||
-        !make_row_tile_map(&mk, k, dtype, gm.N, gm.T, gm.C, KT) || !make_row_tile_map(&mv, v, dtype, gm.N, gm.T, gm.C, KT))
+    if (!make_row_tile_map(&mq, q, dtype, 1, rows, gm.C, kTileM) || !make_row_tile_map(&mdo, d_o, dtype, 1, rows, gm.C, kTileM) ||
+        !make_row_tile_map(&mk, k, dtype, 1, rows, gm.C, KT) || !make_row_tile_map(&mv, v, dtype, 1, rows, gm.C, KT))
         return cudaErrorInvalidValue;
     const int sms = device_sm_count();
 #define NA1D_TC_BWD(E, C, WB) \
-    return launch_bwd<E, C, WB>(mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm, tiles_per_seq, stride, KT, sms, st)
+    return launch_bwd<E, C, WB>(mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm, stride, KT, sms, st)
 #define NA1D_TC_BWD_W(E, C)                          \
     if (gm.win <= 9) { NA1D_TC_BWD(E, C, 9); }       \
     else if (gm.win <= 17) { NA1D_TC_BWD(E, C, 17); } \

@@ -137,6 +137,58 @@ __device__ __forceinline__ void store_rows_coalesced(uint8_t* stage, const float
     }
 }
 
+// floor(x / d) and the remainder for |x| < 2^22, 0 < d < 2^22, with inv_d = 1.f / d: the float quotient is off by at most
+// one, which a single correction step repairs. Replaces the ~40-instruction integer division in per-row index math.
+__device__ __forceinline__ int small_div(int x, int d, float inv_d, int* rem) {
+    int q = __float2int_rd((float)x * inv_d);
+    int r = x - q * d;
+    if (r < 0) { --q; r += d; }
+    else if (r >= d) { ++q; r -= d; }
+    *rem = r;
+    return q;
+}
+
+// Position of a tile's first row on the flattened (sequence, token) axis: token index t, head h, batch index b.
+// One real division at the start; afterwards a persistent CTA moves from tile to tile with adds and compares only.
+struct RowCursor {
+    int t, h, b;
+    int T, H, step_t, step_h, step_b;
+    __device__ __forceinline__ void init(int row, int T_, int H_, int step_rows) {  // row >= 0
+        T = T_; H = H_;
+        const int n = row / T;
+        t = row - n * T;
+        b = n / H;
+        h = n - b * H;
+        const int sn = step_rows / T;
+        step_t = step_rows - sn * T;
+        step_b = sn / H;
+        step_h = sn - step_b * H;
+    }
+    __device__ __forceinline__ void advance() {
+        t += step_t;
+        const int carry = t >= T ? 1 : 0;
+        t -= carry ? T : 0;
+        h += step_h + carry;
+        b += step_b;
+        if (h >= H) { h -= H; ++b; }
+        if (h >= H) { h -= H; ++b; }
+    }
+    // the row `off` rows away from the cursor, -T < off < 2^21
+    __device__ __forceinline__ void row_at(int off, float inv_T, float inv_H, int& tq, int& hq, int& bq) const {
+        const int dn = small_div(t + off, T, inv_T, &tq);
+        const int db = small_div(h + dn, H, inv_H, &hq);
+        bq = b + db;
+    }
+};
+// eight rows further on; T >= 8
+__device__ __forceinline__ void row_step8(int T, int H, int& tq, int& hq, int& bq) {
+    tq += 8;
+    if (tq >= T) {
+        tq -= T;
+        if (++hq >= H) { hq = 0; ++bq; }
+    }
+}
+
 __device__ __forceinline__ float quad_sum(float x) {
     x += __shfl_xor_sync(0xffffffffu, x, 1);
     x += __shfl_xor_sync(0xffffffffu, x, 2);

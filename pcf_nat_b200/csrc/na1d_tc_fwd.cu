@@ -1,8 +1,12 @@
 // Fused NA1D forward on the Blackwell tensor path (sm_100a): persistent, warp-specialised,
 // TMA-staged tiles, tcgen05 MMAs with accumulators (and the probability operand) in tensor memory.
 //
-// A tile is 128 consecutive queries of one sequence. Per tile (192 threads, up to two CTAs per SM):
-//   warp 4  : TMA producer -- Q[128 x C] and K, V rows [t0-left, t0-left+KT), KT = round16(128+win-1),
+// Rows are tiled over the FLATTENED (sequence, token) axis: tile i is rows g0 = 128 i .. g0+127 of the (N*T, C) matrix,
+// so every tile is full whatever T is. A tile may span several sequences; a neighbour outside the query's own sequence is
+// what the reference reads as a zero-padded row (na1d_tensorcore/bf16_ana1d_kernel.cu:99-112): its logit is rpb - 100 and
+// it contributes nothing to the output, which is enforced per element.
+// Per tile (224 threads, up to two CTAs per SM):
+//   warp 4  : TMA producer -- Q[128 x C] and K, V rows [g0-left, g0-left+KT), KT = round16(128+win-1),
 //             into a 2-stage ring. Plain (non-multicast) tile loads; rows outside [0,T) arrive as
 //             zeros, which is the reference's zero padding of K and V
 //             (na1d_tensorcore/bf16_ana1d_kernel.cu:99-112).
@@ -20,6 +24,7 @@
 // Every wait is bounded; on expiry the CTA records a code in a device status word and unwinds
 // (TMEM is always released).
 #include "na1d_internal.h"
+#include <type_traits>
 #include "na1d_tc_common.cuh"
 
 namespace na1d {
@@ -53,14 +58,14 @@ constexpr int kBiasPad = 16;
 struct FwdSmemLayout {
     int stage_q, stage_k, stage_v, stage_bytes, misc, total;
 };
-__host__ __device__ inline FwdSmemLayout fwd_layout(int C, int KT) {
+__host__ __device__ inline FwdSmemLayout fwd_layout(int C, int KT, int bias_heads) {
     FwdSmemLayout L;
     L.stage_q = 0;
     L.stage_k = L.stage_q + round_up(kTileM * C * 2, 1024);
     L.stage_v = L.stage_k + round_up(KT * C * 2, 1024);
     L.stage_bytes = L.stage_v + round_up(KT * C * 2, 1024);
     L.misc = 2 * L.stage_bytes;
-    L.total = L.misc + 1024 + 1008;
+    L.total = L.misc + 256 + round_up(bias_heads * (kBiasPad + 48) * 4, 256) + 1008;  // misc, bias table, alignment slack
     return L;
 }
 
@@ -69,22 +74,23 @@ struct alignas(8) FwdMisc {
     uint64_t s_ready, p_ready, o_ready, o_free, o_staged;
     uint32_t tmem_base;
     int abort;
-    float bias[kBiasPad + 64];
 };
+constexpr int kBiasRow = kBiasPad + 48;  // per-head table: log2e * rpb[h][kk] at index kk + kBiasPad, kk in [-16, 48)
 
 template <typename E, int C, int WB>
 __global__ void __launch_bounds__(kThreads, 2)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, float* __restrict__ lse,
-              const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, int tiles_per_seq, int KT,
-              int total_tiles) {
+              const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, int KT, int total_tiles) {
     constexpr int NG = tc::band_groups(WB);
     constexpr int kRowBytes = C * 2;
     NA1D_CTA_TIME(0);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const FwdSmemLayout L = fwd_layout(C, KT);
+    const FwdSmemLayout L = fwd_layout(C, KT, rpb ? gm.H : 0);
     FwdMisc* misc = reinterpret_cast<FwdMisc*>(smem + L.misc);
+    float* bias_tab = reinterpret_cast<float*>(smem + L.misc + 256);
+    const int rows_total = gm.N * gm.T;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int win = gm.win, left = gm.left, T = gm.T;
@@ -128,13 +134,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1, k = it >> 1;
                 if (!ptx::mbar_wait_relaxed(&misc->empty[s], (k & 1) ^ 1) || *abort_flag) { atomicExch(&g_tc_status, 1); *abort_flag = 1; break; }
-                const int n = tile / tiles_per_seq;
-                const int t0 = (tile - n * tiles_per_seq) * kTileM;
+                const int g0 = tile * kTileM;
                 uint8_t* st = smem + s * L.stage_bytes;
                 ptx::mbar_expect_tx(&misc->full[s], (uint32_t)stage_tx);
-                ptx::tma_load_3d(st + L.stage_q, &tm_q, &misc->full[s], 0, t0, n);
-                ptx::tma_load_3d(st + L.stage_k, &tm_k, &misc->full[s], 0, t0 - left, n);
-                ptx::tma_load_3d(st + L.stage_v, &tm_v, &misc->full[s], 0, t0 - left, n);
+                ptx::tma_load_3d(st + L.stage_q, &tm_q, &misc->full[s], 0, g0, 0);
+                ptx::tma_load_3d(st + L.stage_k, &tm_k, &misc->full[s], 0, g0 - left, 0);
+                ptx::tma_load_3d(st + L.stage_v, &tm_v, &misc->full[s], 0, g0 - left, 0);
             }
         } else if (lane == 1) {
             // ---------------------------------------------------------- output store thread: waits until the softmax warps
@@ -142,9 +147,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             int it = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
                 if (!ptx::mbar_wait_relaxed(&misc->o_staged, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 6); *abort_flag = 1; break; }
-                const int n = tile / tiles_per_seq;
-                const int t0 = (tile - n * tiles_per_seq) * kTileM;
-                ptx::tma_store_3d(&tm_o, smem + (it & 1) * L.stage_bytes + L.stage_q, 0, t0, n);
+                ptx::tma_store_3d(&tm_o, smem + (it & 1) * L.stage_bytes + L.stage_q, 0, tile * kTileM, 0);
                 ptx::tma_store_commit();
                 ptx::tma_store_wait_read();
                 ptx::mbar_arrive(&misc->empty[it & 1]);
@@ -217,26 +220,45 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
         const float sc = gm.scale * kLog2e;
         const float mask2 = kMaskValue * kLog2e;
-        int it = 0;
-        int cached_h = -1;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-            if (tid == 0) NA1D_FSTAMP(0);
-            const int n = tile / tiles_per_seq;
-            const int t0 = (tile - n * tiles_per_seq) * kTileM;
-            const int h = n % gm.H;
-            const int vl = valid_len ? __ldg(valid_len + n / gm.H) : T;
-            const int jmax = min(T, vl);
-            if (rpb && h != cached_h) {
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (r < kBiasPad + 64) {
-                    const int kk = r - kBiasPad;
-                    misc->bias[r] = (kk >= 0 && kk < win) ? __ldg(rpb + h * win + kk) * kLog2e : 0.f;
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                cached_h = h;
+        const float inv_T = 1.f / (float)T, inv_H = 1.f / (float)gm.H;
+        if (rpb) {
+            // bias table of every head, once per CTA (barrier among the 4 softmax warps only)
+            for (int i = r; i < gm.H * kBiasRow; i += 128) {
+                const int hh_ = i / kBiasRow, kk = i - hh_ * kBiasRow - kBiasPad;
+                bias_tab[i] = (kk >= 0 && kk < win) ? __ldg(rpb + hh_ * win + kk) * kLog2e : 0.f;
             }
-            const int jlo = t0 - left + warp * 32, jhi = jlo + 16 + 8 * NG + 16;
-            const bool need_mask = jlo < 0 || jhi > jmax || (t0 + warp * 32 + 32 > vl);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        int it = 0;
+        tc::RowCursor cur;
+        cur.init(blockIdx.x * kTileM, T, gm.H, gridDim.x * kTileM);
+        const int batch = gm.N / gm.H;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it, cur.advance()) {
+            if (tid == 0) NA1D_FSTAMP(0);
+            const int g0 = tile * kTileM;
+            // The four rows this thread sees in the fragments (block b, row half hh = local rows 32 warp + fr + 8k). Per row:
+            //   jb  : key index inside the row's own sequence of neighbour kk is jb + (kk - fa); outside [0, T) it is the
+            //         reference's zero-padded key row
+            //   vle : keys >= vle are masked (0 when the query itself is padding)
+            int jb[2][2], vle[2][2];
+            const float* brow[2][2];
+            bool need_mask = false;
+            {
+                int tq, hq, bq;
+                cur.row_at(warp * 32 + fr, inv_T, inv_H, tq, hq, bq);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const bool live = g0 + warp * 32 + fr + 8 * k < rows_total;
+                    const int vlr = !live ? 0 : valid_len ? min(T, __ldg(valid_len + min(bq, batch - 1))) : T;
+                    brow[k >> 1][k & 1] = bias_tab + hq * kBiasRow + kBiasPad;
+                    jb[k >> 1][k & 1] = tq - left + fa;
+                    vle[k >> 1][k & 1] = tq >= vlr ? 0 : vlr;
+                    need_mask |= tq < left || tq + (win - 1 - left) >= vlr;
+                    tc::row_step8(T, gm.H, tq, hq, bq);
+                }
+            }
+            // masks are needed only when one of the warp's rows touches a sequence end or a padded region
+            need_mask = __any_sync(0xffffffffu, need_mask);
             if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 4); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
             if (tid == 0) NA1D_FSTAMP(1);
@@ -248,30 +270,35 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 tc::ld_frag<NG>(lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b), s[b]);
             ptx::tmem_ld_wait();
             if (tid == 0) NA1D_FSTAMP(2);
-            // logits on the band (log2 domain), everything else -inf
+            // logits on the band (log2 domain), everything else -inf; two straight-line copies, with and without masks
             float mx[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}};
+            auto logits = [&](auto masked_tag) {
+                constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
-            for (int b = 0; b < 2; ++b)
+                for (int b = 0; b < 2; ++b)
 #pragma unroll
-                for (int g = 0; g < NG; ++g)
+                    for (int g = 0; g < NG; ++g)
 #pragma unroll
-                    for (int hh = 0; hh < 2; ++hh)
+                        for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int idx = 4 * g + 2 * hh + e;
-                            const int kk = 8 * (g - hh) + e + fa;
-                            const bool inband = (unsigned)kk < (unsigned)win;
-                            float bias = 0.f;
-                            if (rpb) bias = misc->bias[kk + kBiasPad];
-                            if (need_mask) {
-                                const int j = t0 - left + warp * 32 + 16 * b + 8 * g + fc + e;
-                                const int t = t0 + warp * 32 + 16 * b + 8 * hh + fr;
-                                if (j < 0 || j >= jmax || t >= vl) bias += mask2;
+                            for (int e = 0; e < 2; ++e) {
+                                const int idx = 4 * g + 2 * hh + e;
+                                const int kc = 8 * (g - hh) + e, kk = kc + fa;
+                                const bool inband = (unsigned)kk < (unsigned)win;
+                                float bias = 0.f;
+                                if (rpb) bias = brow[b][hh][kk];
+                                float dot = s[b][idx];
+                                if constexpr (kMasked) {
+                                    const unsigned j = (unsigned)(jb[b][hh] + kc);
+                                    if (j >= (unsigned)T) dot = 0.f;  // key outside the query's own sequence: the reference's zero row
+                                    if (j >= (unsigned)vle[b][hh]) bias += mask2;
+                                }
+                                const float x = inband ? fmaf(dot, sc, bias) : -INFINITY;
+                                s[b][idx] = x;
+                                mx[b][hh] = fmaxf(mx[b][hh], x);
                             }
-                            const float x = inband ? fmaf(s[b][idx], sc, bias) : -INFINITY;
-                            s[b][idx] = x;
-                            mx[b][hh] = fmaxf(mx[b][hh], x);
-                        }
+            };
+            if (need_mask) logits(std::true_type{}); else logits(std::false_type{});
             if (tid == 0) NA1D_FSTAMP(12);
             float sum[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
@@ -296,8 +323,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
                     sum[b][hh] = tc::quad_sum(sum[b][hh]);
-                    const int t = t0 + warp * 32 + 16 * b + 8 * hh + fr;
-                    if (lse && (lane & 3) == 0 && t < T) lse[(size_t)n * T + t] = (mx[b][hh] + tc::fast_log2(sum[b][hh])) * kLn2;
+                    const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
+                    if (lse && (lane & 3) == 0 && gq < rows_total) lse[gq] = (mx[b][hh] + tc::fast_log2(sum[b][hh])) * kLn2;
                     sum[b][hh] = tc::fast_rcp(sum[b][hh]);
                 }
             if (tid == 0) NA1D_FSTAMP(13);
@@ -316,8 +343,18 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
                     for (int g = 0; g < NGP; ++g)
 #pragma unroll
-                        for (int hh = 0; hh < 2; ++hh)
-                            pk[2 * g + hh] = g < NG ? Cvt<E>::pack2(s[b][4 * g + 2 * hh] * sum[b][hh], s[b][4 * g + 2 * hh + 1] * sum[b][hh]) : 0u;
+                        for (int hh = 0; hh < 2; ++hh) {
+                            if (g >= NG) { pk[2 * g + hh] = 0u; continue; }
+                            float p0 = s[b][4 * g + 2 * hh] * sum[b][hh], p1 = s[b][4 * g + 2 * hh + 1] * sum[b][hh];
+                            if (need_mask) {
+                                // a neighbour outside the query's sequence is a zero V row in the reference: it counts in the
+                                // softmax denominator but must not pick up the other sequence's values
+                                const int j0 = jb[b][hh] + 8 * (g - hh);
+                                if ((unsigned)j0 >= (unsigned)T) p0 = 0.f;
+                                if ((unsigned)(j0 + 1) >= (unsigned)T) p1 = 0.f;
+                            }
+                            pk[2 * g + hh] = Cvt<E>::pack2(p0, p1);
+                        }
                     tc::st_pack<NGP>(blk + c0 * 8, pk);
                 }
                 ptx::tmem_st_wait();
@@ -374,13 +411,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
 template <typename E, int C, int WB>
 cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, float* lse,
-                       const float* rpb, const int* valid_len, const Geometry& gm, int tiles_per_seq, int KT, int sm_count,
-                       cudaStream_t st) {
-    const int smem = fwd_layout(C, KT).total;
+                       const float* rpb, const int* valid_len, const Geometry& gm, int KT, int sm_count, cudaStream_t st) {
+    const int smem = fwd_layout(C, KT, rpb ? gm.H : 0).total;
     auto kern = tc_fwd_kernel<E, C, WB>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    const int total = gm.N * tiles_per_seq;
+    const int total = (gm.N * gm.T + kTileM - 1) / kTileM;
     const int per_sm = (2 * (smem + 1024) <= 227 * 1024) ? 2 : 1;
     const int slots = sm_count * per_sm;
     const int grid = total < slots ? total : slots;
@@ -394,7 +430,7 @@ cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     attr[0].val.programmaticStreamSerializationAllowed = (pdl_mode() == 1 || pdl_mode() == 2) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mo, lse, rpb, valid_len, gm, tiles_per_seq, KT, total);
+    return cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mo, lse, rpb, valid_len, gm, KT, total);
 }
 
 }  // namespace
@@ -409,20 +445,20 @@ extern "C" int na1d_debug_fwd_timeline(long long* out) {
 #endif
 
 bool tc_fwd_supports(const Geometry& gm) {
-    return gm.dil == 1 && (gm.C == 64 || gm.C == 32 || gm.C == 16) && gm.win <= 33;
+    return gm.dil == 1 && (gm.C == 64 || gm.C == 32 || gm.C == 16) && gm.win <= 33 && gm.H <= 32 && gm.T >= 32 && gm.T < (1 << 21);
 }
 
 cudaError_t tc_fused_fwd(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
                          const int* valid_len, const Geometry& gm, int dtype, cudaStream_t st) {
     if (!tc_fwd_supports(gm)) return cudaErrorInvalidValue;
     const int KT = round_up(kTileM + gm.win - 1, 16);
-    const int tiles_per_seq = (gm.T + kTileM - 1) / kTileM;
+    const int rows = gm.N * gm.T;  // the tensors are tiled as one (N*T, C) matrix
     CUtensorMap mq, mk, mv, mo;
-    if (!make_row_tile_map(&mq, q, dtype, gm.N, gm.T, gm.C, kTileM) || !make_row_tile_map(&mk, k, dtype, gm.N, gm.T, gm.C, KT) ||
-        !make_row_tile_map(&mv, v, dtype, gm.N, gm.T, gm.C, KT) || !make_row_tile_map(&mo, o, dtype, gm.N, gm.T, gm.C, kTileM))
+    if (!make_row_tile_map(&mq, q, dtype, 1, rows, gm.C, kTileM) || !make_row_tile_map(&mk, k, dtype, 1, rows, gm.C, KT) ||
+        !make_row_tile_map(&mv, v, dtype, 1, rows, gm.C, KT) || !make_row_tile_map(&mo, o, dtype, 1, rows, gm.C, kTileM))
         return cudaErrorInvalidValue;
     const int sms = device_sm_count();
-#define NA1D_TC_FWD(E, C, WB) return launch_fwd<E, C, WB>(mq, mk, mv, mo, lse, rpb, valid_len, gm, tiles_per_seq, KT, sms, st)
+#define NA1D_TC_FWD(E, C, WB) return launch_fwd<E, C, WB>(mq, mk, mv, mo, lse, rpb, valid_len, gm, KT, sms, st)
 #define NA1D_TC_FWD_W(E, C)                          \
     if (gm.win <= 9) { NA1D_TC_FWD(E, C, 9); }       \
     else if (gm.win <= 17) { NA1D_TC_FWD(E, C, 17); } \

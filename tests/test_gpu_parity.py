@@ -247,7 +247,10 @@ def test_bad_arguments_raise_without_touching_the_device():
 
 
 # ------------------------------------------------------------------ tcgen05 family: shapes it must take, and parity there
-TC_SHAPES = [(N, T, C, win, left) for (N, T) in ((3, 200), (2, 128), (1, 129), (2, 1), (1, 1000), (2, 383))
+# (sequences, heads, tokens): tiles run over the flattened (sequence, token) axis, so short sequences of several heads
+# share a tile and long ones straddle tiles
+TC_SHAPES = [(N, H, T, C, win, left) for (N, H, T) in ((3, 1, 200), (2, 1, 128), (1, 1, 129), (2, 2, 32), (1, 1, 1000),
+                                                        (2, 1, 383), (12, 4, 50), (6, 3, 150), (8, 2, 33))
              for (C, win, left) in ((64, 7, 3), (32, 7, 3), (16, 27, 13), (64, 15, 7), (64, 31, 15), (32, 33, 0),
                                     (16, 3, 2), (64, 8, 3), (32, 17, 16), (64, 9, 4), (16, 18, 9))]
 
@@ -258,17 +261,16 @@ def test_tcgen05_forward_backward_shapes(dtype):
     fam = ops.FAMILY_TCGEN05
     old = ops.set_kernel_family(fam)
     try:
-        for idx, (N, T, C, win, left) in enumerate(TC_SHAPES):
+        for idx, (N, H, T, C, win, left) in enumerate(TC_SHAPES):
             assert ops.kernel_family(N, T, C, win, left, 1, dtype) == fam, "tcgen05 family should take this shape"
-            H = 1
             sc = C ** -0.5
             q, k, v = (randn16((N, T, C), dtype, 500 + 3 * idx + i) for i in range(3))
             rpb = 0.3 * torch.randn(H, win, generator=torch.Generator().manual_seed(idx))
-            vl = [T] + [max(1, T - 5)] * (N - 1)
+            vl = [T] + [max(1, T - 5)] * (N // H - 1)
             o, lse = ops.fused_forward(q.cuda(), k.cuda(), v.cuda(), win, left, 1, sc, rpb.cuda(), vl, H)
             ops.device_status()
             o_r, lse_r = orc.na1d_fused(q.float(), k.float(), v.float(), win, left, 1, sc, rpb, vl, H, return_lse=True)
-            tag = "N=%d T=%d C=%d win=%d left=%d " % (N, T, C, win, left)
+            tag = "N=%d H=%d T=%d C=%d win=%d left=%d " % (N, H, T, C, win, left)
             assert_close(o, o_r, dtype, tag + "o")
             assert float((lse.cpu() - lse_r).abs().max()) < 1e-3 * max(1.0, float(lse_r.abs().max())), tag + "lse"
             # backward through the tcgen05 family as well
