@@ -199,46 +199,49 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
             const int nks = KT / 16;
             // this role's part of batch 1 of tile `jt`: S = Q.K^T -> cols [0,KT) (role 0), dP = dO.V^T -> cols [160,160+KT) (role 1)
-            auto batch1 = [&](int jt) -> bool {
+            auto batch1_ready = [&](int jt) -> bool {  // non-blocking: have this role's two operands of tile jt landed?
                 const int s = jt & 1, k = jt >> 1;
-                const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
-                if (role == 0) {
-                    if (!ptx::mbar_wait(&misc->full[s][kK], k & 1) || !ptx::mbar_wait(&misc->full[s][kQ], k & 1)) return false;
-                    ptx::tc_fence_after_sync();
-                    const uint64_t dq0 = ptx::smem_desc(st + L.stage_q, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    const uint64_t dk0 = ptx::smem_desc(st + L.stage_k, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-#pragma unroll
-                    for (int ks = 0; ks < C / 16; ++ks)
-                        ptx::mma_ss(tmem, tc::desc_advance(dq0, ks * 32), tc::desc_advance(dk0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
-                    ptx::mma_commit(&misc->s_ready);
-                } else if (role == 1) {
-                    if (!ptx::mbar_wait(&misc->full[s][kV], k & 1) || !ptx::mbar_wait(&misc->full[s][kDO], k & 1)) return false;
-                    ptx::tc_fence_after_sync();
-                    const uint64_t dd0 = ptx::smem_desc(st + L.stage_do, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    const uint64_t dv0 = ptx::smem_desc(st + L.stage_v, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-#pragma unroll
-                    for (int ks = 0; ks < C / 16; ++ks)
-                        ptx::mma_ss(tmem + kColDP, tc::desc_advance(dd0, ks * 32), tc::desc_advance(dv0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
-                    ptx::mma_commit(&misc->empty[s][kV]);  // nothing else reads V
-                    ptx::mma_commit(&misc->s_ready);
-                }
-                return true;
+                return ptx::mbar_try_wait(&misc->full[s][role == 0 ? kK : kV], k & 1) &&
+                       ptx::mbar_try_wait(&misc->full[s][role == 0 ? kQ : kDO], k & 1);
             };
-            int it = 0;
-            bool ok = blockIdx.x < total_tiles ? batch1(0) : true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+            auto batch1 = [&](int jt) {
+                const int s = jt & 1;
+                const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
+                ptx::tc_fence_after_sync();
+                const uint64_t da0 = ptx::smem_desc(st + (role == 0 ? L.stage_q : L.stage_do), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                const uint64_t db0 = ptx::smem_desc(st + (role == 0 ? L.stage_k : L.stage_v), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                const uint32_t dcol = tmem + (role == 0 ? 0u : (uint32_t)kColDP);
+#pragma unroll
+                for (int ks = 0; ks < C / 16; ++ks)
+                    ptx::mma_ss(dcol, tc::desc_advance(da0, ks * 32), tc::desc_advance(db0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
+                if (role == 1) ptx::mma_commit(&misc->empty[s][kV]);  // nothing else reads V
+                ptx::mma_commit(&misc->s_ready);
+            };
+            // Two job streams per issuer: batch 1 of iteration j (roles 0 and 1; needs the compute warps to have read S/dP of
+            // iteration j-1 and the operands of tile j in shared memory) and batch 2 of iteration i (needs the compute warps'
+            // operand matrices and the drained accumulator). Whichever is ready first is issued first, so a late TMA load never
+            // holds back MMAs whose inputs are already there. Batch 1 runs at most one iteration ahead of batch 2.
+            const int n_it = blockIdx.x < total_tiles ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+            int next_b1 = role < 2 ? 0 : n_it, it = 0;
+            uint32_t polls = 0;
+            bool ok = true;
+            while (it < n_it) {
+                if (next_b1 < n_it && next_b1 <= it + 1 && (next_b1 == 0 || ptx::mbar_try_wait(&misc->s_free, (next_b1 - 1) & 1)) &&
+                    batch1_ready(next_b1)) {
+                    if (role == 0) NA1D_STAMP(8);
+                    batch1(next_b1);
+                    if (role == 0) NA1D_STAMP(9);
+                    ++next_b1;
+                    polls = 0;
+                    continue;
+                }
+                if (!(ptx::mbar_try_wait(&misc->p_ready, it & 1) && ptx::mbar_try_wait(&misc->o_free[role], (it & 1) ^ 1))) {
+                    if (++polls > (1u << 22) || *abort_flag) { ok = false; break; }
+                    continue;
+                }
+                polls = 0;
                 const int s = it & 1;
                 const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
-                // S/dP of this tile are in the compute warps' registers: the next tile's batch 1 may overwrite them
-                if (role < 2) {
-                    if (!ptx::mbar_wait(&misc->s_free, it & 1) || *abort_flag) { ok = false; break; }
-                    ptx::tc_fence_after_sync();
-                    if (role == 0) NA1D_STAMP(8);
-                    if (tile + gridDim.x < total_tiles && !batch1(it + 1)) { ok = false; break; }
-                    if (role == 0) NA1D_STAMP(9);
-                }
-                // the compute warps have written this tile's operands; the epilogue warps have drained the previous outputs
-                if (!ptx::mbar_wait(&misc->p_ready, it & 1) || !ptx::mbar_wait(&misc->o_free[role], (it & 1) ^ 1) || *abort_flag) { ok = false; break; }
                 ptx::tc_fence_after_sync();
                 if (role == 0) NA1D_STAMP(10);
                 // batch 2. dS/P matrices: element (q, c) at (q/8)*lboq + (c/8)*128 + (q%8)*16 + (c%8)*2.
@@ -263,6 +266,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 }
                 ptx::mma_commit(&misc->o_ready);
                 if (role == 0) NA1D_STAMP(11);
+                ++it;
             }
             if (!ok) { atomicExch(&g_tc_bwd_status, 12); *abort_flag = 1; }
         }
@@ -501,9 +505,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
                     for (int c = 0; c < CH; ++c) pk[which][c] = Cvt<E>::pack(acc + c * 8);
                 }
+                if (tid == 128) NA1D_STAMP(14);
 #pragma unroll
                 for (int which = 0; which < 3; ++which) {
                     if (which > 0) asm volatile("bar.sync 2, 128;" ::: "memory");  // previous store has read the buffer
+                    if (which == 1 && tid == 128) NA1D_STAMP(15);
                     const int ms = r - (which == 0 ? right : win - 1);
                     if (ms >= 0 && ms < stride) {
                         const int swz = (C == 64) ? (ms & 7) : (C == 32) ? ((ms >> 1) & 3) : ((ms >> 2) & 1);

@@ -134,6 +134,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1, k = it >> 1;
                 if (!ptx::mbar_wait_relaxed(&misc->empty[s], (k & 1) ^ 1) || *abort_flag) { atomicExch(&g_tc_status, 1); *abort_flag = 1; break; }
+                // At the start every CTA of the grid loads at once and DRAM is the limit: let the first tile land before the
+                // second is requested, so that all CTAs start computing (and storing) early instead of at the end of the burst.
+                if (it == 1 && !ptx::mbar_wait_relaxed(&misc->full[0], 0)) { atomicExch(&g_tc_status, 1); *abort_flag = 1; break; }
                 const int g0 = tile * kTileM;
                 uint8_t* st = smem + s * L.stage_bytes;
                 ptx::mbar_expect_tx(&misc->full[s], (uint32_t)stage_tx);
