@@ -85,9 +85,11 @@ __host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT, int bias_head
 
 // Bias gradient of neighbours outside the query's own sequence (rare: only padded query rows next to a sequence end have
 // a non-zero probability there). Not inlined, to keep the many call sites of the unrolled loops small.
-__device__ __noinline__ void bias_grad_outside(float* dst, float g0, float g1) {
-    if (g0 != 0.f) atomicAdd(dst, g0);
-    if (g1 != 0.f) atomicAdd(dst + 1, g1);
+// row = this head's row of d_rpb, off = window offset of g0 (g1: off + 1); a non-zero gradient implies an offset that is a
+// neighbour (a multiple of the dilation, 1 << dshift).
+__device__ __noinline__ void bias_grad_outside(float* row, int off, int dshift, float g0, float g1) {
+    if (g0 != 0.f) atomicAdd(row + (off >> dshift), g0);
+    if (g1 != 0.f) atomicAdd(row + ((off + 1) >> dshift), g1);
 }
 
 struct alignas(8) BwdMisc {
@@ -119,7 +121,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int rows_total = gm.N * gm.T;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int win = gm.win, left = gm.left, right = gm.win - 1 - gm.left, T = gm.T;
+    // effective (dilated) window: neighbour kk of the reference is offset kk * dil of it
+    const int dil = gm.dil, dmask = dil - 1, dshift = 31 - __clz(dil);
+    const int win = tc::eff_window(gm.win, dil), left = gm.left * dil, right = (gm.win - 1 - gm.left) * dil, T = gm.T;
     const int lboq = KT * 16;  // bytes between 8-query groups of the dS matrix
 
     if (tid == 0) {
@@ -284,7 +288,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             // bias table of every head, once per CTA (barrier among the 4 compute warps only)
             for (int i = r; i < gm.H * kBiasRowB; i += 128) {
                 const int hh_ = i / kBiasRowB, kk = i - hh_ * kBiasRowB - kBiasPad;
-                bias_tab[i] = (kk >= 0 && kk < win) ? __ldg(rpb + hh_ * win + kk) * kLog2e : 0.f;
+                bias_tab[i] = (kk >= 0 && kk < win && (kk & dmask) == 0) ? __ldg(rpb + hh_ * gm.win + (kk >> dshift)) * kLog2e : 0.f;
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
@@ -364,7 +368,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                             for (int e = 0; e < 2; ++e) {
                                 const int idx = 4 * g + 2 * hh + e;
                                 const int kc = 8 * (g - hh) + e, kk = kc + fa;
-                                bool on = (unsigned)kk < (unsigned)win;
+                                bool on = (unsigned)kk < (unsigned)win && (kk & dmask) == 0;
                                 float bias = 0.f;
                                 if (rpb) bias = bias_tab[hrow[b][hh] * kBiasRowB + kBiasPad + kk];
                                 float dot = s[b][idx], dpv = d[b][idx];
@@ -410,7 +414,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                             const bool own = d_rpb && row >= right && row < kTileM - left;
                             const bool out0 = (unsigned)j0 >= (unsigned)T, out1 = (unsigned)(j0 + 1) >= (unsigned)T;
                             if (out0 | out1) {
-                                if (own) bias_grad_outside(d_rpb + hrow[b][hh] * win + kk0, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
+                                if (own) bias_grad_outside(d_rpb + hrow[b][hh] * gm.win, kk0, dshift, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
                                 if (out0) { ds0 = 0.f; p0 = 0.f; }
                                 if (out1) { ds1 = 0.f; p1 = 0.f; }
                             }
@@ -446,18 +450,18 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 const float inv_scale = 1.f / gm.scale;
                 const uint8_t* row = sDS + (r >> 3) * lboq + (r & 7) * 16;
 #pragma unroll 1
-                for (int kk = 0; kk < win; ++kk) {
+                for (int kk = 0; kk < gm.win; ++kk) {
                     {
-                        const int col = r + kk;
+                        const int col = r + kk * dil;
                         float x = own ? (float)*reinterpret_cast<const E*>(row + (col >> 3) * 128 + (col & 7) * 2) * inv_scale : 0.f;
                         if (h_hi < 0) {
                             // no owned row in this warp
                         } else if (one_head) {
 #pragma unroll
                             for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
-                            if (lane == 0 && x != 0.f) atomicAdd(d_rpb + h0 * win + kk, x);
+                            if (lane == 0 && x != 0.f) atomicAdd(d_rpb + h0 * gm.win + kk, x);
                         } else if (x != 0.f) {
-                            atomicAdd(d_rpb + hr * win + kk, x);  // the warp's rows belong to sequences of different heads
+                            atomicAdd(d_rpb + hr * gm.win + kk, x);  // the warp's rows belong to sequences of different heads
                         }
                     }
                 }
@@ -601,7 +605,7 @@ cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUte
 }  // namespace
 
 bool tc_bwd_supports(const Geometry& gm) {
-    return gm.dil == 1 && (gm.C == 64 || gm.C == 32 || gm.C == 16) && gm.win <= 33 && gm.H <= 32 && gm.T >= 32 && gm.T < (1 << 21);
+    return tc::pow2(gm.dil) && (gm.C == 64 || gm.C == 32 || gm.C == 16) && tc::eff_window(gm.win, gm.dil) <= 33 && gm.H <= 32 && gm.T >= 32 && gm.T < (1 << 21);
 }
 
 // Reads and clears the backward kernels' status word (synchronises the device).
@@ -622,8 +626,9 @@ cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void*
                          const void* v, const float* lse, const float* rpb, const int* valid_len, const Geometry& gm, int dtype,
                          cudaStream_t st) {
     if (!tc_bwd_supports(gm)) return cudaErrorInvalidValue;
-    const int KT = round_up(kTileM + gm.win - 1, 16);
-    const int stride = kTileM - (gm.win - 1);
+    const int weff = tc::eff_window(gm.win, gm.dil);
+    const int KT = round_up(kTileM + weff - 1, 16);
+    const int stride = kTileM - (weff - 1);
     const int rows = gm.N * gm.T;  // the tensors are tiled as one (N*T, C) matrix
     CUtensorMap mq, mdo, mk, mv, mdq, mdk, mdv;
     if (!make_row_tile_map(&mdq, dq, dtype, 1, rows, gm.C, stride) || !make_row_tile_map(&mdk, dk, dtype, 1, rows, gm.C, stride) ||
@@ -636,8 +641,8 @@ cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void*
 #define NA1D_TC_BWD(E, C, WB) \
     return launch_bwd<E, C, WB>(mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm, stride, KT, sms, st)
 #define NA1D_TC_BWD_W(E, C)                          \
-    if (gm.win <= 9) { NA1D_TC_BWD(E, C, 9); }       \
-    else if (gm.win <= 17) { NA1D_TC_BWD(E, C, 17); } \
+    if (weff <= 9) { NA1D_TC_BWD(E, C, 9); }       \
+    else if (weff <= 17) { NA1D_TC_BWD(E, C, 17); } \
     else { NA1D_TC_BWD(E, C, 33); }
 #define NA1D_TC_BWD_C(E)                         \
     if (gm.C == 64) { NA1D_TC_BWD_W(E, 64) }     \

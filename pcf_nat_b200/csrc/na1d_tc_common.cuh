@@ -30,6 +30,11 @@ __host__ __device__ constexpr int round_up(int x, int m) { return (x + m - 1) / 
 // column groups of 8 that can hold band entries of a 16-row block
 __host__ __device__ constexpr int band_groups(int win_max) { return (15 + win_max + 7) / 8; }
 
+// Dilation d (a power of two) is handled as a window of (win-1) d + 1 consecutive keys of which every d-th is a neighbour:
+// tiles, halos and masks use the effective window, the band test adds `offset % d == 0`.
+__host__ __device__ constexpr int eff_window(int win, int dil) { return (win - 1) * dil + 1; }
+__host__ __device__ constexpr bool pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
+
 // ---- tcgen05.ld 16x256b: x1 = 4 registers per thread: (row l/4: cols 2(l%4), +1), (row l/4+8: same cols)
 __device__ __forceinline__ void ld_frag1(uint32_t taddr, float* f) {
     uint32_t r[4];

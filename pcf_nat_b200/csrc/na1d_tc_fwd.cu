@@ -93,7 +93,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int rows_total = gm.N * gm.T;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int win = gm.win, left = gm.left, T = gm.T;
+    // effective (dilated) window: neighbour kk of the reference is offset kk * dil of it
+    const int dil = gm.dil, dmask = dil - 1, dshift = 31 - __clz(dil);
+    const int win = tc::eff_window(gm.win, dil), left = gm.left * dil, T = gm.T;
     const int stage_tx = (kTileM + 2 * KT) * kRowBytes;
 
     if (tid == 0) {
@@ -228,7 +230,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             // bias table of every head, once per CTA (barrier among the 4 softmax warps only)
             for (int i = r; i < gm.H * kBiasRow; i += 128) {
                 const int hh_ = i / kBiasRow, kk = i - hh_ * kBiasRow - kBiasPad;
-                bias_tab[i] = (kk >= 0 && kk < win) ? __ldg(rpb + hh_ * win + kk) * kLog2e : 0.f;
+                bias_tab[i] = (kk >= 0 && kk < win && (kk & dmask) == 0) ? __ldg(rpb + hh_ * gm.win + (kk >> dshift)) * kLog2e : 0.f;
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
@@ -287,7 +289,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                             for (int e = 0; e < 2; ++e) {
                                 const int idx = 4 * g + 2 * hh + e;
                                 const int kc = 8 * (g - hh) + e, kk = kc + fa;
-                                const bool inband = (unsigned)kk < (unsigned)win;
+                                const bool inband = (unsigned)kk < (unsigned)win && (kk & dmask) == 0;
                                 float bias = 0.f;
                                 if (rpb) bias = brow[b][hh][kk];
                                 float dot = s[b][idx];
@@ -448,13 +450,14 @@ extern "C" int na1d_debug_fwd_timeline(long long* out) {
 #endif
 
 bool tc_fwd_supports(const Geometry& gm) {
-    return gm.dil == 1 && (gm.C == 64 || gm.C == 32 || gm.C == 16) && gm.win <= 33 && gm.H <= 32 && gm.T >= 32 && gm.T < (1 << 21);
+    return tc::pow2(gm.dil) && (gm.C == 64 || gm.C == 32 || gm.C == 16) && tc::eff_window(gm.win, gm.dil) <= 33 && gm.H <= 32 && gm.T >= 32 && gm.T < (1 << 21);
 }
 
 cudaError_t tc_fused_fwd(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
                          const int* valid_len, const Geometry& gm, int dtype, cudaStream_t st) {
     if (!tc_fwd_supports(gm)) return cudaErrorInvalidValue;
-    const int KT = round_up(kTileM + gm.win - 1, 16);
+    const int weff = tc::eff_window(gm.win, gm.dil);
+    const int KT = round_up(kTileM + weff - 1, 16);
     const int rows = gm.N * gm.T;  // the tensors are tiled as one (N*T, C) matrix
     CUtensorMap mq, mk, mv, mo;
     if (!make_row_tile_map(&mq, q, dtype, 1, rows, gm.C, kTileM) || !make_row_tile_map(&mk, k, dtype, 1, rows, gm.C, KT) ||
@@ -463,8 +466,8 @@ cudaError_t tc_fused_fwd(void* o, float* lse, const void* q, const void* k, cons
     const int sms = device_sm_count();
 #define NA1D_TC_FWD(E, C, WB) return launch_fwd<E, C, WB>(mq, mk, mv, mo, lse, rpb, valid_len, gm, KT, sms, st)
 #define NA1D_TC_FWD_W(E, C)                          \
-    if (gm.win <= 9) { NA1D_TC_FWD(E, C, 9); }       \
-    else if (gm.win <= 17) { NA1D_TC_FWD(E, C, 17); } \
+    if (weff <= 9) { NA1D_TC_FWD(E, C, 9); }       \
+    else if (weff <= 17) { NA1D_TC_FWD(E, C, 17); } \
     else { NA1D_TC_FWD(E, C, 33); }
 #define NA1D_TC_FWD_C(E)                         \
     if (gm.C == 64) { NA1D_TC_FWD_W(E, 64) }     \

@@ -253,6 +253,10 @@ TC_SHAPES = [(N, H, T, C, win, left) for (N, H, T) in ((3, 1, 200), (2, 1, 128),
                                                         (2, 1, 383), (12, 4, 50), (6, 3, 150), (8, 2, 33))
              for (C, win, left) in ((64, 7, 3), (32, 7, 3), (16, 27, 13), (64, 15, 7), (64, 31, 15), (32, 33, 0),
                                     (16, 3, 2), (64, 8, 3), (32, 17, 16), (64, 9, 4), (16, 18, 9))]
+# dilated windows (power-of-two dilation, (win - 1) * dil + 1 <= 33)
+TC_SHAPES_DIL = [(N, H, T, C, win, left, dil) for (N, H, T) in ((3, 1, 200), (12, 4, 50), (2, 2, 129))
+                 for (C, win, left, dil) in ((64, 7, 3, 2), (32, 7, 3, 4), (16, 15, 7, 2), (64, 3, 1, 8), (64, 9, 4, 4),
+                                             (32, 5, 0, 8), (64, 3, 2, 16))]
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["bf16", "fp16"])
@@ -261,33 +265,37 @@ def test_tcgen05_forward_backward_shapes(dtype):
     fam = ops.FAMILY_TCGEN05
     old = ops.set_kernel_family(fam)
     try:
-        for idx, (N, H, T, C, win, left) in enumerate(TC_SHAPES):
-            assert ops.kernel_family(N, T, C, win, left, 1, dtype) == fam, "tcgen05 family should take this shape"
+        for idx, shape in enumerate([t + (1,) for t in TC_SHAPES] + TC_SHAPES_DIL):
+            N, H, T, C, win, left, dil = shape
+            assert ops.kernel_family(N, T, C, win, left, dil, dtype) == fam, "tcgen05 family should take this shape"
             sc = C ** -0.5
             q, k, v = (randn16((N, T, C), dtype, 500 + 3 * idx + i) for i in range(3))
             rpb = 0.3 * torch.randn(H, win, generator=torch.Generator().manual_seed(idx))
             vl = [T] + [max(1, T - 5)] * (N // H - 1)
-            o, lse = ops.fused_forward(q.cuda(), k.cuda(), v.cuda(), win, left, 1, sc, rpb.cuda(), vl, H)
+            o, lse = ops.fused_forward(q.cuda(), k.cuda(), v.cuda(), win, left, dil, sc, rpb.cuda(), vl, H)
             ops.device_status()
-            o_r, lse_r = orc.na1d_fused(q.float(), k.float(), v.float(), win, left, 1, sc, rpb, vl, H, return_lse=True)
-            tag = "N=%d H=%d T=%d C=%d win=%d left=%d " % (N, H, T, C, win, left)
+            o_r, lse_r = orc.na1d_fused(q.float(), k.float(), v.float(), win, left, dil, sc, rpb, vl, H, return_lse=True)
+            tag = "N=%d H=%d T=%d C=%d win=%d left=%d dil=%d " % (N, H, T, C, win, left, dil)
             assert_close(o, o_r, dtype, tag + "o")
             assert float((lse.cpu() - lse_r).abs().max()) < 1e-3 * max(1.0, float(lse_r.abs().max())), tag + "lse"
             # backward through the tcgen05 family as well
-            assert ops.kernel_family(N, T, C, win, left, 1, dtype, backward=True) == fam
+            assert ops.kernel_family(N, T, C, win, left, dil, dtype, backward=True) == fam
             d_o = randn16((N, T, C), dtype, 900 + idx)
-            dq, dk, dv, drpb = ops.fused_backward(d_o.cuda(), q.cuda(), k.cuda(), v.cuda(), o, lse, win, left, 1, sc,
+            dq, dk, dv, drpb = ops.fused_backward(d_o.cuda(), q.cuda(), k.cuda(), v.cuda(), o, lse, win, left, dil, sc,
                                                   rpb.cuda(), vl, H, need_d_rpb=True)
             ops.device_status()
             _, dq_r, dk_r, dv_r, drpb_r = orc.na1d_fused_with_grads(q.float(), k.float(), v.float(), d_o.float(), win,
-                                                                    left, 1, sc, rpb, vl, H)
+                                                                    left, dil, sc, rpb, vl, H)
             assert_close(dq, dq_r, dtype, tag + "dq")
             assert_close(dk, dk_r, dtype, tag + "dk")
             assert_close(dv, dv_r, dtype, tag + "dv")
             assert_close(drpb, drpb_r, dtype, tag + "drpb", factor=2.0)
         # shapes outside the family are refused when it is forced, and taken by the CUDA-core kernels otherwise
-        assert ops.kernel_family(2, 64, 64, 7, 3, 2, dtype) == -10
+        assert ops.kernel_family(2, 64, 64, 7, 3, 3, dtype) == -10    # dilation not a power of two
+        assert ops.kernel_family(2, 64, 64, 15, 7, 4, dtype) == -10   # dilated window wider than 33
         assert ops.kernel_family(2, 64, 24, 7, 3, 1, dtype) == -10
+        assert ops.kernel_family(2, 16, 64, 7, 3, 1, dtype) == -10    # sequences shorter than 32 tokens
     finally:
         ops.set_kernel_family(old)
-    assert ops.kernel_family(2, 64, 64, 7, 3, 2, dtype) == 0
+    assert ops.kernel_family(2, 64, 64, 7, 3, 3, dtype) == 0
+    assert ops.kernel_family(2, 16, 64, 7, 3, 1, dtype) == 0
