@@ -1,0 +1,146 @@
+"""The neighbourhood-attention layer as a packaged module on the fused operator.
+
+``NAttention`` has the constructor, parameter names and state-dict layout of the reference's two layer classes
+
+* ``models/PCF_NATransformer.py:44-178``  -- input ``(N, C, T)``, 1x1 ``Conv1d`` projections with ``groups``
+  (``layout="channels_first"``),
+* ``models/MFA_NATransformer.py:44-177``  -- input ``(N, T, C)``, ``Linear`` projections (``layout="channels_last"``),
+
+so a checkpoint of either loads unchanged (keys ``qkv.*``, ``proj.*``, ``relative_position_bias``, ``attn_mask``).
+Between the two projections the reference runs ``q*scale -> QK -> +rpb -> +mask -> softmax -> dropout -> AV`` as seven or
+more kernels with an fp32 ``(N*heads, T, win)`` tensor in HBM (PCF_NATransformer.py:141-150); here that is one call of
+``na1d_fused`` and the padding mask is computed inside the kernel from ``valid_len = T - padding``.
+
+``fuse_nattention(model)`` rebinds ``forward`` of the reference's own layer objects inside an already built model to the
+same fused path, for hosts that construct the unmodified reference model classes.
+"""
+import types
+
+import torch
+import torch.nn as nn
+
+from .library_op import na1d_fused
+
+
+def _window(win_size):
+    """(win, left) from the reference's ``win_size`` argument: an int (``left = win-1-win//2``, so an even window has its
+    extra key on the right) or ``[win, left]`` (PCF_NATransformer.py:47-54)."""
+    if isinstance(win_size, int):
+        if win_size <= 0:
+            raise ValueError("win_size must be positive")
+        return win_size, win_size - 1 - win_size // 2
+    if isinstance(win_size, (list, tuple)) and len(win_size) == 2:
+        win, left = int(win_size[0]), int(win_size[1])
+        if not (0 <= left < win):
+            raise ValueError("left must satisfy 0 <= left < win_size")
+        return win, left
+    raise ValueError("win_size must be an int or [win_size, left]")
+
+
+def padding_mask(T, win, left, dilation=1, padding=None, dtype=torch.float32, device="cpu"):
+    """The reference's additive mask (PCF_NATransformer.py:87-116): 0 where query t and key t+(kk-left)*dilation are both
+    real frames of the utterance, -100 elsewhere; shape ``(N, 1, T, win)``. Only kept for state-dict compatibility
+    (buffer ``attn_mask``) and for tests: the fused kernels derive the same mask from ``valid_len``."""
+    if padding is None:
+        padding = torch.zeros(1, dtype=torch.int, device=device)
+    valid = (T - padding.to(torch.int64)).view(-1, 1, 1)                                   # (N,1,1)
+    t = torch.arange(T, device=padding.device).view(1, T, 1)
+    j = t + (torch.arange(win, device=padding.device).view(1, 1, win) - left) * dilation
+    bad = (t >= valid) | (j < 0) | (j >= valid)
+    mask = torch.zeros(bad.shape, dtype=dtype, device=padding.device).masked_fill(bad, -100.0)
+    return mask.unsqueeze(1)
+
+
+def _split_heads(x, layout, num_heads, groups):
+    """Projection output -> q, k, v as ``(N*heads, T, head_dim)`` (the copies of PCF_NATransformer.py:126-138 and
+    MFA_NATransformer.py:127-137)."""
+    if layout == "channels_first":
+        N, C3, T = x.shape
+        C = C3 // 3
+        hd = C // num_heads
+        x = x.view(N, C // groups, groups, 3, T).transpose(1, 2).contiguous().view(N, num_heads, hd, 3, T)
+        x = x.permute(3, 0, 1, 4, 2).contiguous().view(3, N * num_heads, T, hd)
+    else:
+        N, T, C3 = x.shape
+        C = C3 // 3
+        hd = C // num_heads
+        x = x.view(N, T, 3, num_heads, hd).permute(2, 0, 3, 1, 4).contiguous().view(3, N * num_heads, T, hd)
+    return x[0], x[1], x[2]
+
+
+def _merge_heads(o, layout, N, num_heads):
+    NH, T, hd = o.shape
+    o = o.view(N, num_heads, T, hd)
+    if layout == "channels_first":
+        return o.transpose(2, 3).contiguous().view(N, num_heads * hd, T)
+    return o.transpose(1, 2).contiguous().view(N, T, num_heads * hd)
+
+
+def _fused_forward(self, x, padding=None):
+    layout = self._na1d_layout
+    if layout == "channels_first":
+        N, C, T = x.shape
+    else:
+        N, T, C = x.shape
+    if float(self.attn_drop.p) != 0.0 and self.training:
+        raise NotImplementedError("attention dropout > 0 is not fused (the reference's configs use 0)")
+    q, k, v = _split_heads(self.qkv(x), layout, self.num_heads, getattr(self, "groups", 1))
+    valid_len = None
+    if not self.training and padding is not None:
+        # eval: the mask follows the utterance's padding (PCF_NATransformer.py:131-134); training uses the constant mask
+        valid_len = (T - padding.to(torch.int64)).clamp_(0, T).to(torch.int32).expand(N).contiguous()
+    o = na1d_fused(q, k, v, self.win_size, self.left, self.dilation, float(self.scale), self.relative_position_bias,
+                   valid_len, self.num_heads)
+    return self.proj_drop(self.proj(_merge_heads(o, layout, N, self.num_heads)))
+
+
+class NAttention(nn.Module):
+    """Drop-in for the reference's ``NAttention`` (same arguments; ``layout`` picks the PCF or the MFA variant)."""
+
+    def __init__(self, frames, dim, num_heads, win_size, dilation=1, groups=1, proj_bias=True, qkv_bias=True, qk_scale=None,
+                 attn_drop=0., proj_drop=0., dtype=torch.float32, layout="channels_first"):
+        super().__init__()
+        if layout not in ("channels_first", "channels_last"):
+            raise ValueError("layout must be 'channels_first' (PCF) or 'channels_last' (MFA)")
+        self.win_size, self.left = _window(win_size)
+        if self.win_size > 80:
+            raise ValueError("win_size <= 80 (PCF_NATransformer.py:53)")
+        head_dim = dim // num_heads
+        if dim % num_heads or head_dim % 8:
+            raise ValueError("dim must split into heads of a multiple of 8 channels")
+        self.dim, self.dilation, self.groups, self.num_heads = dim, dilation, groups, num_heads
+        self.scale = qk_scale or head_dim ** -0.5
+        self._na1d_layout = layout
+        if layout == "channels_first":
+            self.qkv = nn.Conv1d(dim, dim * 3, kernel_size=1, bias=qkv_bias, groups=groups)
+            self.proj = nn.Conv1d(dim, dim, kernel_size=1, bias=proj_bias, groups=groups)
+        else:
+            if groups != 1:
+                raise ValueError("groups is a channels_first (PCF) option")
+            self.qkv = nn.Linear(dim, dim * 3, bias=qkv_bias)
+            self.proj = nn.Linear(dim, dim, bias=proj_bias)
+        self.relative_position_bias = nn.Parameter(torch.zeros((1, num_heads, 1, self.win_size)))
+        nn.init.normal_(self.relative_position_bias, mean=0., std=.02)
+        self.attn_drop = nn.Dropout(attn_drop)
+        self.proj_drop = nn.Dropout(proj_drop)
+        self.register_buffer("attn_mask", padding_mask(frames, self.win_size, self.left, dilation))
+
+    forward = _fused_forward
+
+
+def fuse_nattention(model, layout=None):
+    """Rebind ``forward`` of every reference-style attention layer inside ``model`` to the fused path.
+
+    A layer qualifies when it has ``qkv``, ``proj``, ``relative_position_bias``, ``win_size``, ``left``, ``num_heads`` and
+    ``attn_drop``; its layout is taken from the type of ``qkv`` (``Conv1d`` -> channels_first) unless given.
+    Returns the number of layers rebound."""
+    n = 0
+    for m in model.modules():
+        if isinstance(m, NAttention):
+            continue
+        if all(hasattr(m, a) for a in ("qkv", "proj", "relative_position_bias", "win_size", "left", "num_heads", "attn_drop",
+                                       "proj_drop", "scale", "dilation")):
+            m._na1d_layout = layout or ("channels_first" if isinstance(m.qkv, nn.Conv1d) else "channels_last")
+            m.forward = types.MethodType(_fused_forward, m)
+            n += 1
+    return n

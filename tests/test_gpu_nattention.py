@@ -1,0 +1,98 @@
+"""The packaged NAttention layer on the GPU against whole-layer outputs of the reference (tests/golden/module_*.npz)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+from make_golden_module import MODULE_CASES  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(ROOT, "tests", "golden")
+# a whole layer in 16-bit arithmetic (two projections around the operator): looser than the operator's own bound
+TOL = {torch.bfloat16: 4e-2, torch.float16: 8e-3}
+
+
+def _layer(name, dtype):
+    from pcf_nat_b200 import NAttention
+    model, N, T, dim, heads, win_size, dil, groups, padding = MODULE_CASES[name]
+    g = np.load(os.path.join(GOLD, name + ".npz"))
+    m = NAttention(frames=T, dim=dim, num_heads=heads, win_size=win_size, dilation=dil, groups=groups,
+                   layout="channels_first" if model == "pcf" else "channels_last")
+    m.load_state_dict({k[3:]: torch.from_numpy(g[k]) for k in g.files if k.startswith("sd_")})
+    return m.cuda().to(dtype), g
+
+
+def _close(got, ref, dtype, what):
+    ref = torch.from_numpy(ref)
+    err = float((got.detach().float().cpu() - ref).abs().max())
+    bound = TOL[dtype] * max(1.0, float(ref.abs().max()))
+    assert err <= bound, "%s: max-abs error %.4g > %.4g" % (what, err, bound)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("name", list(MODULE_CASES))
+def test_layer_matches_reference(name, dtype):
+    m, g = _layer(name, dtype)
+    x = torch.from_numpy(g["x"]).cuda().to(dtype)
+    pad = torch.from_numpy(g["padding"]).cuda()
+    m.eval()
+    xe = x.clone().requires_grad_(True)
+    y = m(xe, pad)
+    _close(y, g["y_eval"], dtype, name + " y_eval")
+    y.backward(torch.from_numpy(g["gy"]).cuda().to(dtype))
+    _close(xe.grad, g["dx_eval"], dtype, name + " dx")
+    _close(m.relative_position_bias.grad, g["drpb_eval"], dtype, name + " d_rpb")
+    m.train()
+    _close(m(x, None), g["y_train"], dtype, name + " y_train")
+
+
+def test_fused_layer_on_foreign_module():
+    """fuse_nattention() on an object that only has the reference layer's attributes gives the packaged layer's output."""
+    import torch.nn as nn
+    from pcf_nat_b200 import NAttention, fuse_nattention
+    mine, g = _layer("module_pcf_w7", torch.bfloat16)
+
+    class Foreign(nn.Module):
+        def __init__(self, src):
+            super().__init__()
+            self.qkv, self.proj, self.relative_position_bias = src.qkv, src.proj, src.relative_position_bias
+            self.win_size, self.left, self.num_heads, self.scale = src.win_size, src.left, src.num_heads, src.scale
+            self.dilation, self.groups, self.attn_drop, self.proj_drop = src.dilation, src.groups, src.attn_drop, src.proj_drop
+
+        def forward(self, x, padding=None):
+            raise AssertionError("not fused")
+
+    other = Foreign(mine).eval()
+    assert fuse_nattention(other) == 1
+    x = torch.from_numpy(g["x"]).cuda().to(torch.bfloat16)
+    pad = torch.from_numpy(g["padding"]).cuda()
+    mine.eval()
+    assert torch.equal(other(x, pad), mine(x, pad))
+
+
+def test_library_op_opcheck_and_compile():
+    """The torch.library registration is consistent (schema, fake kernel, autograd) and traces without a graph break."""
+    import pcf_nat_b200
+    g = torch.Generator().manual_seed(5)
+    q, k, v = ((torch.randn(8, 96, 32, generator=g) * 0.5).to(torch.bfloat16).cuda().requires_grad_(True) for _ in range(3))
+    rpb = (0.2 * torch.randn(1, 4, 1, 7, generator=g)).cuda().requires_grad_(True)
+    vl = torch.tensor([96, 80], dtype=torch.int32).cuda()
+    torch.library.opcheck(torch.ops.pcf_nat_b200.na1d_fused_fwd.default, (q, k, v, rpb, vl, 7, 3, 1, 0.17, 4),
+                          test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
+
+    def layer(q, k, v, rpb):
+        return pcf_nat_b200.na1d_fused(q * 1.0, k, v, 7, 3, 1, 0.17, rpb, vl, 4).float().square().sum()
+
+    eager = layer(q, k, v, rpb)
+    ge = torch.autograd.grad(eager, (q, k, v, rpb))
+    compiled = torch.compile(layer, backend="aot_eager", fullgraph=True)
+    out = compiled(q, k, v, rpb)
+    gc = torch.autograd.grad(out, (q, k, v, rpb))
+    assert torch.equal(out, eager)
+    for a, b in zip(ge, gc):
+        assert torch.allclose(a.float(), b.float(), rtol=0, atol=1e-6 * max(1.0, float(a.float().abs().max())))
