@@ -102,8 +102,10 @@ int na1d_fused_forward(void* o, float* lse, const void* q, const void* k, const 
                        void* stream);
 
 /* Gradients of na1d_fused_forward. dq,dk,dv: (N,T,C) 16-bit. d_rpb: (heads,win) fp32, ACCUMULATED
- * into (caller zeroes it), or NULL. delta_ws: caller-provided scratch of N*T fp32 (row sums of
- * d_o*o, written by a pre-pass and read by the main kernel).
+ * into (caller zeroes it), or NULL. delta_ws: caller-provided scratch of N*T fp32. The CUDA-core
+ * kernels keep the row sums of d_o*o there (written by a pre-pass, read by the main kernel); the
+ * tcgen05 kernels need no such pre-pass and use it only for one partial row of d_rpb per CTA, summed
+ * by a second small kernel (when it is too small for that they add to d_rpb with atomics).
  * Replaces the autograd chain AV.backward -> softmax backward -> QK.backward,
  * na1d_tensorcore/nattn.py:46-54 and :69-78. */
 int na1d_fused_backward(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q,

@@ -152,8 +152,10 @@ int na1d_fused_backward(void* dq, void* dk, void* dv, float* d_rpb, const void* 
     cudaStream_t st = (cudaStream_t)stream;
     const int fam = pick_family(g, 1);
     if (fam < 0) return fam;
-    if (fam == 1)  // delta is recomputed inside the kernel from P and dP: neither o nor delta_ws is touched
-        return cuda_status(na1d::tc_fused_bwd(dq, dk, dv, d_rpb, d_o, q, k, v, lse, rpb, valid_len, g, dtype, st));
+    if (fam == 1)  // delta is recomputed inside the kernel from P and dP: o is not read; delta_ws (N*T floats) only holds the
+                   // per-CTA partial sums of the bias gradient
+        return cuda_status(na1d::tc_fused_bwd(dq, dk, dv, d_rpb, d_o, q, k, v, lse, rpb, valid_len, delta_ws,
+                                              (size_t)g.N * (size_t)g.T, g, dtype, st));
     if (int s = cuda_status(na1d::simt_delta(delta_ws, d_o, o, g.N * g.T, g.C, dtype, st))) return s;
     return cuda_status(na1d::simt_fused_bwd(dq, dk, dv, d_rpb, d_o, q, k, v, lse, delta_ws, rpb, valid_len, g, dtype, st));
 }

@@ -25,7 +25,7 @@ int tc_read_status();
 int tc_bwd_read_status();
 bool tc_bwd_supports(const Geometry& gm);
 cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
-                         const void* v, const float* lse, const float* rpb, const int* valid_len, const Geometry& gm, int dtype,
-                         cudaStream_t st);
+                         const void* v, const float* lse, const float* rpb, const int* valid_len, float* scratch,
+                         size_t scratch_floats, const Geometry& gm, int dtype, cudaStream_t st);
 
 }  // namespace na1d

@@ -66,7 +66,7 @@ struct BwdSmemLayout {
     bool own_out;  // a dedicated 128-row staging buffer for the outputs fits next to everything else
 };
 constexpr int kBiasRowB = 16 + 48;  // per-head table: log2e * rpb[h][kk] at index kk + 16, kk in [-16, 48)
-__host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT, int bias_heads) {
+__host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT, int bias_heads, int acc_floats) {
     BwdSmemLayout L;
     L.stage_q = 0;
     L.stage_do = L.stage_q + round_up(kTileM * C * 2, 1024);
@@ -76,7 +76,8 @@ __host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT, int bias_head
     L.ds = 2 * L.stage_bytes;           // dS [128 queries][KT keys]
     L.p = L.ds + kTileM * KT * 2;       // P  [128 queries][KT keys]
     L.out = L.p + kTileM * KT * 2;
-    const int tail = 512 + round_up(bias_heads * kBiasRowB * 4, 256) + 1008;  // misc block, bias table, alignment slack
+    // misc block, bias table, bias-gradient accumulator, alignment slack
+    const int tail = 512 + round_up(bias_heads * kBiasRowB * 4, 256) + round_up(acc_floats * 4, 256) + 1008;
     L.own_out = L.out + round_up(kTileM * C * 2, 1024) + tail <= 227 * 1024;
     L.misc = L.out + (L.own_out ? round_up(kTileM * C * 2, 1024) : 0);
     L.total = L.misc + tail;
@@ -97,6 +98,7 @@ struct alignas(8) BwdMisc {
     uint64_t full[2][4], empty[2][4];
     uint64_t s_ready, s_free, p_ready, o_ready;
     uint64_t o_free[3];  // per accumulator (dQ, dV, dK): its MMA chain restarts as soon as the epilogue has drained it
+    uint64_t acc_done;   // all compute threads have added their last tile to the bias-gradient accumulator
     uint32_t tmem_base;
     int abort;
 };
@@ -106,18 +108,24 @@ __global__ void __launch_bounds__(kThreads, 1)
 tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk,
-              const __grid_constant__ CUtensorMap tm_dv, float* __restrict__ d_rpb, const float* __restrict__ lse,
+              const __grid_constant__ CUtensorMap tm_dv, float* __restrict__ d_rpb, int drpb_direct,
+              const float* __restrict__ lse,
               const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, int stride, int KT,
               int total_tiles) {
     constexpr int NG = tc::band_groups(WB);  // 8-column groups holding the band of a 16-row block
     constexpr int kRowBytes = C * 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const BwdSmemLayout L = bwd_layout(C, KT, rpb ? gm.H : 0);
+    const int n_bias = gm.H * gm.win;  // entries of the bias gradient
+    const BwdSmemLayout L = bwd_layout(C, KT, rpb ? gm.H : 0, d_rpb ? n_bias : 0);
     uint8_t* sDS = smem + L.ds;
     uint8_t* sP = smem + L.p;
     BwdMisc* misc = reinterpret_cast<BwdMisc*>(smem + L.misc);
     float* bias_tab = reinterpret_cast<float*>(smem + L.misc + 512);
+    // per-CTA accumulator of the bias gradient: global atomics on the (H, win) array -- one cache line for the usual sizes --
+    // serialise (5x the whole kernel's time when every tile issued them), so each CTA adds up its tiles here and hands over
+    // one row of partial sums at its end
+    float* bias_acc = bias_tab + round_up((rpb ? gm.H : 0) * kBiasRowB, 64);
     const int rows_total = gm.N * gm.T;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -134,6 +142,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ptx::mbar_init(&misc->p_ready, 128);
         ptx::mbar_init(&misc->o_ready, 3);   // dQ, dV, dK chains
         for (int i = 0; i < 3; ++i) ptx::mbar_init(&misc->o_free[i], 128);
+        ptx::mbar_init(&misc->acc_done, 128);
         misc->abort = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tm_q);
@@ -284,14 +293,16 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const float mask2 = kMaskValue * kLog2e;
         const float inv_T = 1.f / (float)T, inv_H = 1.f / (float)gm.H;
         const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
+        if (d_rpb)
+            for (int i = r; i < n_bias; i += 128) bias_acc[i] = 0.f;
         if (rpb) {
             // bias table of every head, once per CTA (barrier among the 4 compute warps only)
             for (int i = r; i < gm.H * kBiasRowB; i += 128) {
                 const int hh_ = i / kBiasRowB, kk = i - hh_ * kBiasRowB - kBiasPad;
                 bias_tab[i] = (kk >= 0 && kk < win && (kk & dmask) == 0) ? __ldg(rpb + hh_ * gm.win + (kk >> dshift)) * kLog2e : 0.f;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
         }
+        if (rpb || d_rpb) asm volatile("bar.sync 1, 128;" ::: "memory");
         int it = 0;
         // log-sum-exp of the four fragment rows of a tile; loaded one tile ahead so the DRAM latency is hidden
         auto load_lse = [&](int tile_, float (&dst)[2][2]) {
@@ -414,7 +425,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                             const bool own = d_rpb && row >= right && row < kTileM - left;
                             const bool out0 = (unsigned)j0 >= (unsigned)T, out1 = (unsigned)(j0 + 1) >= (unsigned)T;
                             if (out0 | out1) {
-                                if (own) bias_grad_outside(d_rpb + hrow[b][hh] * gm.win, kk0, dshift, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
+                                if (own) bias_grad_outside(bias_acc + hrow[b][hh] * gm.win, kk0, dshift, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
                                 if (out0) { ds0 = 0.f; p0 = 0.f; }
                                 if (out1) { ds1 = 0.f; p1 = 0.f; }
                             }
@@ -434,39 +445,60 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             load_lse(tile + gridDim.x, lse_next);
             if (tid == 0) NA1D_STAMP(5);
             if (d_rpb) {
-                // d_rpb[h][kk] += dS over the query rows this tile owns: thread r reads the band of row r back
-                // from the dS operand (16-bit, scaled), the warp reduces, one atomic per warp and neighbour
+                // bias gradient: column sums of dS over the query rows this tile owns. Lane r reads the band of row r back from
+                // the dS operand (16-bit, scaled); a butterfly leaves the sum of window offset i on lane i * (32 / NV), which
+                // adds it to the CTA's accumulator. Rows of different heads (a warp spans at most two sequences) take one pass
+                // per head.
+                constexpr int NV = WB - 1;  // 8, 16 or 32 offsets through the butterfly; offset NV (full bucket) separately
                 __syncwarp();
                 const int gr = g0 + r;
                 const bool own = r >= right && r < kTileM - left && gr >= 0 && gr < rows_total;
-                int hr = 0;
+                int hr = -1;
                 if (own) {
                     int tr, br;
                     cur.row_at(r - right, inv_T, inv_H, tr, hr, br);
                 }
-                const int h_hi = __reduce_max_sync(0xffffffffu, own ? hr : -1);
-                const int h0 = __reduce_min_sync(0xffffffffu, own ? hr : 0x7fffffff);
-                const bool one_head = h_hi == h0;  // all owned rows of the warp belong to sequences of one head
+                const int h_hi = __reduce_max_sync(0xffffffffu, hr);
+                int hsel = __reduce_min_sync(0xffffffffu, own ? hr : 0x7fffffff);
                 const float inv_scale = 1.f / gm.scale;
                 const uint8_t* row = sDS + (r >> 3) * lboq + (r & 7) * 16;
-#pragma unroll 1
-                for (int kk = 0; kk < gm.win; ++kk) {
-                    {
-                        const int col = r + kk * dil;
-                        float x = own ? (float)*reinterpret_cast<const E*>(row + (col >> 3) * 128 + (col & 7) * 2) * inv_scale : 0.f;
-                        if (h_hi < 0) {
-                            // no owned row in this warp
-                        } else if (one_head) {
+                while (h_hi >= 0) {
+                    const bool mine = own && hr == hsel;
+                    float x[NV];
 #pragma unroll
-                            for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
-                            if (lane == 0 && x != 0.f) atomicAdd(d_rpb + h0 * gm.win + kk, x);
-                        } else if (x != 0.f) {
-                            atomicAdd(d_rpb + hr * gm.win + kk, x);  // the warp's rows belong to sequences of different heads
-                        }
+                    for (int i = 0; i < NV; ++i) {
+                        const int col = r + i;
+                        x[i] = (mine && i < win) ? (float)*reinterpret_cast<const E*>(row + (col >> 3) * 128 + (col & 7) * 2) : 0.f;
                     }
+                    float last = 0.f;  // offset NV exists only when the window fills its bucket
+                    if (win > NV) {
+                        const int col = r + NV;
+                        last = mine ? (float)*reinterpret_cast<const E*>(row + (col >> 3) * 128 + (col & 7) * 2) : 0.f;
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) last += __shfl_xor_sync(0xffffffffu, last, o);
+                    }
+                    const float v = tc::column_sums<NV>(x, lane);
+                    const int off = lane / (32 / NV);
+                    float* acc_row = bias_acc + hsel * gm.win;
+                    if (lane % (32 / NV) == 0 && off < win && (off & dmask) == 0 && v != 0.f) atomicAdd(acc_row + (off >> dshift), v * inv_scale);
+                    if (lane == 1 && win > NV && last != 0.f) atomicAdd(acc_row + (NV >> dshift), last * inv_scale);
+                    if (hsel == h_hi) break;
+                    hsel = __reduce_min_sync(0xffffffffu, (own && hr > hsel) ? hr : 0x7fffffff);
                 }
             }
-
+        }
+        if (d_rpb) {
+            // hand over this CTA's partial bias gradient: every compute thread arrives (also after an aborted loop), warp 0
+            // waits for all of them and writes row blockIdx.x of the partial-sum matrix (or adds to the result directly when
+            // the caller's scratch was too small for one row per CTA)
+            ptx::mbar_arrive(&misc->acc_done);
+            if (warp == 0 && ptx::mbar_wait(&misc->acc_done, 0)) {
+                for (int i = lane; i < n_bias; i += 32) {
+                    const float x = bias_acc[i];
+                    if (drpb_direct) { if (x != 0.f) atomicAdd(d_rpb + i, x); }
+                    else d_rpb[(size_t)blockIdx.x * n_bias + i] = x;
+                }
+            }
         }
     } else if (warp < 8) {
         // ------------------------------------------------------------ epilogue warps (TMEM lanes 32(warp-4)..)
@@ -573,11 +605,22 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
 }
 
+// d_rpb[i] += sum over the CTAs' partial rows (column i of a (rows, n) matrix): one thread per entry, coalesced rows.
+__global__ void bias_grad_reduce_kernel(float* __restrict__ d_rpb, const float* __restrict__ partial, int rows, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float acc = 0.f;
+    for (int r = 0; r < rows; ++r) acc += partial[(size_t)r * n + i];
+    d_rpb[i] += acc;
+}
+
 template <typename E, int C, int WB>
 cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUtensorMap& mk, const CUtensorMap& mv,
-                       const CUtensorMap& mdq, const CUtensorMap& mdk, const CUtensorMap& mdv, float* d_rpb, const float* lse, const float* rpb, const int* valid_len,
-                       const Geometry& gm, int stride, int KT, int sm_count, cudaStream_t st) {
-    const BwdSmemLayout L = bwd_layout(C, KT, rpb ? gm.H : 0);
+                       const CUtensorMap& mdq, const CUtensorMap& mdk, const CUtensorMap& mdv, float* d_rpb, float* scratch, size_t scratch_floats,
+                       const float* lse, const float* rpb, const int* valid_len, const Geometry& gm, int stride, int KT, int sm_count,
+                       cudaStream_t st) {
+    const int n_bias = gm.H * gm.win;
+    const BwdSmemLayout L = bwd_layout(C, KT, rpb ? gm.H : 0, d_rpb ? n_bias : 0);
     const int smem = L.total;
     // only 64-channel rows can be too large for the dedicated output staging buffer
     if constexpr (C != 64) {
@@ -598,8 +641,15 @@ cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUte
     attr[0].val.programmaticStreamSerializationAllowed = (pdl_mode() == 1 || pdl_mode() == 3) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm,
-                                       stride, KT, total);
+    // bias gradient: one partial row per CTA in the caller's scratch, summed by a second tiny kernel; if the scratch cannot
+    // hold grid rows the CTAs add their row to the result with atomics instead
+    const bool partial_rows = d_rpb && scratch && scratch_floats >= (size_t)grid * n_bias;
+    float* bias_out = !d_rpb ? nullptr : partial_rows ? scratch : d_rpb;
+    e = cudaLaunchKernelEx(&cfg, kern, mq, mdo, mk, mv, mdq, mdk, mdv, bias_out, partial_rows ? 0 : 1, lse, rpb, valid_len, gm,
+                           stride, KT, total);
+    if (e != cudaSuccess || !partial_rows) return e;
+    bias_grad_reduce_kernel<<<(n_bias + 127) / 128, 128, 0, st>>>(d_rpb, scratch, grid, n_bias);
+    return cudaGetLastError();
 }
 
 }  // namespace
@@ -623,8 +673,8 @@ extern "C" int na1d_debug_bwd_timeline(long long* out) {
 #endif
 
 cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
-                         const void* v, const float* lse, const float* rpb, const int* valid_len, const Geometry& gm, int dtype,
-                         cudaStream_t st) {
+                         const void* v, const float* lse, const float* rpb, const int* valid_len, float* scratch,
+                         size_t scratch_floats, const Geometry& gm, int dtype, cudaStream_t st) {
     if (!tc_bwd_supports(gm)) return cudaErrorInvalidValue;
     const int weff = tc::eff_window(gm.win, gm.dil);
     const int KT = round_up(kTileM + weff - 1, 16);
@@ -639,7 +689,7 @@ cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void*
         return cudaErrorInvalidValue;
     const int sms = device_sm_count();
 #define NA1D_TC_BWD(E, C, WB) \
-    return launch_bwd<E, C, WB>(mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, lse, rpb, valid_len, gm, stride, KT, sms, st)
+    return launch_bwd<E, C, WB>(mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, scratch, scratch_floats, lse, rpb, valid_len, gm, stride, KT, sms, st)
 #define NA1D_TC_BWD_W(E, C)                          \
     if (weff <= 9) { NA1D_TC_BWD(E, C, 9); }       \
     else if (weff <= 17) { NA1D_TC_BWD(E, C, 17); } \

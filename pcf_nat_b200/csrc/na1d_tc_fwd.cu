@@ -20,7 +20,7 @@
 //             quad shuffles each, normalise, round to 16 bits -- the reference rounds probabilities to
 //             16 bits before its A.V product too (bf16_ana1d_kernel.cu:301-306) -- and store P over the
 //             S columns of TMEM (zeros outside the band). Later the same warps read O from TMEM, stage it
-//             in the tile's idle Q buffer and one thread issues a TMA tile store (rows >= T are clipped).
+//             in the tile's idle V buffer and one thread issues a TMA tile store (rows >= T are clipped).
 // Every wait is bounded; on expiry the CTA records a code in a device status word and unwinds
 // (TMEM is always released).
 #include "na1d_internal.h"
@@ -56,21 +56,26 @@ constexpr int kOColB = 96;   // O accumulator of the odd key steps: inside the S
 constexpr int kBiasPad = 16;
 
 struct FwdSmemLayout {
-    int stage_q, stage_k, stage_v, stage_bytes, misc, total;
+    int q, ring, stage_k, stage_v, stage_bytes, misc, total;  // q: the single Q buffer; ring: first K/V stage
 };
 __host__ __device__ inline FwdSmemLayout fwd_layout(int C, int KT, int bias_heads) {
     FwdSmemLayout L;
-    L.stage_q = 0;
-    L.stage_k = L.stage_q + round_up(kTileM * C * 2, 1024);
-    L.stage_v = L.stage_k + round_up(KT * C * 2, 1024);
-    L.stage_bytes = L.stage_v + round_up(KT * C * 2, 1024);
-    L.misc = 2 * L.stage_bytes;
+    // Q is needed only by the S MMAs at the start of a tile, so one buffer serves both stages: it is refilled as soon as
+    // those MMAs retire. K and V live in a 2-stage ring; the finished O is staged in the tile's V buffer (idle once the
+    // P.V MMAs have retired). 16 KB less than a Q buffer per stage: two CTAs per SM also for the widest window bucket.
+    L.q = 0;
+    L.ring = round_up(kTileM * C * 2, 1024);
+    L.stage_k = 0;
+    L.stage_v = round_up(KT * C * 2, 1024);
+    L.stage_bytes = 2 * round_up(KT * C * 2, 1024);
+    L.misc = L.ring + 2 * L.stage_bytes;
     L.total = L.misc + 256 + round_up(bias_heads * (kBiasPad + 48) * 4, 256) + 1008;  // misc, bias table, alignment slack
     return L;
 }
 
 struct alignas(8) FwdMisc {
-    uint64_t full[2], empty[2];
+    uint64_t full[2], empty[2];  // K/V ring
+    uint64_t full_q, empty_q;    // the single Q buffer
     uint64_t s_ready, p_ready, o_ready, o_free, o_staged;
     uint32_t tmem_base;
     int abort;
@@ -96,10 +101,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     // effective (dilated) window: neighbour kk of the reference is offset kk * dil of it
     const int dil = gm.dil, dmask = dil - 1, dshift = 31 - __clz(dil);
     const int win = tc::eff_window(gm.win, dil), left = gm.left * dil, T = gm.T;
-    const int stage_tx = (kTileM + 2 * KT) * kRowBytes;
+    const int stage_tx = 2 * KT * kRowBytes;
 
     if (tid == 0) {
         for (int s = 0; s < 2; ++s) { ptx::mbar_init(&misc->full[s], 1); ptx::mbar_init(&misc->empty[s], 1); }
+        ptx::mbar_init(&misc->full_q, 1);
+        ptx::mbar_init(&misc->empty_q, 1);
         ptx::mbar_init(&misc->s_ready, 1);
         ptx::mbar_init(&misc->p_ready, 128);
         ptx::mbar_init(&misc->o_ready, 2);  // one commit per MMA issuer
@@ -135,14 +142,18 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             int it = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1, k = it >> 1;
-                if (!ptx::mbar_wait_relaxed(&misc->empty[s], (k & 1) ^ 1) || *abort_flag) { atomicExch(&g_tc_status, 1); *abort_flag = 1; break; }
+                const int g0 = tile * kTileM;
+                // Q: free once the S MMAs of the previous tile have retired
+                if (!ptx::mbar_wait_relaxed(&misc->empty_q, (it & 1) ^ 1) || *abort_flag) { atomicExch(&g_tc_status, 1); *abort_flag = 1; break; }
                 // At the start every CTA of the grid loads at once and DRAM is the limit: let the first tile land before the
                 // second is requested, so that all CTAs start computing (and storing) early instead of at the end of the burst.
                 if (it == 1 && !ptx::mbar_wait_relaxed(&misc->full[0], 0)) { atomicExch(&g_tc_status, 1); *abort_flag = 1; break; }
-                const int g0 = tile * kTileM;
-                uint8_t* st = smem + s * L.stage_bytes;
+                ptx::mbar_expect_tx(&misc->full_q, (uint32_t)(kTileM * kRowBytes));
+                ptx::tma_load_3d(smem + L.q, &tm_q, &misc->full_q, 0, g0, 0);
+                // K, V: free once the tile two back has stored its output (staged in its V buffer)
+                if (!ptx::mbar_wait_relaxed(&misc->empty[s], (k & 1) ^ 1) || *abort_flag) { atomicExch(&g_tc_status, 1); *abort_flag = 1; break; }
+                uint8_t* st = smem + L.ring + s * L.stage_bytes;
                 ptx::mbar_expect_tx(&misc->full[s], (uint32_t)stage_tx);
-                ptx::tma_load_3d(st + L.stage_q, &tm_q, &misc->full[s], 0, g0, 0);
                 ptx::tma_load_3d(st + L.stage_k, &tm_k, &misc->full[s], 0, g0 - left, 0);
                 ptx::tma_load_3d(st + L.stage_v, &tm_v, &misc->full[s], 0, g0 - left, 0);
             }
@@ -152,7 +163,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             int it = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
                 if (!ptx::mbar_wait_relaxed(&misc->o_staged, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 6); *abort_flag = 1; break; }
-                ptx::tma_store_3d(&tm_o, smem + (it & 1) * L.stage_bytes + L.stage_q, 0, tile * kTileM, 0);
+                ptx::tma_store_3d(&tm_o, smem + L.ring + (it & 1) * L.stage_bytes + L.stage_v, 0, tile * kTileM, 0);
                 ptx::tma_store_commit();
                 ptx::tma_store_wait_read();
                 ptx::mbar_arrive(&misc->empty[it & 1]);
@@ -168,20 +179,22 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             int it = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1, k = it >> 1;
-                const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
+                const uint32_t st = ptx::smem_u32(smem + L.ring + s * L.stage_bytes);
                 // S overwrites the columns that held the previous tile's P and odd-step accumulator: both must be drained
-                if (!ptx::mbar_wait(&misc->full[s], k & 1) || !ptx::mbar_wait(&misc->o_free, (it & 1) ^ 1) || *abort_flag) {
+                if (!ptx::mbar_wait(&misc->full[s], k & 1) || !ptx::mbar_wait(&misc->full_q, it & 1) ||
+                    !ptx::mbar_wait(&misc->o_free, (it & 1) ^ 1) || *abort_flag) {
                     atomicExch(&g_tc_status, 2); *abort_flag = 1; break;
                 }
                 ptx::tc_fence_after_sync();
                 NA1D_FSTAMP(8);
                 {
-                    const uint64_t a0 = ptx::smem_desc(st + L.stage_q, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                    const uint64_t a0 = ptx::smem_desc(ptx::smem_u32(smem + L.q), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
                     const uint64_t b0 = ptx::smem_desc(st + L.stage_k, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
 #pragma unroll
                     for (int ks = 0; ks < C / 16; ++ks)
                         ptx::mma_ss(tmem, tc::desc_advance(a0, ks * 32), tc::desc_advance(b0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
                 }
+                ptx::mma_commit(&misc->empty_q);  // Q is read by nothing else
                 ptx::mma_commit(&misc->s_ready);
                 NA1D_FSTAMP(9);
                 if (!ptx::mbar_wait(&misc->p_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 3); *abort_flag = 1; break; }
@@ -205,7 +218,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             int it = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1, k = it >> 1;
-                const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
+                const uint32_t st = ptx::smem_u32(smem + L.ring + s * L.stage_bytes);
                 if (!ptx::mbar_wait(&misc->full[s], k & 1) || !ptx::mbar_wait(&misc->p_ready, it & 1) || *abort_flag) {
                     atomicExch(&g_tc_status, 7); *abort_flag = 1; break;
                 }
@@ -369,12 +382,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             ptx::mbar_arrive(&misc->p_ready);
             if (tid == 0) NA1D_FSTAMP(3);
 
-            // epilogue: O -> 16 bits -> the tile's idle Q buffer (same swizzle as the tensor map) -> TMA store
+            // epilogue: O -> 16 bits -> the tile's idle V buffer (same swizzle as the tensor map) -> TMA store
             if (!ptx::mbar_wait(&misc->o_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 5); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
             if (tid == 0) NA1D_FSTAMP(4);
             {
-                uint8_t* sO = smem + (it & 1) * L.stage_bytes + L.stage_q;
+                uint8_t* sO = smem + L.ring + (it & 1) * L.stage_bytes + L.stage_v;  // this tile's V buffer: P.V has retired
                 // row r, 16-byte chunk c at r*rowbytes + ((c ^ swz(r)) * 16): the TMA swizzle of this row size
                 const int swz = (C == 64) ? (r & 7) : (C == 32) ? ((r >> 1) & 3) : ((r >> 2) & 1);
                 constexpr int HALF = C >= 32 ? C / 2 : C;  // columns per round (two rounds keep the register count down)

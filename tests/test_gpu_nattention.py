@@ -96,3 +96,27 @@ def test_library_op_opcheck_and_compile():
     assert torch.equal(out, eager)
     for a, b in zip(ge, gc):
         assert torch.allclose(a.float(), b.float(), rtol=0, atol=1e-6 * max(1.0, float(a.float().abs().max())))
+
+
+def test_extractor_fused_equals_unfused_chain():
+    """A small PCF-NAT-style extractor: the fused layer and the reference's unfused operator chain (drop-in QK / AV functions
+    around torch softmax) give the same loss and gradients."""
+    from pcf_nat_b200.model import PCFNATExtractor
+    kw = dict(frames=64, feat=24, dim=64, heads=4, win=7, stages=2, blocks=2, emb=32, classes=40)
+    torch.manual_seed(1)
+    a = PCFNATExtractor(attention="fused", **kw).cuda()
+    b = PCFNATExtractor(attention="unfused", **kw).cuda()
+    b.load_state_dict(a.state_dict())
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(8, 24, 64, generator=g).cuda()
+    y = torch.randint(0, 40, (8,), generator=g).cuda()
+    out = []
+    for m in (a, b):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = m(x, y)
+        loss.backward()
+        out.append((float(loss.detach()), m.front.weight.grad.float().clone(), m.stages[0][0].attn.relative_position_bias.grad.clone()))
+    assert abs(out[0][0] - out[1][0]) < 2e-2 * max(1.0, abs(out[1][0]))
+    for i in (1, 2):
+        ref = out[1][i]
+        assert float((out[0][i] - ref).abs().max()) <= 5e-2 * max(1e-3, float(ref.abs().max()))
