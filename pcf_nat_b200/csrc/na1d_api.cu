@@ -98,9 +98,9 @@ int na1d_v_backward(void* v_gd, const float* attn, const void* result_gd, int64_
     return na1d_k_backward(v_gd, attn, result_gd, N, T, C, win, left, dil, dtype, stream);
 }
 
-static int pick_family(const na1d::Geometry& g, int backward) {
+static int pick_family(const na1d::Geometry& g, int backward, bool has_bias = false, bool wants_bias_grad = false) {
     const int forced = g_family_override.load();
-    const bool tc_ok = backward ? na1d::tc_bwd_supports(g) : na1d::tc_fwd_supports(g);
+    const bool tc_ok = backward ? na1d::tc_bwd_supports(g, has_bias, wants_bias_grad) : na1d::tc_fwd_supports(g);
     if (forced == 0) return 0;
     if (forced == 1) return tc_ok ? 1 : NA1D_ERR_UNSUPPORTED;
     return tc_ok ? 1 : 0;
@@ -150,7 +150,7 @@ int na1d_fused_backward(void* dq, void* dk, void* dv, float* d_rpb, const void* 
     if (int s = check_geometry(N, heads, T, C, win, left, dil, dtype, scale, g)) return s;
     if (d_rpb && heads * win * 4 > 48 * 1024) return NA1D_ERR_TOO_LARGE;
     cudaStream_t st = (cudaStream_t)stream;
-    const int fam = pick_family(g, 1);
+    const int fam = pick_family(g, 1, rpb != nullptr, d_rpb != nullptr);
     if (fam < 0) return fam;
     if (fam == 1)  // delta is recomputed inside the kernel from P and dP: o is not read; delta_ws (N*T floats) only holds the
                    // per-CTA partial sums of the bias gradient

@@ -18,12 +18,14 @@ cudaError_t simt_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const voi
 cudaError_t window_index(int* j_out, unsigned char* inr, int T, int win, int left, int dil, cudaStream_t st);
 
 // ---- tcgen05 / TMA family (na1d_tc_fwd.cu)
-bool tc_fwd_supports(const Geometry& gm);
+bool tc_fwd_supports(const Geometry& gm);  // shape limits of the tcgen05 forward
 cudaError_t tc_fused_fwd(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
                          const int* valid_len, const Geometry& gm, int dtype, cudaStream_t st);
 int tc_read_status();
 int tc_bwd_read_status();
-bool tc_bwd_supports(const Geometry& gm);
+// shape limits of the tcgen05 backward, including whether its shared memory fits with a bias table (has_bias) and the
+// bias-gradient accumulators (wants_bias_grad)
+bool tc_bwd_supports(const Geometry& gm, bool has_bias = false, bool wants_bias_grad = false);
 cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
                          const void* v, const float* lse, const float* rpb, const int* valid_len, float* scratch,
                          size_t scratch_floats, const Geometry& gm, int dtype, cudaStream_t st);

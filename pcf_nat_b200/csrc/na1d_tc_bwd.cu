@@ -93,6 +93,50 @@ __device__ __noinline__ void bias_grad_outside(float* row, int off, int dshift, 
     if (g1 != 0.f) atomicAdd(row + ((off + 1) >> dshift), g1);
 }
 
+// Bias gradient of one tile, one warp: column sums of dS over the warp's owned query rows (hr = the row's head, -1 for a row
+// this tile does not own). Lane r has the address of row r of the dS operand (16-bit, scaled); a shuffle butterfly leaves the
+// sum of window offset i on lane i * (32 / NV), which adds it to the warp's own accumulator (no atomics: lanes hold distinct
+// offsets). Rows of different heads (a warp spans at most two sequences) take one pass per head. NV = 8, 16 or 32 offsets go
+// through the butterfly; offset NV exists only when the window fills its bucket. Not inlined: it keeps the tile loop short.
+template <typename E, int NV>
+__device__ __noinline__ void bias_grad_tile(const uint8_t* row, int r, int lane, int hr, int win, int ref_win, int dmask,
+                                            int dshift, float inv_scale, float* acc) {
+    const int h_hi = __reduce_max_sync(0xffffffffu, hr);
+    if (h_hi < 0) return;
+    int hsel = __reduce_min_sync(0xffffffffu, hr >= 0 ? hr : 0x7fffffff);
+    for (;;) {
+        const bool mine = hr == hsel;
+        float x[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int col = r + i;
+            x[i] = (mine && i < win) ? (float)*reinterpret_cast<const E*>(row + (col >> 3) * 128 + (col & 7) * 2) : 0.f;
+        }
+        float last = 0.f;
+        if (win > NV) {
+            const int col = r + NV;
+            last = mine ? (float)*reinterpret_cast<const E*>(row + (col >> 3) * 128 + (col & 7) * 2) : 0.f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) last += __shfl_xor_sync(0xffffffffu, last, o);
+        }
+        const float v = tc::column_sums<NV>(x, lane);
+        const int off = lane / (32 / NV);
+        float* acc_row = acc + hsel * ref_win;
+        if (lane % (32 / NV) == 0 && off < win && (off & dmask) == 0) acc_row[off >> dshift] += v * inv_scale;
+        __syncwarp();
+        if (lane == 0 && win > NV) acc_row[NV >> dshift] += last * inv_scale;
+        if (hsel == h_hi) break;
+        hsel = __reduce_min_sync(0xffffffffu, hr > hsel ? hr : 0x7fffffff);
+        __syncwarp();
+    }
+}
+
+// The layout as both the launcher and the kernel compute it (one function, so they cannot disagree): bias table for every
+// head when there is a bias, four per-warp (H, win) accumulators when its gradient is wanted.
+__host__ __device__ inline BwdSmemLayout bwd_layout_for(int C, int KT, const Geometry& gm, bool has_bias, bool wants_bias_grad) {
+    return bwd_layout(C, KT, has_bias ? gm.H : 0, wants_bias_grad ? 4 * gm.H * gm.win : 0);
+}
+
 struct alignas(8) BwdMisc {
     // ring barriers per stage and per buffer (kQ, kDO, kK, kV): each buffer is refilled as soon as its last reader retires
     uint64_t full[2][4], empty[2][4];
@@ -117,14 +161,14 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int n_bias = gm.H * gm.win;  // entries of the bias gradient
-    const BwdSmemLayout L = bwd_layout(C, KT, rpb ? gm.H : 0, d_rpb ? n_bias : 0);
+    const BwdSmemLayout L = bwd_layout_for(C, KT, gm, rpb != nullptr, d_rpb != nullptr);
     uint8_t* sDS = smem + L.ds;
     uint8_t* sP = smem + L.p;
     BwdMisc* misc = reinterpret_cast<BwdMisc*>(smem + L.misc);
     float* bias_tab = reinterpret_cast<float*>(smem + L.misc + 512);
-    // per-CTA accumulator of the bias gradient: global atomics on the (H, win) array -- one cache line for the usual sizes --
-    // serialise (5x the whole kernel's time when every tile issued them), so each CTA adds up its tiles here and hands over
-    // one row of partial sums at its end
+    // accumulators of the bias gradient, one (H, win) array per compute warp: global atomics on the result -- one cache line
+    // for the usual sizes -- serialise (5x the whole kernel's time when every tile issued them), so each warp adds up its
+    // tiles here without atomics and the CTA hands over one row of partial sums at its end
     float* bias_acc = bias_tab + round_up((rpb ? gm.H : 0) * kBiasRowB, 64);
     const int rows_total = gm.N * gm.T;
 
@@ -294,7 +338,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const float inv_T = 1.f / (float)T, inv_H = 1.f / (float)gm.H;
         const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
         if (d_rpb)
-            for (int i = r; i < n_bias; i += 128) bias_acc[i] = 0.f;
+            for (int i = r; i < 4 * n_bias; i += 128) bias_acc[i] = 0.f;
         if (rpb) {
             // bias table of every head, once per CTA (barrier among the 4 compute warps only)
             for (int i = r; i < gm.H * kBiasRowB; i += 128) {
@@ -317,126 +361,240 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         };
         float lse_next[2][2];
         load_lse(blockIdx.x, lse_next);
+        int prev_hr = -1;
         tc::RowCursor cur;  // row tile * stride = g0 + right
         cur.init(blockIdx.x * stride, T, gm.H, gridDim.x * stride);
         const int batch = gm.N / gm.H;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it, cur.advance()) {
             if (tid == 0) NA1D_STAMP(0);
             const int g0 = tile * stride - right;
-            // the four query rows this thread sees in the fragments: block b, row half hh (lse was fetched one tile ahead)
-            // The four rows this thread sees in the fragments (local rows 32 warp + fr + 8k; lse was fetched one tile ahead):
-            //   jb  : key index inside the row's own sequence of neighbour kk is jb + (kk - fa); outside [0, T) it is the
-            //         reference's zero-padded K/V row
-            //   vle : keys >= vle are masked (0 when the query itself is padding);  -1 marks a row outside the tensor
-            float lse2[2][2];
-            int jb[2][2], vle[2][2], hrow[2][2];
-            bool need_mask = false;
-            {
-                int tq, hq, bq;
-                cur.row_at(warp * 32 + fr - right, inv_T, inv_H, tq, hq, bq);
+            if constexpr (WB == 33) {
+                // Widest window bucket: the two 16-row blocks of the warp are processed one after the other in a ROLLED loop.
+                // 48 fragment values of S and of dP per block and thread: holding both blocks at once spilled registers, and
+                // the unrolled code of both did not fit the instruction cache (measured: 2-3x more cycles per tile).
+                if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 14); *abort_flag = 1; break; }
+                ptx::tc_fence_after_sync();
+                bool failed = false;
+#pragma unroll 1
+                for (int b = 0; b < 2; ++b) {
+                    // the two rows of this block this thread sees (row half hh): see the comments of the unrolled path below
+                    float lse2[2];
+                    int jb[2], vle[2], hrow[2];
+                    bool need_mask = false;
+                    {
+                        int tq, hq, bq;
+                        cur.row_at(warp * 32 + 16 * b + fr - right, inv_T, inv_H, tq, hq, bq);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int gq = g0 + warp * 32 + fr + 8 * k;
-                    const bool live = gq >= 0 && gq < rows_total;
-                    const int vlr = !live ? 0 : valid_len ? min(T, __ldg(valid_len + min(max(bq, 0), batch - 1))) : T;
-                    hrow[k >> 1][k & 1] = hq;
-                    jb[k >> 1][k & 1] = tq - left + fa;
-                    vle[k >> 1][k & 1] = !live ? -1 : tq >= vlr ? 0 : vlr;
-                    need_mask |= tq < left || tq + right >= vlr;
-                    lse2[k >> 1][k & 1] = lse_next[k >> 1][k & 1] * kLog2e;
-                    tc::row_step8(T, gm.H, tq, hq, bq);
-                }
-            }
-            // masks are needed only when one of the warp's rows touches a sequence end or a padded region
-            need_mask = __any_sync(0xffffffffu, need_mask);
-            if (tid == 0) NA1D_STAMP(1);
-            if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 14); *abort_flag = 1; break; }
-            ptx::tc_fence_after_sync();
-            if (tid == 0) NA1D_STAMP(2);
-
-            float s[2][4 * NG], d[2][4 * NG];
+                        for (int hh = 0; hh < 2; ++hh) {
+                            const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
+                            const bool live = gq >= 0 && gq < rows_total;
+                            const int vlr = !live ? 0 : valid_len ? min(T, __ldg(valid_len + min(max(bq, 0), batch - 1))) : T;
+                            hrow[hh] = hq;
+                            jb[hh] = tq - left + fa;
+                            vle[hh] = !live ? -1 : tq >= vlr ? 0 : vlr;
+                            need_mask |= tq < left || tq + right >= vlr;
+                            lse2[hh] = (b ? lse_next[1][hh] : lse_next[0][hh]) * kLog2e;
+                            tc::row_step8(T, gm.H, tq, hq, bq);
+                        }
+                    }
+                    need_mask = __any_sync(0xffffffffu, need_mask);
+                    float s1[4 * NG], d1[4 * NG];
+                    const uint32_t a = lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b);
+                    tc::ld_frag<NG>(a, s1);
+                    tc::ld_frag<NG>(a + kColDP, d1);
+                    ptx::tmem_ld_wait();
+                    if (b == 1) {  // S and dP of this tile are out of tensor memory
+                        ptx::tc_fence_before_sync();
+                        ptx::mbar_arrive(&misc->s_free);
+                    }
+                    float delta[2] = {0.f, 0.f};
+                    auto elements = [&](auto masked_tag) {
+                        constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                const uint32_t a = lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b);
-                tc::ld_frag<NG>(a, s[b]);
-                tc::ld_frag<NG>(a + kColDP, d[b]);
-            }
-            ptx::tmem_ld_wait();
-            ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(&misc->s_free);
-            if (tid == 0) NA1D_STAMP(3);
-            float delta[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-            // two straight-line copies of the element loop, with and without masks
-            auto elements = [&](auto masked_tag) {
-                constexpr bool kMasked = decltype(masked_tag)::value;
+                        for (int g = 0; g < NG; ++g)
 #pragma unroll
-                for (int b = 0; b < 2; ++b)
+                            for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const int idx = 4 * g + 2 * hh + e;
+                                    const int kc = 8 * (g - hh) + e, kk = kc + fa;
+                                    bool on = (unsigned)kk < (unsigned)win && (kk & dmask) == 0;
+                                    float bias = 0.f;
+                                    if (rpb) bias = bias_tab[hrow[hh] * kBiasRowB + kBiasPad + kk];
+                                    float dot = s1[idx], dpv = d1[idx];
+                                    if constexpr (kMasked) {
+                                        const unsigned j = (unsigned)(jb[hh] + kc);
+                                        if (j >= (unsigned)T) { dot = 0.f; dpv = 0.f; }
+                                        if ((int)j >= vle[hh] || (int)j < 0) bias += mask2;
+                                        on = on && vle[hh] >= 0;
+                                    }
+                                    const float x = fmaf(dot, sc, bias) - lse2[hh];
+                                    const float p = on ? tc::fast_exp2(x) : 0.f;
+                                    s1[idx] = p;
+                                    d1[idx] = dpv;
+                                    delta[hh] = fmaf(p, dpv, delta[hh]);
+                                }
+                    };
+                    if (need_mask) elements(std::true_type{}); else elements(std::false_type{});
+                    delta[0] = tc::quad_sum(delta[0]);
+                    delta[1] = tc::quad_sum(delta[1]);
+                    if (b == 0) {
+                        // batch 2 of the previous tile must have finished reading the operand matrices before they are rewritten
+                        if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { failed = true; break; }
+                        if (d_rpb && it > 0)
+                            bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask,
+                                                      dshift, 1.f / gm.scale, bias_acc + warp * n_bias);
+                    }
+                    uint32_t pk_p[2 * NG], pk_d[2 * NG];
 #pragma unroll
                     for (int g = 0; g < NG; ++g)
 #pragma unroll
-                        for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-                            for (int e = 0; e < 2; ++e) {
-                                const int idx = 4 * g + 2 * hh + e;
-                                const int kc = 8 * (g - hh) + e, kk = kc + fa;
-                                bool on = (unsigned)kk < (unsigned)win && (kk & dmask) == 0;
-                                float bias = 0.f;
-                                if (rpb) bias = bias_tab[hrow[b][hh] * kBiasRowB + kBiasPad + kk];
-                                float dot = s[b][idx], dpv = d[b][idx];
-                                if constexpr (kMasked) {
-                                    const unsigned j = (unsigned)(jb[b][hh] + kc);
-                                    if (j >= (unsigned)T) { dot = 0.f; dpv = 0.f; }  // the reference's zero-padded K/V row
-                                    if ((int)j >= vle[b][hh] || (int)j < 0) bias += mask2;
-                                    on = on && vle[b][hh] >= 0;
+                        for (int hh = 0; hh < 2; ++hh) {
+                            const int idx = 4 * g + 2 * hh;
+                            float ds0 = s1[idx] * (d1[idx] - delta[hh]);
+                            float ds1 = s1[idx + 1] * (d1[idx + 1] - delta[hh]);
+                            float p0 = s1[idx], p1 = s1[idx + 1];
+                            if (need_mask) {
+                                const int kc = 8 * (g - hh), kk0 = kc + fa;
+                                const int j0 = jb[hh] + kc;
+                                const int row = warp * 32 + 16 * b + 8 * hh + fr;
+                                const bool own = d_rpb && row >= right && row < kTileM - left;
+                                const bool out0 = (unsigned)j0 >= (unsigned)T, out1 = (unsigned)(j0 + 1) >= (unsigned)T;
+                                if (out0 | out1) {
+                                    if (own) bias_grad_outside(bias_acc + warp * n_bias + hrow[hh] * gm.win, kk0, dshift, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
+                                    if (out0) { ds0 = 0.f; p0 = 0.f; }
+                                    if (out1) { ds1 = 0.f; p1 = 0.f; }
                                 }
-                                const float x = fmaf(dot, sc, bias) - lse2[b][hh];
-                                const float p = on ? tc::fast_exp2(x) : 0.f;
-                                s[b][idx] = p;
-                                d[b][idx] = dpv;
-                                delta[b][hh] = fmaf(p, dpv, delta[b][hh]);
                             }
-            };
-            if (need_mask) elements(std::true_type{}); else elements(std::false_type{});
-            if (tid == 0) NA1D_STAMP(12);
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) delta[b][hh] = tc::quad_sum(delta[b][hh]);
-            // batch 2 of the previous tile must have finished reading the operand matrices before they are rewritten
-            if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
-            if (tid == 0) NA1D_STAMP(13);
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                uint32_t pk_p[2 * NG], pk_d[2 * NG];
-#pragma unroll
-                for (int g = 0; g < NG; ++g)
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
-                        const int idx = 4 * g + 2 * hh;
-                        float ds0 = s[b][idx] * (d[b][idx] - delta[b][hh]);
-                        float ds1 = s[b][idx + 1] * (d[b][idx + 1] - delta[b][hh]);
-                        float p0 = s[b][idx], p1 = s[b][idx + 1];
-                        if (need_mask) {
-                            // a neighbour outside the query's sequence is a zero K/V row in the reference: its logit still has a
-                            // bias gradient, but it must not reach the other sequence's dK/dV nor this query's dQ
-                            const int kc = 8 * (g - hh), kk0 = kc + fa;
-                            const int j0 = jb[b][hh] + kc;
-                            const int row = warp * 32 + 16 * b + 8 * hh + fr;
-                            const bool own = d_rpb && row >= right && row < kTileM - left;
-                            const bool out0 = (unsigned)j0 >= (unsigned)T, out1 = (unsigned)(j0 + 1) >= (unsigned)T;
-                            if (out0 | out1) {
-                                if (own) bias_grad_outside(bias_acc + hrow[b][hh] * gm.win, kk0, dshift, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
-                                if (out0) { ds0 = 0.f; p0 = 0.f; }
-                                if (out1) { ds1 = 0.f; p1 = 0.f; }
-                            }
+                            pk_d[2 * g + hh] = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
+                            pk_p[2 * g + hh] = Cvt<E>::pack2(p0, p1);
                         }
-                        pk_d[2 * g + hh] = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
-                        pk_p[2 * g + hh] = Cvt<E>::pack2(p0, p1);
+                    const uint32_t blk = (uint32_t)(4 * warp + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * warp + 2 * b) * 128u;
+                    tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d, lane);
+                    tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
+                }
+                if (failed) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
+            } else {
+                // the four query rows this thread sees in the fragments: block b, row half hh (lse was fetched one tile ahead)
+                // The four rows this thread sees in the fragments (local rows 32 warp + fr + 8k; lse was fetched one tile ahead):
+                //   jb  : key index inside the row's own sequence of neighbour kk is jb + (kk - fa); outside [0, T) it is the
+                //         reference's zero-padded K/V row
+                //   vle : keys >= vle are masked (0 when the query itself is padding);  -1 marks a row outside the tensor
+                float lse2[2][2];
+                int jb[2][2], vle[2][2], hrow[2][2];
+                bool need_mask = false;
+                {
+                    int tq, hq, bq;
+                    cur.row_at(warp * 32 + fr - right, inv_T, inv_H, tq, hq, bq);
+    #pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int gq = g0 + warp * 32 + fr + 8 * k;
+                        const bool live = gq >= 0 && gq < rows_total;
+                        const int vlr = !live ? 0 : valid_len ? min(T, __ldg(valid_len + min(max(bq, 0), batch - 1))) : T;
+                        hrow[k >> 1][k & 1] = hq;
+                        jb[k >> 1][k & 1] = tq - left + fa;
+                        vle[k >> 1][k & 1] = !live ? -1 : tq >= vlr ? 0 : vlr;
+                        need_mask |= tq < left || tq + right >= vlr;
+                        lse2[k >> 1][k & 1] = lse_next[k >> 1][k & 1] * kLog2e;
+                        tc::row_step8(T, gm.H, tq, hq, bq);
                     }
-                // core matrix of the block's first row / first column: row group 4w+2b, column group 4w+2b
-                const uint32_t blk = (uint32_t)(4 * warp + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * warp + 2 * b) * 128u;
-                tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d, lane);
-                tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
+                }
+                // masks are needed only when one of the warp's rows touches a sequence end or a padded region
+                need_mask = __any_sync(0xffffffffu, need_mask);
+                if (tid == 0) NA1D_STAMP(1);
+                if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 14); *abort_flag = 1; break; }
+                ptx::tc_fence_after_sync();
+                if (tid == 0) NA1D_STAMP(2);
+
+                float s[2][4 * NG], d[2][4 * NG];
+    #pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    const uint32_t a = lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b);
+                    tc::ld_frag<NG>(a, s[b]);
+                    tc::ld_frag<NG>(a + kColDP, d[b]);
+                }
+                ptx::tmem_ld_wait();
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(&misc->s_free);
+                if (tid == 0) NA1D_STAMP(3);
+                float delta[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+                // two straight-line copies of the element loop, with and without masks
+                auto elements = [&](auto masked_tag) {
+                    constexpr bool kMasked = decltype(masked_tag)::value;
+    #pragma unroll
+                    for (int b = 0; b < 2; ++b)
+    #pragma unroll
+                        for (int g = 0; g < NG; ++g)
+    #pragma unroll
+                            for (int hh = 0; hh < 2; ++hh)
+    #pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const int idx = 4 * g + 2 * hh + e;
+                                    const int kc = 8 * (g - hh) + e, kk = kc + fa;
+                                    bool on = (unsigned)kk < (unsigned)win && (kk & dmask) == 0;
+                                    float bias = 0.f;
+                                    if (rpb) bias = bias_tab[hrow[b][hh] * kBiasRowB + kBiasPad + kk];
+                                    float dot = s[b][idx], dpv = d[b][idx];
+                                    if constexpr (kMasked) {
+                                        const unsigned j = (unsigned)(jb[b][hh] + kc);
+                                        if (j >= (unsigned)T) { dot = 0.f; dpv = 0.f; }  // the reference's zero-padded K/V row
+                                        if ((int)j >= vle[b][hh] || (int)j < 0) bias += mask2;
+                                        on = on && vle[b][hh] >= 0;
+                                    }
+                                    const float x = fmaf(dot, sc, bias) - lse2[b][hh];
+                                    const float p = on ? tc::fast_exp2(x) : 0.f;
+                                    s[b][idx] = p;
+                                    d[b][idx] = dpv;
+                                    delta[b][hh] = fmaf(p, dpv, delta[b][hh]);
+                                }
+                };
+                if (need_mask) elements(std::true_type{}); else elements(std::false_type{});
+                if (tid == 0) NA1D_STAMP(12);
+    #pragma unroll
+                for (int b = 0; b < 2; ++b)
+    #pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) delta[b][hh] = tc::quad_sum(delta[b][hh]);
+                // batch 2 of the previous tile must have finished reading the operand matrices before they are rewritten
+                if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
+                if (tid == 0) NA1D_STAMP(13);
+                // Bias gradient of the PREVIOUS tile, read back from its dS operand now: while batch 2 runs its operand fetches own
+                // the shared-memory bandwidth and the same read-back took thousands of cycles; here the tensor pipe is done with it.
+                if (d_rpb && it > 0)
+                    bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask, dshift,
+                                              1.f / gm.scale, bias_acc + warp * n_bias);
+    #pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    uint32_t pk_p[2 * NG], pk_d[2 * NG];
+    #pragma unroll
+                    for (int g = 0; g < NG; ++g)
+    #pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {
+                            const int idx = 4 * g + 2 * hh;
+                            float ds0 = s[b][idx] * (d[b][idx] - delta[b][hh]);
+                            float ds1 = s[b][idx + 1] * (d[b][idx + 1] - delta[b][hh]);
+                            float p0 = s[b][idx], p1 = s[b][idx + 1];
+                            if (need_mask) {
+                                // a neighbour outside the query's sequence is a zero K/V row in the reference: its logit still has a
+                                // bias gradient, but it must not reach the other sequence's dK/dV nor this query's dQ
+                                const int kc = 8 * (g - hh), kk0 = kc + fa;
+                                const int j0 = jb[b][hh] + kc;
+                                const int row = warp * 32 + 16 * b + 8 * hh + fr;
+                                const bool own = d_rpb && row >= right && row < kTileM - left;
+                                const bool out0 = (unsigned)j0 >= (unsigned)T, out1 = (unsigned)(j0 + 1) >= (unsigned)T;
+                                if (out0 | out1) {
+                                    if (own) bias_grad_outside(bias_acc + warp * n_bias + hrow[b][hh] * gm.win, kk0, dshift, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
+                                    if (out0) { ds0 = 0.f; p0 = 0.f; }
+                                    if (out1) { ds1 = 0.f; p1 = 0.f; }
+                                }
+                            }
+                            pk_d[2 * g + hh] = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
+                            pk_p[2 * g + hh] = Cvt<E>::pack2(p0, p1);
+                        }
+                    // core matrix of the block's first row / first column: row group 4w+2b, column group 4w+2b
+                    const uint32_t blk = (uint32_t)(4 * warp + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * warp + 2 * b) * 128u;
+                    tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d, lane);
+                    tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
+                }
             }
             if (tid == 0) NA1D_STAMP(4);
             ptx::fence_proxy_async_smem();
@@ -445,48 +603,18 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             load_lse(tile + gridDim.x, lse_next);
             if (tid == 0) NA1D_STAMP(5);
             if (d_rpb) {
-                // bias gradient: column sums of dS over the query rows this tile owns. Lane r reads the band of row r back from
-                // the dS operand (16-bit, scaled); a butterfly leaves the sum of window offset i on lane i * (32 / NV), which
-                // adds it to the CTA's accumulator. Rows of different heads (a warp spans at most two sequences) take one pass
-                // per head.
-                constexpr int NV = WB - 1;  // 8, 16 or 32 offsets through the butterfly; offset NV (full bucket) separately
-                __syncwarp();
+                // head of the row this lane will read back (-1: a row this tile does not own)
                 const int gr = g0 + r;
-                const bool own = r >= right && r < kTileM - left && gr >= 0 && gr < rows_total;
-                int hr = -1;
-                if (own) {
+                prev_hr = -1;
+                if (r >= right && r < kTileM - left && gr >= 0 && gr < rows_total) {
                     int tr, br;
-                    cur.row_at(r - right, inv_T, inv_H, tr, hr, br);
-                }
-                const int h_hi = __reduce_max_sync(0xffffffffu, hr);
-                int hsel = __reduce_min_sync(0xffffffffu, own ? hr : 0x7fffffff);
-                const float inv_scale = 1.f / gm.scale;
-                const uint8_t* row = sDS + (r >> 3) * lboq + (r & 7) * 16;
-                while (h_hi >= 0) {
-                    const bool mine = own && hr == hsel;
-                    float x[NV];
-#pragma unroll
-                    for (int i = 0; i < NV; ++i) {
-                        const int col = r + i;
-                        x[i] = (mine && i < win) ? (float)*reinterpret_cast<const E*>(row + (col >> 3) * 128 + (col & 7) * 2) : 0.f;
-                    }
-                    float last = 0.f;  // offset NV exists only when the window fills its bucket
-                    if (win > NV) {
-                        const int col = r + NV;
-                        last = mine ? (float)*reinterpret_cast<const E*>(row + (col >> 3) * 128 + (col & 7) * 2) : 0.f;
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) last += __shfl_xor_sync(0xffffffffu, last, o);
-                    }
-                    const float v = tc::column_sums<NV>(x, lane);
-                    const int off = lane / (32 / NV);
-                    float* acc_row = bias_acc + hsel * gm.win;
-                    if (lane % (32 / NV) == 0 && off < win && (off & dmask) == 0 && v != 0.f) atomicAdd(acc_row + (off >> dshift), v * inv_scale);
-                    if (lane == 1 && win > NV && last != 0.f) atomicAdd(acc_row + (NV >> dshift), last * inv_scale);
-                    if (hsel == h_hi) break;
-                    hsel = __reduce_min_sync(0xffffffffu, (own && hr > hsel) ? hr : 0x7fffffff);
+                    cur.row_at(r - right, inv_T, inv_H, tr, prev_hr, br);
                 }
             }
         }
+        if (d_rpb && it > 0 && ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) && !*abort_flag)  // the last tile's share
+            bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask, dshift,
+                                      1.f / gm.scale, bias_acc + warp * n_bias);
         if (d_rpb) {
             // hand over this CTA's partial bias gradient: every compute thread arrives (also after an aborted loop), warp 0
             // waits for all of them and writes row blockIdx.x of the partial-sum matrix (or adds to the result directly when
@@ -494,7 +622,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             ptx::mbar_arrive(&misc->acc_done);
             if (warp == 0 && ptx::mbar_wait(&misc->acc_done, 0)) {
                 for (int i = lane; i < n_bias; i += 32) {
-                    const float x = bias_acc[i];
+                    const float x = (bias_acc[i] + bias_acc[n_bias + i]) + (bias_acc[2 * n_bias + i] + bias_acc[3 * n_bias + i]);
                     if (drpb_direct) { if (x != 0.f) atomicAdd(d_rpb + i, x); }
                     else d_rpb[(size_t)blockIdx.x * n_bias + i] = x;
                 }
@@ -620,7 +748,7 @@ cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUte
                        const float* lse, const float* rpb, const int* valid_len, const Geometry& gm, int stride, int KT, int sm_count,
                        cudaStream_t st) {
     const int n_bias = gm.H * gm.win;
-    const BwdSmemLayout L = bwd_layout(C, KT, rpb ? gm.H : 0, d_rpb ? n_bias : 0);
+    const BwdSmemLayout L = bwd_layout_for(C, KT, gm, rpb != nullptr, d_rpb != nullptr);
     const int smem = L.total;
     // only 64-channel rows can be too large for the dedicated output staging buffer
     if constexpr (C != 64) {
@@ -654,8 +782,14 @@ cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUte
 
 }  // namespace
 
-bool tc_bwd_supports(const Geometry& gm) {
-    return tc::pow2(gm.dil) && (gm.C == 64 || gm.C == 32 || gm.C == 16) && tc::eff_window(gm.win, gm.dil) <= 33 && gm.H <= 32 && gm.T >= 32 && gm.T < (1 << 21);
+bool tc_bwd_supports(const Geometry& gm, bool has_bias, bool wants_bias_grad) {
+    if (!(tc::pow2(gm.dil) && (gm.C == 64 || gm.C == 32 || gm.C == 16) && tc::eff_window(gm.win, gm.dil) <= 33 && gm.H <= 32 &&
+          gm.T >= 32 && gm.T < (1 << 21)))
+        return false;
+    // 64-channel rows with the widest window bucket leave 1.5 KB of shared memory: a bias table of more than 4 heads or the
+    // bias-gradient accumulators do not fit there, and the call goes to the CUDA-core kernels
+    const int KT = round_up(kTileM + tc::eff_window(gm.win, gm.dil) - 1, 16);
+    return bwd_layout_for(gm.C, KT, gm, has_bias, wants_bias_grad).total <= 227 * 1024;
 }
 
 // Reads and clears the backward kernels' status word (synchronises the device).
@@ -675,7 +809,7 @@ extern "C" int na1d_debug_bwd_timeline(long long* out) {
 cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
                          const void* v, const float* lse, const float* rpb, const int* valid_len, float* scratch,
                          size_t scratch_floats, const Geometry& gm, int dtype, cudaStream_t st) {
-    if (!tc_bwd_supports(gm)) return cudaErrorInvalidValue;
+    if (!tc_bwd_supports(gm, rpb != nullptr, d_rpb != nullptr)) return cudaErrorInvalidValue;
     const int weff = tc::eff_window(gm.win, gm.dil);
     const int KT = round_up(kTileM + weff - 1, 16);
     const int stride = kTileM - (weff - 1);
