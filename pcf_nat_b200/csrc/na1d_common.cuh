@@ -43,6 +43,7 @@ template <> struct Cvt<__nv_bfloat16> {
     static __device__ __forceinline__ uint32_t pack2(float a, float b) {
         __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t);
     }
+    static __device__ __forceinline__ float from_bits(unsigned short raw) { return __uint_as_float((uint32_t)raw << 16); }
 };
 template <> struct Cvt<__half> {
     static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
@@ -59,6 +60,7 @@ template <> struct Cvt<__half> {
     static __device__ __forceinline__ uint32_t pack2(float a, float b) {
         __half2 t = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&t);
     }
+    static __device__ __forceinline__ float from_bits(unsigned short raw) { return __half2float(__ushort_as_half(raw)); }
 };
 
 }  // namespace na1d
