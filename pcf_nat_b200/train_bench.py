@@ -24,7 +24,9 @@ def main(argv=None):
     ap.add_argument("--frames", type=int, default=300)
     ap.add_argument("--attention", default="fused", choices=["fused", "unfused"])
     ap.add_argument("--launch", default="graph", choices=["graph", "eager"],
-                    help="graph: the whole step (forward, backward, all-reduce, optimizer) is one CUDA graph replay")
+                    help="graph: the whole step (forward, backward, optimizer) is one CUDA graph replay; single GPU only -- "
+                         "with more than one rank the step always runs eagerly (a captured NCCL all-reduce inside a "
+                         "DistributedDataParallel step did not complete here)")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="strong: the global batch is split over the GPUs; weak: every GPU gets the whole global batch")
     args = ap.parse_args(argv)
@@ -41,7 +43,10 @@ def main(argv=None):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a short collective timeout: a rank that fails must end the job instead of leaving the others waiting
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+        args.launch = "eager"
     lo, hi = parallel.shard_range(args.global_batch, world, rank) if args.scaling == "strong" else (0, args.global_batch)
     per_gpu = hi - lo
 
@@ -66,7 +71,7 @@ def main(argv=None):
             opt.step()
             return loss
 
-        for _ in range(max(args.warmup, 11 if (world > 1 and args.launch == "graph") else 3)):
+        for _ in range(max(args.warmup, 3)):
             loss = eager_step()
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
