@@ -153,7 +153,10 @@ int na1d_window_index(int32_t* j_out, uint8_t* in_range, int64_t T, int64_t win,
                       int64_t dil, void* stream);
 
 /* Which kernel family the fused entry points would pick for a shape: 0 = CUDA-core kernels,
- * 1 = tcgen05/TMA kernels. Host-only query, no device work. */
+ * 1 = tcgen05/TMA kernels. Host-only query, no device work. The answer assumes one head, no bias and
+ * no bias gradient: more than 32 heads, or 64-channel rows with an effective window above 17 together
+ * with a bias of several heads or its gradient (no shared memory left for them), still move a call
+ * to the CUDA-core kernels. */
 int na1d_fused_kernel_family(int64_t N, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil,
                              int dtype, int backward);
 

@@ -69,7 +69,7 @@ __host__ __device__ inline FwdSmemLayout fwd_layout(int C, int KT, int bias_head
     L.stage_v = round_up(KT * C * 2, 1024);
     L.stage_bytes = 2 * round_up(KT * C * 2, 1024);
     L.misc = L.ring + 2 * L.stage_bytes;
-    L.total = L.misc + 256 + round_up(bias_heads * (kBiasPad + 48) * 4, 256) + 1008;  // misc, bias table, alignment slack
+    L.total = L.misc + 256 + round_up(2 * bias_heads * (kBiasPad + 48) * 4, 256) + 1008;  // misc, two bias tables, alignment slack
     return L;
 }
 
@@ -241,8 +241,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const float inv_T = 1.f / (float)T, inv_H = 1.f / (float)gm.H;
         if (rpb) {
             // bias table of every head, once per CTA (barrier among the 4 softmax warps only)
-            for (int i = r; i < gm.H * kBiasRow; i += 128) {
-                const int hh_ = i / kBiasRow, kk = i - hh_ * kBiasRow - kBiasPad;
+            // two copies, the second shifted by one entry: a thread reads the biases of its two adjacent columns with one
+            // 8-byte load whatever the parity of its first offset
+            for (int i = r; i < 2 * gm.H * kBiasRow; i += 128) {
+                const int copy = i / (gm.H * kBiasRow), j = i - copy * gm.H * kBiasRow;
+                const int hh_ = j / kBiasRow, kk = j - hh_ * kBiasRow - kBiasPad + copy;
                 bias_tab[i] = (kk >= 0 && kk < win && (kk & dmask) == 0) ? __ldg(rpb + hh_ * gm.win + (kk >> dshift)) * kLog2e : 0.f;
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -268,7 +271,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 for (int k = 0; k < 4; ++k) {
                     const bool live = g0 + warp * 32 + fr + 8 * k < rows_total;
                     const int vlr = !live ? 0 : valid_len ? min(T, __ldg(valid_len + min(bq, batch - 1))) : T;
-                    brow[k >> 1][k & 1] = bias_tab + hq * kBiasRow + kBiasPad;
+                    brow[k >> 1][k & 1] = bias_tab + ((fa & 1) ? gm.H * kBiasRow - 1 : 0) + hq * kBiasRow + kBiasPad + fa;
                     jb[k >> 1][k & 1] = tq - left + fa;
                     vle[k >> 1][k & 1] = tq >= vlr ? 0 : vlr;
                     need_mask |= tq < left || tq + (win - 1 - left) >= vlr;
@@ -297,14 +300,15 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
                     for (int g = 0; g < NG; ++g)
 #pragma unroll
-                        for (int hh = 0; hh < 2; ++hh)
+                        for (int hh = 0; hh < 2; ++hh) {
+                            float2 bias2 = make_float2(0.f, 0.f);  // biases of the thread's two adjacent columns of this group
+                            if (rpb) bias2 = *reinterpret_cast<const float2*>(brow[b][hh] + 8 * (g - hh));
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int idx = 4 * g + 2 * hh + e;
                                 const int kc = 8 * (g - hh) + e, kk = kc + fa;
                                 const bool inband = (unsigned)kk < (unsigned)win && (kk & dmask) == 0;
-                                float bias = 0.f;
-                                if (rpb) bias = brow[b][hh][kk];
+                                float bias = e ? bias2.y : bias2.x;
                                 float dot = s[b][idx];
                                 if constexpr (kMasked) {
                                     const unsigned j = (unsigned)(jb[b][hh] + kc);
@@ -315,6 +319,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                                 s[b][idx] = x;
                                 mx[b][hh] = fmaxf(mx[b][hh], x);
                             }
+                        }
             };
             if (need_mask) logits(std::true_type{}); else logits(std::false_type{});
             if (tid == 0) NA1D_FSTAMP(12);
