@@ -66,6 +66,9 @@ struct BwdSmemLayout {
     bool own_out;  // a dedicated 128-row staging buffer for the outputs fits next to everything else
 };
 constexpr int kBiasRowB = 16 + 48;  // per-head table: log2e * rpb[h][kk] at index kk + 16, kk in [-16, 48)
+// Depth of the operand ring: 64-channel tiles fill shared memory with two stages; narrower rows leave room for a third, which
+// takes the TMA load latency (about 3 k cycles under load) out of the loop "batch 2 retires -> refill -> batch 1 -> compute".
+__host__ __device__ constexpr int bwd_stages(int C) { return C == 64 ? 2 : 3; }
 __host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT, int bias_heads, int acc_floats) {
     BwdSmemLayout L;
     L.stage_q = 0;
@@ -73,7 +76,7 @@ __host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT, int bias_head
     L.stage_k = L.stage_do + round_up(kTileM * C * 2, 1024);
     L.stage_v = L.stage_k + round_up(KT * C * 2, 1024);
     L.stage_bytes = L.stage_v + round_up(KT * C * 2, 1024);
-    L.ds = 2 * L.stage_bytes;           // dS [128 queries][KT keys]
+    L.ds = bwd_stages(C) * L.stage_bytes;  // dS [128 queries][KT keys]
     L.p = L.ds + kTileM * KT * 2;       // P  [128 queries][KT keys]
     L.out = L.p + kTileM * KT * 2;
     // misc block, bias table, bias-gradient accumulator, alignment slack
@@ -150,7 +153,7 @@ __host__ __device__ inline BwdSmemLayout bwd_layout_for(int C, int KT, const Geo
 
 struct alignas(8) BwdMisc {
     // ring barriers per stage and per buffer (kQ, kDO, kK, kV): each buffer is refilled as soon as its last reader retires
-    uint64_t full[2][4], empty[2][4];
+    uint64_t full[3][4], empty[3][4];
     uint64_t s_ready, s_free, p_ready, o_ready;
     uint64_t o_free[3];  // per accumulator (dQ, dV, dK): its MMA chain restarts as soon as the epilogue has drained it
     uint64_t acc_done;   // all compute threads have added their last tile to the bias-gradient accumulator
@@ -168,6 +171,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, int stride, int KT,
               int total_tiles) {
     constexpr int NG = tc::band_groups(WB);  // 8-column groups holding the band of a 16-row block
+    constexpr int NS = bwd_stages(C);         // ring depth: tile `it` uses stage it % NS in ring round it / NS
     constexpr int kRowBytes = C * 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -190,7 +194,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int lboq = KT * 16;  // bytes between 8-query groups of the dS matrix
 
     if (tid == 0) {
-        for (int s = 0; s < 2; ++s)
+        for (int s = 0; s < NS; ++s)
             for (int b = 0; b < 4; ++b) { ptx::mbar_init(&misc->full[s][b], 1); ptx::mbar_init(&misc->empty[s][b], 1); }
         ptx::mbar_init(&misc->s_ready, 2);   // S chain and dP chain
         ptx::mbar_init(&misc->s_free, 128);
@@ -235,7 +239,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (lane == 0) {
             int it = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-                const int s = it & 1, k = it >> 1;
+                const int s = it % NS, k = it / NS;
                 const int g0 = tile * stride - right;  // first flattened row of the window
                 uint8_t* st = smem + s * L.stage_bytes;
                 // buffers in the order in which the previous user of this stage releases them: V after batch 1, then K
@@ -268,12 +272,12 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             const int nks = KT / 16;
             // this role's part of batch 1 of tile `jt`: S = Q.K^T -> cols [0,KT) (role 0), dP = dO.V^T -> cols [160,160+KT) (role 1)
             auto batch1_ready = [&](int jt) -> bool {  // non-blocking: have this role's two operands of tile jt landed?
-                const int s = jt & 1, k = jt >> 1;
+                const int s = jt % NS, k = jt / NS;
                 return ptx::mbar_try_wait(&misc->full[s][role == 0 ? kK : kV], k & 1) &&
                        ptx::mbar_try_wait(&misc->full[s][role == 0 ? kQ : kDO], k & 1);
             };
             auto batch1 = [&](int jt) {
-                const int s = jt & 1;
+                const int s = jt % NS;
                 const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
                 ptx::tc_fence_after_sync();
                 const uint64_t da0 = ptx::smem_desc(st + (role == 0 ? L.stage_q : L.stage_do), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
@@ -308,7 +312,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     continue;
                 }
                 polls = 0;
-                const int s = it & 1;
+                const int s = it % NS;
                 const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
                 ptx::tc_fence_after_sync();
                 if (role == 0) NA1D_STAMP(10);
@@ -648,7 +652,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         int it = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
             const int out_row = tile * stride;  // first flattened row this tile stores (dQ, dK and dV alike)
-            uint8_t* st = smem + (it & 1) * L.stage_bytes;
+            uint8_t* st = smem + (it % NS) * L.stage_bytes;
             if (!ptx::mbar_wait_relaxed(&misc->o_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 15); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
             if (tid == 128) NA1D_STAMP(6);
@@ -727,9 +731,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     ptx::tma_store_commit();
                     ptx::tma_store_wait_read();
                     // the staging used the tile's Q, dO and K buffers: only now may the producer refill them
-                    ptx::mbar_arrive(&misc->empty[it & 1][kQ]);
-                    ptx::mbar_arrive(&misc->empty[it & 1][kDO]);
-                    ptx::mbar_arrive(&misc->empty[it & 1][kK]);
+                    ptx::mbar_arrive(&misc->empty[it % NS][kQ]);
+                    ptx::mbar_arrive(&misc->empty[it % NS][kDO]);
+                    ptx::mbar_arrive(&misc->empty[it % NS][kK]);
                     NA1D_STAMP(7);
                 }
             }
