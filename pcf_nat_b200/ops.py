@@ -39,7 +39,7 @@ def _shape3(x):
 
 
 def _band_call(fn_name, out, a, b, N, T, C, win, left, dil, ref):
-    with torch.cuda.device(ref.device):
+    with _on_device(ref.device):
         check(getattr(_L, fn_name)(_p(out), _p(a), _p(b), N, T, C, win, left, dil, _dtype_code(ref), _stream(ref)),
               fn_name)
     return out
@@ -99,8 +99,25 @@ def v_backward(attn, result_gd, win, left, dil=1):
 def _prep_rpb(rpb, heads, win, dev):
     if rpb is None:
         return None
-    r = rpb.detach().to(device=dev, dtype=torch.float32).reshape(heads, win).contiguous()
-    return r
+    r = rpb.detach()
+    if r.dtype != torch.float32 or r.device != dev:
+        r = r.to(device=dev, dtype=torch.float32)
+    return r.reshape(heads, win).contiguous()
+
+
+class _on_device:
+    """``torch.cuda.device(dev)`` only when ``dev`` is not already current (the context manager costs ~10 us per call)."""
+
+    def __init__(self, dev):
+        self.ctx = None if dev.index == torch.cuda.current_device() else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
 
 
 def _prep_valid(valid_len, batch, dev):
@@ -120,7 +137,7 @@ def fused_forward(q, k, v, win, left, dil=1, scale=1.0, rpb=None, valid_len=None
     lse = torch.empty((N, T), dtype=torch.float32, device=q.device) if need_lse else None
     r = _prep_rpb(rpb, heads, win, q.device)
     vl = _prep_valid(valid_len, N // max(heads, 1), q.device)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         check(_L.na1d_fused_forward(_p(o), _p(lse), _p(q), _p(k), _p(v), _p(r), _p(vl), N, heads, T, C, win, left,
                                     dil, float(scale), _dtype_code(q), _stream(q)), "na1d_fused_forward")
     return o, lse
@@ -137,7 +154,7 @@ def fused_backward(d_o, q, k, v, o, lse, win, left, dil=1, scale=1.0, rpb=None, 
     r = _prep_rpb(rpb, heads, win, q.device)
     vl = _prep_valid(valid_len, N // max(heads, 1), q.device)
     d_rpb = torch.zeros((heads, win), dtype=torch.float32, device=q.device) if need_d_rpb else None
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         check(_L.na1d_fused_backward(_p(dq), _p(dk), _p(dv), _p(d_rpb), _p(d_o), _p(q), _p(k), _p(v), _p(o), _p(lse),
                                      _p(r), _p(vl), _p(delta), N, heads, T, C, win, left, dil, float(scale),
                                      _dtype_code(q), _stream(q)), "na1d_fused_backward")
