@@ -828,6 +828,7 @@ cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void*
                          const void* v, const float* lse, const float* rpb, const int* valid_len, float* scratch,
                          size_t scratch_floats, const Geometry& gm, int dtype, cudaStream_t st) {
     if (!tc_bwd_supports(gm, rpb != nullptr, d_rpb != nullptr)) return cudaErrorInvalidValue;
+    bind_primary_context();
     const int weff = tc::eff_window(gm.win, gm.dil);
     const int KT = round_up(kTileM + weff - 1, 16);
     const int stride = kTileM - (weff - 1);

@@ -231,6 +231,7 @@ __device__ __forceinline__ float quad_max(float x) {
 // Tensor map over a dense (N, T, C) 16-bit tensor viewed as dims (C, T, N), box (C, rows, 1).
 bool make_row_tile_map(CUtensorMap* map, const void* base, int dtype, int N, int T, int C, int box_rows);
 int device_sm_count();
+void bind_primary_context();
 bool pdl_enabled();
 int pdl_mode();
 

@@ -474,6 +474,7 @@ bool tc_fwd_supports(const Geometry& gm) {
 cudaError_t tc_fused_fwd(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
                          const int* valid_len, const Geometry& gm, int dtype, cudaStream_t st) {
     if (!tc_fwd_supports(gm)) return cudaErrorInvalidValue;
+    bind_primary_context();
     const int weff = tc::eff_window(gm.win, gm.dil);
     const int KT = round_up(kTileM + weff - 1, 16);
     const int rows = gm.N * gm.T;  // the tensors are tiled as one (N*T, C) matrix

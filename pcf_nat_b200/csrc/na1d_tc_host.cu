@@ -49,6 +49,13 @@ int pdl_mode() {  // 0 off, 1 both kernels, 2 forward only, 3 backward only
 }
 bool pdl_enabled() { return pdl_mode() != 0; }
 
+// The tensor-map encoder is a DRIVER call and needs the device's primary context current on the calling thread. A thread that
+// has made no runtime call yet (an autograd worker whose first CUDA work is this library) has none: bind it explicitly.
+void bind_primary_context() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+}
+
 int device_sm_count() {
     static int cached[64] = {0};
     int dev = 0;

@@ -120,3 +120,17 @@ def test_extractor_fused_equals_unfused_chain():
     for i in (1, 2):
         ref = out[1][i]
         assert float((out[0][i] - ref).abs().max()) <= 5e-2 * max(1e-3, float(ref.abs().max()))
+
+
+def test_backward_is_first_cuda_work_of_its_thread():
+    """The autograd worker thread may reach the operator's backward before it has made any CUDA runtime call: the library
+    binds the device's context itself before it encodes tensor maps (a driver call). Run in a fresh process so that the
+    worker thread really is fresh."""
+    import subprocess
+    code = (
+        "import sys, torch; sys.path.insert(0, %r); import pcf_nat_b200\n"
+        "q, k, v = (torch.randn(8, 200, 32).to(torch.bfloat16).cuda().requires_grad_(True) for _ in range(3))\n"
+        "o = pcf_nat_b200.na1d_fused(q, k, v, 7, 3, 1, 1.0, None, None, 4)\n"
+        "o.backward(torch.ones_like(o)); torch.cuda.synchronize(); print('ok', float(q.grad.float().abs().sum()) > 0)\n" % ROOT)
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "ok True" in out.stdout, out.stderr[-2000:]
