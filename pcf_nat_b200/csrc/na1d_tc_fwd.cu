@@ -238,6 +238,14 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
         const float sc = gm.scale * kLog2e;
         const float mask2 = kMaskValue * kLog2e;
+        // which of the thread's fragment slots are neighbours: slot (g, hh, e) is window offset 8 (g - hh) + e + fa, the same
+        // for every tile, so the band test is one bit of a per-thread constant (class c = 2 (g - hh + 1) + e)
+        uint32_t band_bits = 0;
+#pragma unroll
+        for (int c = 0; c < 2 * (NG + 1); ++c) {
+            const int kk = 8 * ((c >> 1) - 1) + (c & 1) + fa;
+            if ((unsigned)kk < (unsigned)win && (kk & dmask) == 0) band_bits |= 1u << c;
+        }
         const float inv_T = 1.f / (float)T, inv_H = 1.f / (float)gm.H;
         if (rpb) {
             // bias table of every head, once per CTA (barrier among the 4 softmax warps only)
@@ -306,8 +314,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int idx = 4 * g + 2 * hh + e;
-                                const int kc = 8 * (g - hh) + e, kk = kc + fa;
-                                const bool inband = (unsigned)kk < (unsigned)win && (kk & dmask) == 0;
+                                const int kc = 8 * (g - hh) + e;  // window offset minus the lane constant fa
+                                const bool inband = (band_bits >> (2 * (g - hh + 1) + e)) & 1u;
                                 float bias = e ? bias2.y : bias2.x;
                                 float dot = s[b][idx];
                                 if constexpr (kMasked) {
