@@ -1,18 +1,28 @@
 #!/usr/bin/env python
-"""Benchmark of the NA1D hot path: fused forward+backward queries/s at the PCF-NAT training shape.
+"""Benchmark of the NA1D hot path and of the model-level workloads built on it.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--replays R]
+    python bench.py --sweep OUT.md [--quick]          # the window/dilation/length/head-dim sweep as a markdown table
 
-One "step" is one forward+backward pass of the fused neighbourhood-attention operator over one
-batch of synthetic inputs (seeded N(0,1) stand-ins for log-mel features). Rank 0 prints one JSON
-line. N>1 is launched by torchrun, one rank per GPU; the op has no exchange step, so every rank
-runs the same per-GPU batch (weak scaling) and the only collectives are the timing barrier and the
-max-over-ranks reduction of the elapsed time.
+Operator workloads (default: the PCF-NAT training shape): one "step" is one forward+backward pass of the fused
+neighbourhood-attention operator over one batch of synthetic inputs (seeded N(0,1) stand-ins for log-mel features).
+The K steps are captured once in a CUDA graph over rotating buffer sets larger than L2; the graph is replayed R times,
+every replay timed with CUDA events on the launching stream, and the MEDIAN replay gives `ms_per_step` (so
+`ms_per_step * steps` is one replay of exactly K steps). N>1 is launched by torchrun, one rank per GPU; the operator has
+no exchange step, so every rank runs the same per-GPU batch (weak scaling) and the only collectives are the timing
+barrier and the max-over-ranks reduction of the elapsed time.
+
+Model workloads (`cfg5_train`, `cfg5_embed`): the PCF-NAT-style extractor of `pcf_nat_b200.model`, batch-sharded over the
+ranks with an NCCL gradient all-reduce (training) or an embedding all-gather (extraction); see `pcf_nat_b200.model_bench`.
+
+Rank 0 prints one JSON line.
 """
 import argparse
 import ctypes
+import itertools
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -23,18 +33,20 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# name -> (batch, heads, T, C, win, dil, backward)
+# name -> batch, heads, T, C, win, dil, backward
 WORKLOADS = {
-    # BASELINE configs[1]: the shape the metric is quoted on
+    # the shape the headline metric is quoted on: 128 utterances x 4 heads, 200 frames, head dim 64, window 7
     "cfg2_train_B128_H4_L200_D64_w7": dict(B=128, H=4, T=200, C=64, win=7, dil=1, bwd=True),
-    # BASELINE configs[3]: long-utterance forward
+    # long-utterance inference: 16 utterances x 8 heads, 3000 frames, window 15, forward only
     "cfg4_long_B16_H8_L3000_D64_w15": dict(B=16, H=8, T=3000, C=64, win=15, dil=1, bwd=False),
     # the shape the reference's own yaml trains (configs/pcf_nat4x4.yaml:16-17,50-53)
     "real_B512_H16_L150_D16_w27": dict(B=512, H=16, T=150, C=16, win=27, dil=1, bwd=True),
 }
+MODEL_WORKLOADS = ("cfg5_train", "cfg5_embed")
 DEFAULT = "cfg2_train_B128_H4_L200_D64_w7"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from one ncu --set full capture of this
-# same command (profiles/tcgen05_fused_cfg2_train.md). Writes still resident in L2 when the kernel ends are not in it.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from an `ncu --set full` capture of this
+# command; a constant taken from that capture, not something this run measures (writes still resident in L2 when the
+# kernel ends are not in it)
 NCU_TRAFFIC = {"cfg2_train_B128_H4_L200_D64_w7": 52.92e6 + 4.00e6}
 L2_BYTES = 126 * 1024 * 1024
 
@@ -43,6 +55,11 @@ def algorithmic_bytes(N, T, C, bwd):
     fwd = 8 * N * T * C + 4 * N * T          # read q,k,v; write o; write lse
     back = 16 * N * T * C + 4 * N * T        # read q,k,v,o,dO,lse; write dq,dk,dv
     return fwd, (back if bwd else 0)
+
+
+def moved_bytes_bwd(N, T, C):
+    """What the tcgen05 backward has to move: it never reads o (delta is recomputed from P and dP)."""
+    return 14 * N * T * C + 4 * N * T
 
 
 def peaks():
@@ -102,11 +119,11 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def make_host_inputs(w, seed=1):
+def make_host_inputs(w, seed=1, dtype=torch.bfloat16, scale=1.0):
     N = w["B"] * w["H"]
     g = torch.Generator().manual_seed(seed)
     shape = (N, w["T"], w["C"])
-    return [torch.randn(shape, generator=g).to(torch.bfloat16) for _ in range(4)]  # q, k, v, dO
+    return [(torch.randn(shape, generator=g) * scale).to(dtype) for _ in range(4)]  # q, k, v, dO
 
 
 # ------------------------------------------------------------------------------------------ reference arm
@@ -156,7 +173,8 @@ def run_reference(args, w, name):
         "value": val, "unit": "queries/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "sample": "%d of %d sequences per step" % (n_s, N)},
+        "config": {"workload": name, "N": N, "T": w["T"], "C": w["C"], "win": w["win"], "dil": w["dil"],
+                   "sample": "%d of %d sequences per step" % (n_s, N)},
         "cpu_baseline": {"value": val, "unit": "queries/s", "cores": cores, "kind": "port",
                          "sample": "%d of %d sequences x %d steps, fp32 eager oracle" % (n_s, N, args.steps)},
         "e2e": {"value": val, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -164,20 +182,102 @@ def run_reference(args, w, name):
     print(json.dumps(line), flush=True)
 
 
-# ------------------------------------------------------------------------------------------ our arm
-class BufferSet:
-    def __init__(self, w, dev, host):
-        N = w["B"] * w["H"]
-        self.q, self.k, self.v, self.d_o = (x.to(dev) for x in host)
-        e = lambda: torch.empty_like(self.q)
-        self.o, self.dq, self.dk, self.dv = e(), e(), e(), e()
-        self.lse = torch.empty((N, w["T"]), dtype=torch.float32, device=dev)
-        self.delta = torch.empty((N, w["T"]), dtype=torch.float32, device=dev)
+# ------------------------------------------------------------------------------------------ operator timing
+class OpBench:
+    """Rotating device buffer sets of one operator shape and graph-replay timing through the C ABI."""
+
+    def __init__(self, L, dev, N, H, T, C, win, dil, dtype, bwd, host=None, seed=2, scale=1.0, max_sets=8):
+        self.L, self.dev = L, dev
+        self.N, self.H, self.T, self.C, self.win, self.dil, self.bwd = N, H, T, C, win, dil, bwd
+        self.left = win - 1 - win // 2
+        self.code = 0 if dtype == torch.bfloat16 else 1
+        self.per_set = (9 if bwd else 4) * N * T * C * 2
+        # the other sets in the rotation exceed L2 several times over
+        self.n_sets = int(max(4, min(max_sets, (3 * L2_BYTES) // self.per_set + 2)))
+        g = torch.Generator(device=dev).manual_seed(seed)
+        self.sets = []
+        for _ in range(self.n_sets):
+            if host is not None:
+                q, k, v, d_o = (x.to(dev) for x in host)
+            else:
+                q, k, v, d_o = ((torch.randn(N, T, C, device=dev, generator=g) * scale).to(dtype) for _ in range(4))
+            s = dict(q=q, k=k, v=v, d_o=d_o, o=torch.empty_like(q), lse=torch.empty(N, T, device=dev))
+            if bwd:
+                s.update(dq=torch.empty_like(q), dk=torch.empty_like(q), dv=torch.empty_like(q), delta=torch.empty(N, T, device=dev))
+            self.sets.append(s)
+        self.stream = torch.cuda.Stream(dev)
+
+    def _fwd(self, s, st):
+        P = lambda t: ctypes.c_void_p(t.data_ptr())
+        rc = self.L.na1d_fused_forward(P(s["o"]), P(s["lse"]), P(s["q"]), P(s["k"]), P(s["v"]), None, None, self.N, self.H,
+                                       self.T, self.C, self.win, self.left, self.dil, 1.0, self.code, st)
+        assert rc == 0, rc
+
+    def _bwd(self, s, st):
+        P = lambda t: ctypes.c_void_p(t.data_ptr())
+        rc = self.L.na1d_fused_backward(P(s["dq"]), P(s["dk"]), P(s["dv"]), None, P(s["d_o"]), P(s["q"]), P(s["k"]), P(s["v"]),
+                                        P(s["o"]), P(s["lse"]), None, None, P(s["delta"]), self.N, self.H, self.T, self.C,
+                                        self.win, self.left, self.dil, 1.0, self.code, st)
+        assert rc == 0, rc
+
+    def run_steps(self, n, what="both"):
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        for i in range(n):
+            s = self.sets[i % self.n_sets]
+            if what in ("both", "fwd"):
+                self._fwd(s, st)
+            if self.bwd and what in ("both", "bwd"):
+                self._bwd(s, st)
+
+    def timed(self, steps, what, replays, sync_ranks=None):
+        """Median device time (ms) of one replay of a CUDA graph holding `steps` steps; every replay timed by events."""
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(self.stream):
+            self.run_steps(2, what)                      # lazy module load / first-use set-up outside capture
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=self.stream):
+                self.run_steps(steps, what)
+            g.replay()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
+            torch.cuda.synchronize()
+            if sync_ranks:
+                sync_ranks()
+            ev[0].record(self.stream)
+            for i in range(replays):
+                g.replay()
+                ev[i + 1].record(self.stream)
+            torch.cuda.synchronize()
+            if sync_ranks:
+                sync_ranks()
+        ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(replays)]
+        return statistics.median(ms), min(ms), max(ms)
+
+
+def spot_check(ob, dtype):
+    """A few sequences of buffer set 0 against the fp32 oracle (checker only; outside every timed region)."""
+    from oracle import na1d_oracle as orc
+    s = ob.sets[0]
+    tol = 2e-2 if dtype == torch.bfloat16 else 5e-3
+    worst = 0.0
+    for n0 in sorted({0, ob.N // 2, ob.N - 1}):
+        f = lambda x: x[n0:n0 + 1].float().cpu()
+        if ob.bwd:
+            o_r, dq_r, dk_r, dv_r, _ = orc.na1d_fused_with_grads(f(s["q"]), f(s["k"]), f(s["v"]), f(s["d_o"]), ob.win, ob.left, ob.dil)
+            pairs = [("o", s["o"], o_r, 1.0), ("dq", s["dq"], dq_r, None), ("dk", s["dk"], dk_r, None), ("dv", s["dv"], dv_r, None)]
+        else:
+            pairs = [("o", s["o"], orc.na1d_fused(f(s["q"]), f(s["k"]), f(s["v"]), ob.win, ob.left, ob.dil), 1.0)]
+        for name, got, ref, mag in pairs:
+            err = float((f(got) - ref).abs().max())
+            bound = tol * (mag if mag is not None else max(1.0, float(ref.abs().max())))
+            if not err <= bound:
+                raise SystemExit("bench: %s of sequence %d differs from the oracle by %.3e (bound %.1e)" % (name, n0, err, bound))
+            worst = max(worst, err / bound)
+    return worst
 
 
 def run_ours(args, w, name):
     import torch.distributed as dist
-    from pcf_nat_b200 import _lib, na1d_fused
+    from pcf_nat_b200 import _lib, na1d_fused, ops
     L = _lib.lib()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -194,63 +294,26 @@ def run_ours(args, w, name):
     left = win - 1 - win // 2
     fwd_b, bwd_b = algorithmic_bytes(N, T, C, w["bwd"])
     host = make_host_inputs(w, seed=1 + rank)
-    per_set = (9 if w["bwd"] else 4) * N * T * C * 2
-    n_sets = max(4, (3 * L2_BYTES) // per_set + 2)   # the other sets in the rotation exceed L2 several times over
-    sets = [BufferSet(w, dev, host) for _ in range(n_sets)]
-    P = lambda t: ctypes.c_void_p(t.data_ptr())
-    stream = torch.cuda.Stream(dev)
+    ob = OpBench(L, dev, N, H, T, C, win, dil, torch.bfloat16, w["bwd"], host=host, max_sets=64)
+    sync_ranks = dist.barrier if world > 1 else None
 
-    def launch_fwd(s, st):
-        rc = L.na1d_fused_forward(P(s.o), P(s.lse), P(s.q), P(s.k), P(s.v), None, None, N, H, T, C, win, left, dil,
-                                  1.0, 0, st)
-        assert rc == 0, rc
-
-    def launch_bwd(s, st):
-        rc = L.na1d_fused_backward(P(s.dq), P(s.dk), P(s.dv), None, P(s.d_o), P(s.q), P(s.k), P(s.v), P(s.o),
-                                   P(s.lse), None, None, P(s.delta), N, H, T, C, win, left, dil, 1.0, 0, st)
-        assert rc == 0, rc
-
-    def run_steps(n, what="both", start=0):
-        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        for i in range(n):
-            s = sets[(start + i) % n_sets]
-            if what in ("both", "fwd"):
-                launch_fwd(s, st)
-            if w["bwd"] and what in ("both", "bwd"):
-                launch_bwd(s, st)
-
-    def timed(n, what):
-        """Device time of n steps replayed from one CUDA graph, ms, max over ranks."""
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(stream):
-            run_steps(2, what)                      # lazy module load / first-use setup outside capture
-            torch.cuda.synchronize()
-            with torch.cuda.graph(g, stream=stream):
-                run_steps(n, what)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize()
-            e0.record(stream)
-            g.replay()
-            e1.record(stream)
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-            ms = e0.elapsed_time(e1)
-        return parallel.max_over_ranks(ms, dev)
-
-    with torch.cuda.stream(stream):
-        run_steps(args.warmup)
+    with torch.cuda.stream(ob.stream):
+        ob.run_steps(max(args.warmup, 3))
         torch.cuda.synchronize()
+    ops.device_status()
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms_total = timed(args.steps, "both")
-    ms_fwd = timed(args.steps, "fwd")
-    ms_bwd = timed(args.steps, "bwd") if w["bwd"] else 0.0
+    R = args.replays
+    med_total, lo_total, hi_total = ob.timed(args.steps, "both", R, sync_ranks)
+    med_fwd, _, _ = ob.timed(args.steps, "fwd", R, sync_ranks)
+    med_bwd = ob.timed(args.steps, "bwd", R, sync_ranks)[0] if w["bwd"] else 0.0
+    ops.device_status()   # an expired bounded wait would have ended kernels early: such a timing must not be reported
+    ms_total = parallel.max_over_ranks(med_total, dev)
+    ms_fwd = parallel.max_over_ranks(med_fwd, dev)
+    ms_bwd = parallel.max_over_ranks(med_bwd, dev)
+    checked = spot_check(ob, torch.bfloat16)
 
     # ---- end to end through the public torch API with HOST buffers: every step copies its q, k, v, dO from pinned host
     # memory and its o, dq, dk, dv back. Three streams and two buffer slots, as a training input pipeline would run it:
@@ -275,6 +338,7 @@ def run_ours(args, w, name):
             ev_up[sl].record(s_up)
         with torch.cuda.stream(s_run):
             s_run.wait_event(ev_up[sl])
+            s_run.wait_event(ev_down[sl])               # the download of this slot's previous results is done
             q, k, v, d_o = (x.detach() for x in dev_in[sl])
             if w["bwd"]:
                 q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
@@ -304,8 +368,9 @@ def run_ours(args, w, name):
     s_down.wait_stream(s_up)
     e1.record(s_down)
     torch.cuda.synchronize()
-    ms_e2e = e0.elapsed_time(e1)
-    ms_e2e = parallel.max_over_ranks(ms_e2e, dev)
+    ms_e2e_rank = e0.elapsed_time(e1)
+    ms_e2e = parallel.max_over_ranks(ms_e2e_rank, dev)
+    ops.device_status()
     clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
@@ -316,32 +381,60 @@ def run_ours(args, w, name):
         dom_bytes = bwd_b if w["bwd"] else fwd_b
         ach = dom_bytes / (dom_ms * 1e-3) / 1e9
         fam = L.na1d_fused_kernel_family(N, T, C, win, left, dil, 0, 1 if w["bwd"] else 0)
+        h2d, d2h = 4 * N * T * C * 2, n_out * N * T * C * 2
         line = {
             "metric": "NA1D fwd+bwd queries/sec/GPU" if w["bwd"] else "NA1D fwd queries/sec/GPU",
             "value": world * queries * args.steps / (ms_total * 1e-3), "unit": "queries/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": name, "N": N, "T": T, "C": C, "win": win, "dil": dil,
-                       "l2": "rotating %d buffer sets of %.0f MB (> L2 between reuses)" % (n_sets, per_set / 1e6),
-                       "launch": "one CUDA graph of all timed steps", "kernel_family": ["cuda-core", "tcgen05"][fam]},
+                       "l2": "rotating %d buffer sets of %.0f MB (> L2 between reuses)" % (ob.n_sets, ob.per_set / 1e6),
+                       "launch": "one CUDA graph of the %d timed steps, replayed %d times; ms_per_step = median replay / steps "
+                                 "(min %.4f, max %.4f ms per step on rank 0)" % (args.steps, R, lo_total / args.steps, hi_total / args.steps),
+                       "kernel_family": ["cuda-core", "tcgen05"][fam],
+                       "checked": "outputs of 3 sequences against the fp32 oracle after the timed region (worst error/bound %.2f); "
+                                  "device status word clean" % checked},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                         "traffic": NCU_TRAFFIC.get(name), "peak_kind": peak_kind,
+                         "traffic": NCU_TRAFFIC.get(name),
+                         "traffic_source": "ncu capture of this kernel at this workload, a constant (not measured by this run)",
+                         "peak_kind": peak_kind,
                          "kernel": ("fused backward" if w["bwd"] else "fused forward") + (" (tcgen05)" if fam == 1 else " (cuda-core)"),
                          "algorithmic_bytes_per_launch": dom_bytes},
             "roofline_step": {"fwd_us": 1e3 * ms_fwd / args.steps, "bwd_us": 1e3 * ms_bwd / args.steps,
                               "fwd_frac": fwd_b / (ms_fwd / args.steps * 1e-3) / 1e9 / peak,
                               "step_frac": (fwd_b + bwd_b) / (ms_total / args.steps * 1e-3) / 1e9 / peak},
             "e2e": {"value": world * queries * e2e_steps / (ms_e2e * 1e-3), "unit": "queries/s",
-                    "h2d_bytes_per_step": 4 * N * T * C * 2, "d2h_bytes_per_step": n_out * N * T * C * 2,
-                    "steps": e2e_steps},
-            "gpu_launches": args.steps * (3 if w["bwd"] else 1),
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "rank0_h2d_gbs": h2d * e2e_steps / (ms_e2e_rank * 1e-3) / 1e9,
+                    "rank0_d2h_gbs": d2h * e2e_steps / (ms_e2e_rank * 1e-3) / 1e9,
+                    "bound": "host<->device copies (uploads and downloads overlap each other and the kernels)"},
+            "gpu_launches": args.steps * (2 if w["bwd"] else 1),
             "clocks": clocks,
         }
+        if w["bwd"] and fam == 1:
+            moved = moved_bytes_bwd(N, T, C)
+            line["roofline"]["moved_bytes_per_launch"] = moved
+            line["roofline"]["frac_moved_bytes"] = moved / (dom_ms * 1e-3) / 1e9 / peak
         line["cpu_baseline"] = cpu_baseline(w) if world == 1 and not args.no_cpu_baseline else None
-        line["reference_cuda"] = reference_cuda_baseline(w, dev, host) if world == 1 else None
+        if world == 1:
+            line["reference_cuda"] = reference_cuda_baseline(w, dev, host)
+            line["compat_pair"] = compat_pair_timing(L, w, dev, host, line["reference_cuda"])
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def _time_fn(fn, iters, stream=None):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(iters):
+        fn()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return 1e3 * e0.elapsed_time(e1) / iters
 
 
 def reference_cuda_baseline(w, dev, host, iters=30):
@@ -389,18 +482,59 @@ def reference_cuda_baseline(w, dev, host, iters=30):
     res = {}
     with torch.cuda.stream(torch.cuda.default_stream(dev)):   # the reference launches on the legacy default stream
         for name, fn in (("kernels_only", kernels_only), ("unfused_chain", chain)):
-            for _ in range(3):
-                fn()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(iters):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
-            us = 1e3 * e0.elapsed_time(e1) / iters
+            us = _time_fn(fn, iters)
             res[name] = {"us_per_step": us, "queries_per_s": N * T / (us * 1e-6)}
     res["note"] = "reference na1d_tensorcore bf16 kernels compiled for sm_100a, same GPU, same shape, single buffer set (L2-warm)"
+    return res
+
+
+def compat_pair_timing(L, w, dev, host, ref, iters=30):
+    """The unfused drop-in pair of this library (the six entry points an unmodified model file reaches through
+    `getNA1dFunction`), timed like `reference_cuda_baseline`: the six launches alone and inside the unfused chain."""
+    N, T, C, win, dil = w["B"] * w["H"], w["T"], w["C"], w["win"], w["dil"]
+    if not w["bwd"]:
+        return None
+    left = win - 1 - win // 2
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    q, k, v, d_o = (x.to(dev) for x in host)
+    attn = torch.empty(N, T, win, dtype=torch.float32, device=dev)
+    attn_gd = torch.empty_like(attn)
+    out, q_gd, k_gd, v_gd = (torch.empty_like(q) for _ in range(4))
+    j = torch.arange(T, device=dev).unsqueeze(1) + (torch.arange(win, device=dev).unsqueeze(0) - left) * dil
+    mask = torch.where((j < 0) | (j >= T), -100.0, 0.0).unsqueeze(0)
+    stream = torch.cuda.Stream(dev)
+    res = {}
+    with torch.cuda.stream(stream):
+        st = ctypes.c_void_p(stream.cuda_stream)
+
+        def call(fn, a, b, c):
+            rc = getattr(L, fn)(P(a), P(b), P(c), N, T, C, win, left, dil, 0, st)
+            assert rc == 0, (fn, rc)
+
+        def kernels_only():
+            call("na1d_qk_forward", attn, q, k)
+            call("na1d_av_forward", out, attn, v)
+            call("na1d_a_backward", attn_gd, d_o, v)
+            call("na1d_v_backward", v_gd, attn, d_o)
+            call("na1d_q_backward", q_gd, attn_gd, k)
+            call("na1d_k_backward", k_gd, attn_gd, q)
+
+        def chain():
+            call("na1d_qk_forward", attn, q, k)
+            p = torch.softmax(attn + mask, -1)
+            call("na1d_av_forward", out, p, v)
+            call("na1d_a_backward", attn_gd, d_o, v)
+            call("na1d_v_backward", v_gd, p, d_o)
+            ds = (p * (attn_gd - (p * attn_gd).sum(-1, keepdim=True))).contiguous()
+            call("na1d_q_backward", q_gd, ds, k)
+            call("na1d_k_backward", k_gd, ds, q)
+
+        for name, fn in (("kernels_only", kernels_only), ("unfused_chain", chain)):
+            us = _time_fn(fn, iters, stream)
+            res[name] = {"us_per_step": us, "queries_per_s": N * T / (us * 1e-6)}
+            if ref and name in ref:
+                res[name]["speedup_vs_reference_cuda"] = ref[name]["us_per_step"] / us
+    res["note"] = "the six unfused entry points of this library, same shape and buffers as reference_cuda (single buffer set, L2-warm)"
     return res
 
 
@@ -431,16 +565,70 @@ def cpu_baseline(w, budget_s=12.0):
             "sample": "%d of %d sequences x %d passes (%.1f s), fp32 eager oracle" % (n_s, N, n, dt)}
 
 
+# ------------------------------------------------------------------------------------------ shape sweep
+def run_sweep(args):
+    """Forward and forward+backward time of every (dtype, window, dilation, length, head dim) of the sweep
+    (64 utterances x 4 heads, inputs scaled by D^-1/4) plus the named shapes, as a markdown table."""
+    from pcf_nat_b200 import _lib, ops
+    if not torch.cuda.is_available():
+        raise SystemExit("the sweep needs a CUDA device")
+    L = _lib.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peak, peak_kind = peaks()
+    cases = list(itertools.product((torch.bfloat16, torch.float16), (3, 7, 15, 31), (1, 2, 4), (200, 400, 1000), (32, 64)))
+    if args.quick:
+        cases = [c for c in cases if c[0] == torch.bfloat16 and c[3] in (200, 1000) and c[4] == 64 and c[1] in (7, 15, 31)]
+    named = [("training shape", torch.bfloat16, 7, 1, 200, 64, 128, 4), ("long utterance", torch.bfloat16, 15, 1, 3000, 64, 16, 8),
+             ("reference yaml", torch.bfloat16, 27, 1, 150, 16, 512, 16)]
+    lines = ["fractions are of the %s copy bandwidth %.1f GB/s; graph of 20 steps, median of 11 replays" % (peak_kind, peak), "",
+             "| case | dtype | win | dil | L | D | N | family fwd/bwd | fwd us | fwd frac | fwd+bwd us | fwd+bwd Gq/s | fwd+bwd frac |",
+             "|---|---|---|---|---|---|---|---|---|---|---|---|---|"]
+    print("\n".join(lines), flush=True)
+
+    def row(tag, dtype, win, dil, T, C, b, h):
+        N = b * h
+        ob = OpBench(L, dev, N, h, T, C, win, dil, dtype, True, scale=C ** -0.25)
+        fam = "%s/%s" % tuple(["cuda-core", "tcgen05"][L.na1d_fused_kernel_family(N, T, C, win, ob.left, dil, ob.code, bw)] for bw in (0, 1))
+        t_f = 1e3 * ob.timed(20, "fwd", 11)[0] / 20
+        t_b = 1e3 * ob.timed(20, "both", 11)[0] / 20
+        ops.device_status()
+        fb, tb = 8 * N * T * C + 4 * N * T, 24 * N * T * C + 8 * N * T
+        lines.append("| %s | %s | %d | %d | %d | %d | %d | %s | %.1f | %.2f | %.1f | %.2f | %.2f |" % (
+            tag, "bf16" if ob.code == 0 else "fp16", win, dil, T, C, N, fam, t_f, fb / t_f / 1e3 / peak, t_b,
+            N * T / t_b / 1e3, tb / t_b / 1e3 / peak))
+        print(lines[-1], flush=True)
+        del ob
+        torch.cuda.empty_cache()
+
+    for tag, dtype, win, dil, T, C, b, h in named:
+        row(tag, dtype, win, dil, T, C, b, h)
+    for dtype, win, dil, T, C in cases:
+        row("sweep", dtype, win, dil, T, C, 64, 4)
+    with open(args.sweep, "w") as f:
+        f.write("\n".join(lines) + "\n")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--replays", type=int, default=101, help="replays of the graph of --steps steps; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=DEFAULT, choices=list(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT, choices=list(WORKLOADS) + list(MODEL_WORKLOADS))
     ap.add_argument("--ref-budget", type=float, default=90.0, help="seconds of CPU work for --impl reference")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", default=None, metavar="OUT.md", help="run the shape sweep and write the table to this file")
+    ap.add_argument("--quick", action="store_true", help="with --sweep: a bf16, D=64 subset")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"], help="model workloads: split or replicate the batch")
+    ap.add_argument("--attention", default="fused", choices=["fused", "unfused"], help="model workloads: operator variant")
     args = ap.parse_args()
+    if args.sweep:
+        return run_sweep(args)
+    if args.workload in MODEL_WORKLOADS:
+        from pcf_nat_b200 import model_bench
+        return model_bench.run(args)
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, w, args.workload)

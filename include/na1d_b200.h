@@ -37,7 +37,7 @@ extern "C" {
 #define NA1D_ERR_BAD_HEADS (-5)      /* heads <= 0 or N % heads != 0 */
 #define NA1D_ERR_MISALIGNED (-6)     /* a 16-bit tensor pointer is not 16-byte aligned */
 #define NA1D_ERR_CUDA (-7)           /* a CUDA runtime/driver call failed; see na1d_last_cuda_error() */
-#define NA1D_ERR_DEVICE_TIMEOUT (-8) /* a bounded wait inside a kernel expired (reported by na1d_check_status) */
+#define NA1D_ERR_DEVICE_TIMEOUT (-8) /* a bounded wait inside a kernel expired (reported by na1d_device_status) */
 #define NA1D_ERR_TOO_LARGE (-9)      /* problem exceeds a fixed capacity of the entry point */
 #define NA1D_ERR_UNSUPPORTED (-10)   /* the kernel family forced by na1d_set_kernel_family cannot run this shape */
 

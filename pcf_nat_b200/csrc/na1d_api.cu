@@ -119,10 +119,15 @@ int na1d_set_kernel_family(int family) {
 }
 
 int na1d_device_status(void) {
+    // both words are read (and cleared) before anything is reported; an expired wait in either kernel wins over a failed read
     const int v = na1d::tc_read_status();
     const int w = na1d::tc_bwd_read_status();
-    if (v < 0 || w < 0) return cuda_status(cudaGetLastError());
-    return (v == 0 && w == 0) ? NA1D_OK : NA1D_ERR_DEVICE_TIMEOUT;
+    if (v > 0 || w > 0) return NA1D_ERR_DEVICE_TIMEOUT;
+    if (v < 0 || w < 0) {
+        const cudaError_t e = cudaGetLastError();
+        return cuda_status(e == cudaSuccess ? cudaErrorUnknown : e);
+    }
+    return NA1D_OK;
 }
 
 int na1d_fused_forward(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,

@@ -39,14 +39,6 @@ namespace na1d {
 // Device status word of this translation unit (device symbols are per file without relocatable device code).
 __device__ int g_tc_bwd_status = 0;
 
-#ifdef NA1D_TIMELINE
-// Development aid (not compiled by default): clock64 stamps of CTA 0, [tile][slot].
-__device__ long long g_bwd_timeline[64 * 16];
-#define NA1D_STAMP(slot) do { if (blockIdx.x == 0 && it < 64) g_bwd_timeline[it * 16 + (slot)] = clock64(); } while (0)
-#else
-#define NA1D_STAMP(slot) do { } while (0)
-#endif
-
 namespace {
 
 using tc::kTileM;
@@ -193,7 +185,29 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int win = tc::eff_window(gm.win, dil), left = gm.left * dil, right = (gm.win - 1 - gm.left) * dil, T = gm.T;
     const int lboq = KT * 16;  // bytes between 8-query groups of the dS matrix
 
-    if (tid == 0) {
+    // Loads of tile `tile` (iteration `it` of this CTA) into ring stage it % NS, in the order in which the previous user of the
+    // stage releases its buffers: V after batch 1, then K (dQ = dS.K is issued first in batch 2), dO (dV), Q (dK).
+    auto produce = [&](int tile, int it) -> bool {
+        const int s = it % NS, k = it / NS;
+        const int g0 = tile * stride - right;  // first flattened row of the window
+        uint8_t* st = smem + s * L.stage_bytes;
+        bool ok = true;
+        auto refill = [&](int buf, uint8_t* dst, const CUtensorMap* map, int rows, int row0) {
+            if (!ok) return;
+            if (!ptx::mbar_wait_relaxed(&misc->empty[s][buf], (k & 1) ^ 1) || *(volatile int*)&misc->abort) { ok = false; return; }
+            ptx::mbar_expect_tx(&misc->full[s][buf], (uint32_t)(rows * kRowBytes));
+            ptx::tma_load_3d(dst, map, &misc->full[s][buf], 0, row0, 0);
+        };
+        refill(kV, st + L.stage_v, &tm_v, KT, g0 - left);
+        refill(kK, st + L.stage_k, &tm_k, KT, g0 - left);
+        refill(kDO, st + L.stage_do, &tm_do, kTileM, g0);
+        refill(kQ, st + L.stage_q, &tm_q, kTileM, g0);
+        return ok;
+    };
+    bool first_ok = true;
+    if (tid == kProducerWarp * 32) {
+        // The producer thread sets up the barriers and requests the CTA's first tile at once: the loads are in flight while
+        // the other warps clear the operand matrices, allocate tensor memory and meet at the barrier below.
         for (int s = 0; s < NS; ++s)
             for (int b = 0; b < 4; ++b) { ptx::mbar_init(&misc->full[s][b], 1); ptx::mbar_init(&misc->empty[s][b], 1); }
         ptx::mbar_init(&misc->s_ready, 2);   // S chain and dP chain
@@ -211,9 +225,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ptx::prefetch_tensormap(&tm_dq);
         ptx::prefetch_tensormap(&tm_dk);
         ptx::prefetch_tensormap(&tm_dv);
+        // global memory written by the predecessor kernel is read from here on
+        ptx::grid_dependency_wait();
+        first_ok = produce((int)blockIdx.x, 0);
     }
     if (warp == 0) {
-        __syncwarp();
         ptx::tmem_alloc(&misc->tmem_base, kTmemCols);
         ptx::tmem_relinquish();
     }
@@ -228,35 +244,18 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     ptx::tc_fence_after_sync();
     const uint32_t tmem = misc->tmem_base;
     volatile int* abort_flag = &misc->abort;
-    // Everything above touched only this CTA's shared and tensor memory. From here on global memory written by
-    // earlier kernels is read and outputs are written: wait for the predecessor, and let the successor start its
-    // own set-up as this grid drains.
+    // Outputs are written from here on: wait for the predecessor, and let the successor start its own set-up as this
+    // grid drains.
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
 
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int it = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-                const int s = it % NS, k = it / NS;
-                const int g0 = tile * stride - right;  // first flattened row of the window
-                uint8_t* st = smem + s * L.stage_bytes;
-                // buffers in the order in which the previous user of this stage releases them: V after batch 1, then K
-                // (dQ = dS.K is issued first in batch 2), dO (dV), Q (dK)
-                bool ok = true;
-                auto refill = [&](int buf, uint8_t* dst, const CUtensorMap* map, int rows, int row0) {
-                    if (!ok) return;
-                    if (!ptx::mbar_wait_relaxed(&misc->empty[s][buf], (k & 1) ^ 1) || *abort_flag) { ok = false; return; }
-                    ptx::mbar_expect_tx(&misc->full[s][buf], (uint32_t)(rows * kRowBytes));
-                    ptx::tma_load_3d(dst, map, &misc->full[s][buf], 0, row0, 0);
-                };
-                refill(kV, st + L.stage_v, &tm_v, KT, g0 - left);
-                refill(kK, st + L.stage_k, &tm_k, KT, g0 - left);
-                refill(kDO, st + L.stage_do, &tm_do, kTileM, g0);
-                refill(kQ, st + L.stage_q, &tm_q, kTileM, g0);
-                if (!ok) { atomicExch(&g_tc_bwd_status, 11); *abort_flag = 1; break; }
-            }
+            int it = 1;
+            bool ok = first_ok;
+            for (int tile = blockIdx.x + gridDim.x; ok && tile < total_tiles; tile += gridDim.x, ++it) ok = produce(tile, it);
+            if (!ok) { atomicExch(&g_tc_bwd_status, 11); *abort_flag = 1; }
         }
     } else if (warp >= kMmaWarp) {
         // ------------------------------------------------------------ MMA issuers
@@ -300,9 +299,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             while (it < n_it) {
                 if (next_b1 < n_it && next_b1 <= it + 1 && (next_b1 == 0 || ptx::mbar_try_wait(&misc->s_free, (next_b1 - 1) & 1)) &&
                     batch1_ready(next_b1)) {
-                    if (role == 0) NA1D_STAMP(8);
                     batch1(next_b1);
-                    if (role == 0) NA1D_STAMP(9);
                     ++next_b1;
                     polls = 0;
                     continue;
@@ -315,7 +312,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 const int s = it % NS;
                 const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
                 ptx::tc_fence_after_sync();
-                if (role == 0) NA1D_STAMP(10);
                 // batch 2. dS/P matrices: element (q, c) at (q/8)*lboq + (c/8)*128 + (q%8)*16 + (c%8)*2.
                 if (role == 0) {
                     //   dQ = dS.K : A K-major (M = queries, K = KT keys): K-adjacent core matrices 128 B apart, 8-row groups lboq apart
@@ -337,7 +333,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     if constexpr (OWN_OUT) ptx::mma_commit(&misc->empty[s][role == 1 ? kDO : kQ]);  // dO: dP and dV done; Q: S and dK done
                 }
                 ptx::mma_commit(&misc->o_ready);
-                if (role == 0) NA1D_STAMP(11);
                 ++it;
             }
             if (!ok) { atomicExch(&g_tc_bwd_status, 12); *abort_flag = 1; }
@@ -389,7 +384,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         cur.init(blockIdx.x * stride, T, gm.H, gridDim.x * stride);
         const int batch = gm.N / gm.H;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it, cur.advance()) {
-            if (tid == 0) NA1D_STAMP(0);
             const int g0 = tile * stride - right;
             if constexpr (WB == 33) {
                 // Widest window bucket: the two 16-row blocks of the warp are processed one after the other in a ROLLED loop.
@@ -524,10 +518,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 }
                 // masks are needed only when one of the warp's rows touches a sequence end or a padded region
                 need_mask = __any_sync(0xffffffffu, need_mask);
-                if (tid == 0) NA1D_STAMP(1);
                 if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 14); *abort_flag = 1; break; }
                 ptx::tc_fence_after_sync();
-                if (tid == 0) NA1D_STAMP(2);
 
                 float s[2][4 * NG], d[2][4 * NG];
     #pragma unroll
@@ -539,7 +531,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 ptx::tmem_ld_wait();
                 ptx::tc_fence_before_sync();
                 ptx::mbar_arrive(&misc->s_free);
-                if (tid == 0) NA1D_STAMP(3);
                 float delta[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
                 // two straight-line copies of the element loop, with and without masks
                 auto elements = [&](auto masked_tag) {
@@ -572,14 +563,12 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                                 }
                 };
                 if (need_mask) elements(std::true_type{}); else elements(std::false_type{});
-                if (tid == 0) NA1D_STAMP(12);
     #pragma unroll
                 for (int b = 0; b < 2; ++b)
     #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) delta[b][hh] = tc::quad_sum(delta[b][hh]);
                 // batch 2 of the previous tile must have finished reading the operand matrices before they are rewritten
                 if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
-                if (tid == 0) NA1D_STAMP(13);
                 // Bias gradient of the PREVIOUS tile, read back from its dS operand now: while batch 2 runs its operand fetches own
                 // the shared-memory bandwidth and the same read-back took thousands of cycles; here the tensor pipe is done with it.
                 if (d_rpb && it > 0)
@@ -619,12 +608,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
                 }
             }
-            if (tid == 0) NA1D_STAMP(4);
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&misc->p_ready);
             load_lse(tile + gridDim.x, lse_next);
-            if (tid == 0) NA1D_STAMP(5);
             if (d_rpb) {
                 // head of the row this lane will read back (-1: a row this tile does not own)
                 const int gr = g0 + r;
@@ -663,7 +650,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             uint8_t* st = smem + (it % NS) * L.stage_bytes;
             if (!ptx::mbar_wait_relaxed(&misc->o_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 15); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
-            if (tid == 128) NA1D_STAMP(6);
             // owned rows: dQ rows [right, right+stride), dK/dV rows [win-1, 128); both land on global rows
             // [out_row, out_row+stride) and are staged from row 0 of the (now idle) Q / dO / K buffers
             auto stage_rows = [&](uint8_t* buf, const float* acc, int m_first) {
@@ -692,11 +678,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
                     for (int c = 0; c < CH; ++c) pk[which][c] = Cvt<E>::pack(acc + c * 8);
                 }
-                if (tid == 128) NA1D_STAMP(14);
 #pragma unroll
                 for (int which = 0; which < 3; ++which) {
                     if (which > 0) asm volatile("bar.sync 2, 128;" ::: "memory");  // previous store has read the buffer
-                    if (which == 1 && tid == 128) NA1D_STAMP(15);
                     const int ms = r - (which == 0 ? right : win - 1);
                     if (ms >= 0 && ms < stride) {
                         const int swz = (C == 64) ? (ms & 7) : (C == 32) ? ((ms >> 1) & 3) : ((ms >> 2) & 1);
@@ -712,7 +696,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     }
                 }
                 asm volatile("bar.sync 2, 128;" ::: "memory");
-                if (tid == 128) NA1D_STAMP(7);
             } else {
                 // no room for a staging buffer: use the tile's idle Q / dO / K buffers and release the stage afterwards
                 float acc[C];
@@ -742,7 +725,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     ptx::mbar_arrive(&misc->empty[it % NS][kQ]);
                     ptx::mbar_arrive(&misc->empty[it % NS][kDO]);
                     ptx::mbar_arrive(&misc->empty[it % NS][kK]);
-                    NA1D_STAMP(7);
                 }
             }
         }
@@ -825,12 +807,6 @@ int tc_bwd_read_status() {
     if (v != 0) cudaMemcpyToSymbol(g_tc_bwd_status, &zero, sizeof(int));
     return v;
 }
-
-#ifdef NA1D_TIMELINE
-extern "C" int na1d_debug_bwd_timeline(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_bwd_timeline, sizeof(long long) * 64 * 16);
-}
-#endif
 
 cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
                          const void* v, const float* lse, const float* rpb, const int* valid_len, float* scratch,

@@ -31,17 +31,6 @@ namespace na1d {
 
 __device__ int g_tc_status = 0;
 
-#ifdef NA1D_TIMELINE
-__device__ unsigned long long g_fwd_cta_times[512 * 4];  // per CTA: start, after set-up, first S ready, end (globaltimer ns)
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define NA1D_CTA_TIME(slot) do { if (threadIdx.x == 0 && blockIdx.x < 512) g_fwd_cta_times[blockIdx.x * 4 + (slot)] = gtime(); } while (0)
-__device__ long long g_fwd_timeline[64 * 16];
-#define NA1D_FSTAMP(slot) do { if (blockIdx.x == 0 && it < 64) g_fwd_timeline[it * 16 + (slot)] = clock64(); } while (0)
-#else
-#define NA1D_FSTAMP(slot) do { } while (0)
-#define NA1D_CTA_TIME(slot) do { } while (0)
-#endif
-
 namespace {
 
 using tc::kTileM;
@@ -89,7 +78,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, int KT, int total_tiles) {
     constexpr int NG = tc::band_groups(WB);
     constexpr int kRowBytes = C * 2;
-    NA1D_CTA_TIME(0);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const FwdSmemLayout L = fwd_layout(C, KT, rpb ? gm.H : 0);
@@ -103,7 +91,29 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int win = tc::eff_window(gm.win, dil), left = gm.left * dil, T = gm.T;
     const int stage_tx = 2 * KT * kRowBytes;
 
-    if (tid == 0) {
+    // Loads of tile `tile` (iteration `it` of this CTA): Q into the single Q buffer, K and V into ring stage it % 2.
+    auto produce = [&](int tile, int it) -> bool {
+        const int s = it & 1, k = it >> 1;
+        const int g0 = tile * kTileM;
+        // Q: free once the S MMAs of the previous tile have retired
+        if (!ptx::mbar_wait_relaxed(&misc->empty_q, (it & 1) ^ 1) || *(volatile int*)&misc->abort) return false;
+        // At the start every CTA of the grid loads at once and DRAM is the limit: let the first tile land before the
+        // second is requested, so that all CTAs start computing (and storing) early instead of at the end of the burst.
+        if (it == 1 && !ptx::mbar_wait_relaxed(&misc->full[0], 0)) return false;
+        ptx::mbar_expect_tx(&misc->full_q, (uint32_t)(kTileM * kRowBytes));
+        ptx::tma_load_3d(smem + L.q, &tm_q, &misc->full_q, 0, g0, 0);
+        // K, V: free once the tile two back has stored its output (staged in its V buffer)
+        if (!ptx::mbar_wait_relaxed(&misc->empty[s], (k & 1) ^ 1) || *(volatile int*)&misc->abort) return false;
+        uint8_t* st = smem + L.ring + s * L.stage_bytes;
+        ptx::mbar_expect_tx(&misc->full[s], (uint32_t)stage_tx);
+        ptx::tma_load_3d(st + L.stage_k, &tm_k, &misc->full[s], 0, g0 - left, 0);
+        ptx::tma_load_3d(st + L.stage_v, &tm_v, &misc->full[s], 0, g0 - left, 0);
+        return true;
+    };
+    bool first_ok = true;
+    if (tid == 4 * 32) {
+        // The producer thread sets up the barriers and requests the CTA's first tile at once: the loads are in flight
+        // while the other warps allocate tensor memory and meet at the barrier below.
         for (int s = 0; s < 2; ++s) { ptx::mbar_init(&misc->full[s], 1); ptx::mbar_init(&misc->empty[s], 1); }
         ptx::mbar_init(&misc->full_q, 1);
         ptx::mbar_init(&misc->empty_q, 1);
@@ -118,9 +128,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ptx::prefetch_tensormap(&tm_k);
         ptx::prefetch_tensormap(&tm_v);
         ptx::prefetch_tensormap(&tm_o);
+        // global memory written by the predecessor kernel is read from here on
+        ptx::grid_dependency_wait();
+        first_ok = produce((int)blockIdx.x, 0);
     }
     if (warp == 0) {
-        __syncwarp();
         ptx::tmem_alloc(&misc->tmem_base, kTmemCols);
         ptx::tmem_relinquish();
     }
@@ -129,34 +141,18 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     ptx::tc_fence_after_sync();
     const uint32_t tmem = misc->tmem_base;
     volatile int* abort_flag = &misc->abort;
-    // Everything above touched only this CTA's shared and tensor memory. From here on global memory written by
-    // earlier kernels is read and outputs are written: wait for the predecessor, and let the successor start its
-    // own set-up as this grid drains.
+    // Outputs are written from here on: wait for the predecessor, and let the successor start its own set-up as this
+    // grid drains.
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
-    NA1D_CTA_TIME(1);
 
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int it = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-                const int s = it & 1, k = it >> 1;
-                const int g0 = tile * kTileM;
-                // Q: free once the S MMAs of the previous tile have retired
-                if (!ptx::mbar_wait_relaxed(&misc->empty_q, (it & 1) ^ 1) || *abort_flag) { atomicExch(&g_tc_status, 1); *abort_flag = 1; break; }
-                // At the start every CTA of the grid loads at once and DRAM is the limit: let the first tile land before the
-                // second is requested, so that all CTAs start computing (and storing) early instead of at the end of the burst.
-                if (it == 1 && !ptx::mbar_wait_relaxed(&misc->full[0], 0)) { atomicExch(&g_tc_status, 1); *abort_flag = 1; break; }
-                ptx::mbar_expect_tx(&misc->full_q, (uint32_t)(kTileM * kRowBytes));
-                ptx::tma_load_3d(smem + L.q, &tm_q, &misc->full_q, 0, g0, 0);
-                // K, V: free once the tile two back has stored its output (staged in its V buffer)
-                if (!ptx::mbar_wait_relaxed(&misc->empty[s], (k & 1) ^ 1) || *abort_flag) { atomicExch(&g_tc_status, 1); *abort_flag = 1; break; }
-                uint8_t* st = smem + L.ring + s * L.stage_bytes;
-                ptx::mbar_expect_tx(&misc->full[s], (uint32_t)stage_tx);
-                ptx::tma_load_3d(st + L.stage_k, &tm_k, &misc->full[s], 0, g0 - left, 0);
-                ptx::tma_load_3d(st + L.stage_v, &tm_v, &misc->full[s], 0, g0 - left, 0);
-            }
+            int it = 1;
+            bool ok = first_ok;
+            for (int tile = blockIdx.x + gridDim.x; ok && tile < total_tiles; tile += gridDim.x, ++it) ok = produce(tile, it);
+            if (!ok) { atomicExch(&g_tc_status, 1); *abort_flag = 1; }
         } else if (lane == 1) {
             // ---------------------------------------------------------- output store thread: waits until the softmax warps
             // have staged a tile's O, issues the TMA store, and frees the stage once the store has read shared memory
@@ -186,7 +182,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     atomicExch(&g_tc_status, 2); *abort_flag = 1; break;
                 }
                 ptx::tc_fence_after_sync();
-                NA1D_FSTAMP(8);
                 {
                     const uint64_t a0 = ptx::smem_desc(ptx::smem_u32(smem + L.q), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
                     const uint64_t b0 = ptx::smem_desc(st + L.stage_k, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
@@ -196,10 +191,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 }
                 ptx::mma_commit(&misc->empty_q);  // Q is read by nothing else
                 ptx::mma_commit(&misc->s_ready);
-                NA1D_FSTAMP(9);
                 if (!ptx::mbar_wait(&misc->p_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 3); *abort_flag = 1; break; }
                 ptx::tc_fence_after_sync();
-                NA1D_FSTAMP(10);
                 {
                     const uint64_t b0 = ptx::smem_desc(st + L.stage_v, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
 #pragma unroll 1
@@ -207,7 +200,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                         ptx::mma_ts(tmem + kOCol, tmem + ks * 8, tc::desc_advance(b0, ks * 16 * kRowBytes), idesc_o, ks > 0 ? 1u : 0u);
                 }
                 ptx::mma_commit(&misc->o_ready);
-                NA1D_FSTAMP(11);
             }
         }
     } else if (warp == 6) {
@@ -263,7 +255,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         cur.init(blockIdx.x * kTileM, T, gm.H, gridDim.x * kTileM);
         const int batch = gm.N / gm.H;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it, cur.advance()) {
-            if (tid == 0) NA1D_FSTAMP(0);
             const int g0 = tile * kTileM;
             // The four rows this thread sees in the fragments (block b, row half hh = local rows 32 warp + fr + 8k). Per row:
             //   jb  : key index inside the row's own sequence of neighbour kk is jb + (kk - fa); outside [0, T) it is the
@@ -290,15 +281,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             need_mask = __any_sync(0xffffffffu, need_mask);
             if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 4); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
-            if (tid == 0) NA1D_FSTAMP(1);
-            if (it == 0) NA1D_CTA_TIME(2);
 
             float s[2][4 * NG];
 #pragma unroll
             for (int b = 0; b < 2; ++b)
                 tc::ld_frag<NG>(lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b), s[b]);
             ptx::tmem_ld_wait();
-            if (tid == 0) NA1D_FSTAMP(2);
             // logits on the band (log2 domain), everything else -inf; two straight-line copies, with and without masks
             float mx[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}};
             auto logits = [&](auto masked_tag) {
@@ -330,7 +318,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                         }
             };
             if (need_mask) logits(std::true_type{}); else logits(std::false_type{});
-            if (tid == 0) NA1D_FSTAMP(12);
             float sum[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
             for (int b = 0; b < 2; ++b)
@@ -358,7 +345,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     if (lse && (lane & 3) == 0 && gq < rows_total) lse[gq] = (mx[b][hh] + tc::fast_log2(sum[b][hh])) * kLn2;
                     sum[b][hh] = tc::fast_rcp(sum[b][hh]);
                 }
-            if (tid == 0) NA1D_FSTAMP(13);
             // P over the S columns. Per 16-lane block the band occupies NGP 8-key groups starting at the block's own
             // first row; every other 16-key chunk of the row range is zeroed. The two sets are disjoint, so one wait.
             {
@@ -390,15 +376,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 }
                 ptx::tmem_st_wait();
             }
-            if (tid == 0) NA1D_FSTAMP(15);
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&misc->p_ready);
-            if (tid == 0) NA1D_FSTAMP(3);
 
             // epilogue: O -> 16 bits -> the tile's idle V buffer (same swizzle as the tensor map) -> TMA store
             if (!ptx::mbar_wait(&misc->o_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 5); *abort_flag = 1; break; }
             ptx::tc_fence_after_sync();
-            if (tid == 0) NA1D_FSTAMP(4);
             {
                 uint8_t* sO = smem + L.ring + (it & 1) * L.stage_bytes + L.stage_v;  // this tile's V buffer: P.V has retired
                 // row r, 16-byte chunk c at r*rowbytes + ((c ^ swz(r)) * 16): the TMA swizzle of this row size
@@ -414,7 +397,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                     }
                     ptx::tmem_ld_wait();
                     if (c0 + HALF >= C) {
-                        if (tid == 0) NA1D_FSTAMP(6);
                         ptx::tc_fence_before_sync();
                         ptx::mbar_arrive(&misc->o_free);
                     }
@@ -425,15 +407,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                         *reinterpret_cast<uint4*>(sO + r * kRowBytes + (((c0 / 8 + c) ^ swz) * 16)) = Cvt<E>::pack(&acc[c * 8]);
                 }
                 ptx::fence_proxy_async_smem();
-                if (tid == 0) NA1D_FSTAMP(7);
                 ptx::mbar_arrive(&misc->o_staged);  // the store thread takes it from here
             }
-            if (tid == 0) NA1D_FSTAMP(5);
         }
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
-    NA1D_CTA_TIME(3);
     if (warp == 0) {
         __syncwarp();
         ptx::tmem_dealloc(tmem, kTmemCols);
@@ -465,15 +444,6 @@ cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
 }
 
 }  // namespace
-
-#ifdef NA1D_TIMELINE
-extern "C" int na1d_debug_fwd_cta_times(unsigned long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_fwd_cta_times, sizeof(unsigned long long) * 512 * 4);
-}
-extern "C" int na1d_debug_fwd_timeline(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_fwd_timeline, sizeof(long long) * 64 * 16);
-}
-#endif
 
 bool tc_fwd_supports(const Geometry& gm) {
     return tc::pow2(gm.dil) && (gm.C == 64 || gm.C == 32 || gm.C == 16) && tc::eff_window(gm.win, gm.dil) <= 33 && gm.H <= 32 && gm.T >= 32 && gm.T < (1 << 21);

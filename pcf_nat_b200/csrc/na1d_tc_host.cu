@@ -1,6 +1,7 @@
 // Host-side helpers shared by the tcgen05 kernels: TMA tensor maps and device properties.
 #include "na1d_internal.h"
 #include "na1d_tc_common.cuh"
+#include <atomic>
 #include <cstdlib>
 
 namespace na1d {
@@ -40,11 +41,13 @@ bool make_row_tile_map(CUtensorMap* map, const void* base, int dtype, int N, int
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Programmatic dependent launch can be switched off with NA1D_PDL=0 in the environment (read once).
-// Programmatic dependent launch is off unless NA1D_PDL says otherwise (measured: it shortens back-to-back launches of one
-// kernel but not the alternating forward/backward sequence of a training step).
-int pdl_mode() {  // 0 off, 1 both kernels, 2 forward only, 3 backward only
-    static const int m = []() { const char* e = getenv("NA1D_PDL"); return e ? (int)(e[0] - '0') : 0; }();
+// Programmatic dependent launch is off unless NA1D_PDL (read once) says otherwise (measured: it shortens back-to-back
+// launches of one kernel but not the alternating forward/backward sequence of a training step).
+int pdl_mode() {  // 0 off, 1 both kernels, 2 forward only, 3 backward only; anything else counts as 0
+    static const int m = []() {
+        const char* e = getenv("NA1D_PDL");
+        return (e && e[0] >= '1' && e[0] <= '3' && e[1] == '\0') ? (int)(e[0] - '0') : 0;
+    }();
     return m;
 }
 bool pdl_enabled() { return pdl_mode() != 0; }
@@ -57,15 +60,15 @@ void bind_primary_context() {
 }
 
 int device_sm_count() {
-    static int cached[64] = {0};
+    static std::atomic<int> cached[64];  // zero-initialised; racing first calls store the same value
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int n = 0;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
 }
 
 }  // namespace na1d

@@ -42,6 +42,50 @@ def test_two_gloo_ranks_shard_by_utterance_and_agree_on_slowest_rank():
     assert slowest == 2.0
 
 
+def _dp_worker(rank, world, port, out):
+    """Data-parallel step of a small model on this rank's half of the batch: flat gradients, one mean all-reduce; and the
+    embedding all-gather of the extraction path."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from pcf_nat_b200 import parallel
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 3))
+    x, y = torch.randn(8, 6), torch.randn(8, 3)
+    flat = parallel.flat_gradient_buffer(net.parameters())
+    lo, hi = parallel.shard_range(8, world, rank)
+    for _ in range(2):   # the second pass checks that zeroing the flat buffer resets every view
+        flat.zero_()
+        torch.nn.functional.mse_loss(net(x[lo:hi]), y[lo:hi]).backward()
+        assert all(p.grad.data_ptr() >= flat.data_ptr() for p in net.parameters()), "a gradient left the flat buffer"
+        parallel.all_reduce_mean(flat)
+    emb = net(x[lo:hi]).detach()
+    rows = parallel.all_gather_rows(emb)
+    if rank == 0:
+        out.put((flat.clone(), rows.clone()))
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_flat_gradient_allreduce_and_embedding_gather():
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_dp_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    flat, rows = out.get()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    # single-process result on the whole batch: equal shards, mean-reduced losses -> the mean of the shard gradients
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 3))
+    x, y = torch.randn(8, 6), torch.randn(8, 3)
+    torch.nn.functional.mse_loss(net(x), y).backward()
+    ref = torch.cat([p.grad.reshape(-1) for p in net.parameters()])
+    torch.testing.assert_close(flat, ref, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(rows, net(x).detach(), rtol=1e-5, atol=1e-6)
+
+
 def test_shard_range_is_a_partition():
     from pcf_nat_b200.parallel import shard_range
     for total in (0, 1, 7, 128, 129):
