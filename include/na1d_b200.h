@@ -39,7 +39,8 @@ extern "C" {
 #define NA1D_ERR_CUDA (-7)           /* a CUDA runtime/driver call failed; see na1d_last_cuda_error() */
 #define NA1D_ERR_DEVICE_TIMEOUT (-8) /* a bounded wait inside a kernel expired (reported by na1d_device_status) */
 #define NA1D_ERR_TOO_LARGE (-9)      /* problem exceeds a fixed capacity of the entry point */
-#define NA1D_ERR_UNSUPPORTED (-10)   /* the kernel family forced by na1d_set_kernel_family cannot run this shape */
+#define NA1D_ERR_UNSUPPORTED (-10)   /* the requested kernel family / tiling cannot run this shape */
+#define NA1D_ERR_BAD_STRIDE (-11)    /* a stride is not a positive multiple of 8 elements, or the token stride is below C */
 
 #define NA1D_MAX_WINDOW 128 /* the reference asserts win <= 80, models/PCF_NATransformer.py:53 */
 
@@ -145,6 +146,41 @@ int na1d_fused_backward_static(void* dq, void* dk, void* dv, float* d_rpb, const
                                int dtype, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Strided forms of the fused pair: q, k, v, o (and the gradients) may be views with arbitrary batch / head / token
+ * strides, so that the head split and merge around the operator need no copies. Each `*_strides` argument is a HOST
+ * pointer to three int64 element strides {batch, head, token} of a tensor addressed as [batch][head][token][channel]
+ * (channel stride 1): a dense (N,T,C) tensor has {heads*T*C, T*C, C}; the q slice of a packed projection output
+ * (batch, T, 3, heads, C) has {T*3*heads*C, C, 3*heads*C} and starts at the packed tensor's base (k: + heads*C
+ * elements, v: + 2*heads*C); an output laid out (batch, T, heads, C) has {T*heads*C, C, heads*C}. Strides must be
+ * positive multiples of 8 elements and pointers 16-byte aligned (NA1D_ERR_BAD_STRIDE / NA1D_ERR_MISALIGNED otherwise);
+ * output views must not overlap themselves or each other. lse stays dense (N,T). These calls run the tcgen05 kernels on
+ * the segmented tiling only (C in {16,32,64}, win <= 33, heads <= 32, T >= 2*dil; NA1D_ERR_UNSUPPORTED otherwise --
+ * make dense copies and use the dense entry points then).
+ * Replaces the head split of models/MFA_NATransformer.py:127-137 (and models/PCF_NATransformer.py:126-138), the head
+ * merge of :151-152, and their autograd copies, together with the fused layer core above.
+ * ---------------------------------------------------------------------------------------- */
+/* 1 when the strided forward AND backward accept this shape (with a bias / with its gradient wanted), 0 when not,
+ * negative for an invalid geometry. Host-only; lets a layer choose between the strided and the dense route up front. */
+int na1d_fused_strided_supported(int64_t heads, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil,
+                                 int dtype, int has_bias, int wants_bias_grad);
+
+int na1d_fused_forward_strided(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
+                               const int32_t* valid_len, const int64_t* o_strides, const int64_t* q_strides,
+                               const int64_t* k_strides, const int64_t* v_strides, int64_t N, int64_t heads,
+                               int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil, float scale, int dtype,
+                               void* stream);
+
+/* scratch: `scratch_floats` fp32 of device memory for the per-CTA partial rows of d_rpb (148 * heads * win is always
+ * enough; with less, or NULL, the kernel adds to d_rpb with atomics). o is not needed. */
+int na1d_fused_backward_strided(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q,
+                                const void* k, const void* v, const float* lse, const float* rpb,
+                                const int32_t* valid_len, float* scratch, int64_t scratch_floats,
+                                const int64_t* dq_strides, const int64_t* dk_strides, const int64_t* dv_strides,
+                                const int64_t* d_o_strides, const int64_t* q_strides, const int64_t* k_strides,
+                                const int64_t* v_strides, int64_t N, int64_t heads, int64_t T, int64_t C, int64_t win,
+                                int64_t left, int64_t dil, float scale, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Window index arithmetic as the kernels compute it, for bit-exact checking:
  * j_out[t,kk] = t + (kk-left)*dil (int32, (T,win)); in_range[t,kk] = 1 if 0 <= j < T else 0.
  * Restates the implicit pad+unfold indexing of models/PCF_NATransformer.py:158-165.
@@ -160,9 +196,23 @@ int na1d_window_index(int32_t* j_out, uint8_t* in_range, int64_t T, int64_t win,
 int na1d_fused_kernel_family(int64_t N, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil,
                              int dtype, int backward);
 
+/* As na1d_fused_kernel_family, but tells the two tilings of the tcgen05 kernels apart: 0 = CUDA-core kernels,
+ * 1 = tcgen05 on the flat tiling (tiles over the dense (N*T, C) matrix; dilation 1, or a power of two with
+ * (win-1)*dil+1 <= 33), 2 = tcgen05 on the segmented tiling (tiles inside one residue class t = r mod dil of one
+ * sequence: every dilation; also what the strided entry points run). Mirrors the tile heuristics of the reference's
+ * launchers, na1d_tensorcore/bf16_ana1d_kernel.cu:495-580. */
+int na1d_fused_kernel_tiling(int64_t N, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil,
+                             int dtype, int backward);
+
 /* Force a kernel family for the fused entry points: -1 = automatic (default), 0 = CUDA-core,
- * 1 = tcgen05/TMA. Process-wide; meant for tests and benchmarks. Returns the previous setting. */
+ * 1 = tcgen05/TMA (either tiling), 2 = tcgen05/TMA on the segmented tiling. Process-wide; meant for tests and
+ * benchmarks. Returns the previous setting. */
 int na1d_set_kernel_family(int family);
+
+/* Hits and misses of the library's cache of encoded TMA tensor maps since the process started (the cache is keyed by
+ * pointer, extents, strides, box and element type; its only global state, behind a lock). Host-only.
+ * No counterpart in the reference (its kernels take raw pointers). */
+int na1d_tensor_map_cache_stats(int64_t* hits, int64_t* misses);
 
 /* Synchronises the device, then returns and clears the device-side status word: 0 = every bounded
  * wait inside the tcgen05 kernels completed, otherwise NA1D_ERR_DEVICE_TIMEOUT. */

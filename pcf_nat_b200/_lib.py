@@ -65,6 +65,16 @@ _lib.na1d_window_index.restype = _i32
 _lib.na1d_window_index.argtypes = [_ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]
 _lib.na1d_fused_kernel_family.restype = _i32
 _lib.na1d_fused_kernel_family.argtypes = [_i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32]
+_lib.na1d_fused_kernel_tiling.restype = _i32
+_lib.na1d_fused_kernel_tiling.argtypes = [_i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32]
+_lib.na1d_fused_strided_supported.restype = _i32
+_lib.na1d_fused_strided_supported.argtypes = [_i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32]
+_lib.na1d_fused_forward_strided.restype = _i32
+_lib.na1d_fused_forward_strided.argtypes = [_ptr] * 7 + [_ptr] * 4 + [_i64] * 7 + [_f32, _i32, _ptr]
+_lib.na1d_fused_backward_strided.restype = _i32
+_lib.na1d_fused_backward_strided.argtypes = [_ptr] * 12 + [_i64] + [_ptr] * 7 + [_i64] * 7 + [_f32, _i32, _ptr]
+_lib.na1d_tensor_map_cache_stats.restype = _i32
+_lib.na1d_tensor_map_cache_stats.argtypes = [_ptr, _ptr]
 _lib.na1d_set_kernel_family.restype = _i32
 _lib.na1d_set_kernel_family.argtypes = [_i32]
 _lib.na1d_device_status.restype = _i32

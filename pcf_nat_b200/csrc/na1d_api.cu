@@ -54,7 +54,8 @@ const char* na1d_status_string(int status) {
         case NA1D_ERR_CUDA: return "a CUDA call failed (see na1d_last_cuda_error)";
         case NA1D_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
         case NA1D_ERR_TOO_LARGE: return "problem exceeds a fixed capacity of this entry point (e.g. N*T above NA1D_STATIC_SCRATCH_ROWS)";
-        case NA1D_ERR_UNSUPPORTED: return "the forced kernel family does not support this shape";
+        case NA1D_ERR_UNSUPPORTED: return "the requested kernel family or tiling does not support this shape";
+        case NA1D_ERR_BAD_STRIDE: return "bad stride: element strides must be positive multiples of 8, the token stride >= C";
         default: return "unknown status";
     }
 }
@@ -98,15 +99,44 @@ int na1d_v_backward(void* v_gd, const float* attn, const void* result_gd, int64_
     return na1d_k_backward(v_gd, attn, result_gd, N, T, C, win, left, dil, dtype, stream);
 }
 
+// 0 = CUDA-core kernels, 1 = tcgen05 kernels on the flat tiling, 2 = tcgen05 kernels on the segmented tiling.
+// The flat tiling takes dilation 1 and those power-of-two dilations whose dilated window still fits the widest band bucket;
+// the segmented tiling takes every dilation (each residue class of a sequence is a dilation-1 problem) at the price of
+// partly empty last tiles. With a dilation both can run, the one with the cheaper band bucket per useful row wins.
 static int pick_family(const na1d::Geometry& g, int backward, bool has_bias = false, bool wants_bias_grad = false) {
     const int forced = g_family_override.load();
-    const bool tc_ok = backward ? na1d::tc_bwd_supports(g, has_bias, wants_bias_grad) : na1d::tc_fwd_supports(g);
+    const bool flat_ok = backward ? na1d::tc_bwd_supports(g, has_bias, wants_bias_grad) : na1d::tc_fwd_supports(g);
+    const bool seg_ok = backward ? na1d::tc_bwd_seg_supports(g, has_bias, wants_bias_grad) : na1d::tc_seg_supports(g);
     if (forced == 0) return 0;
-    if (forced == 1) return tc_ok ? 1 : NA1D_ERR_UNSUPPORTED;
-    return tc_ok ? 1 : 0;
+    if (forced == 2) return seg_ok ? 2 : NA1D_ERR_UNSUPPORTED;
+    int pick = 0;
+    if (flat_ok && seg_ok && g.dil > 1) {
+        // relative cost of a tile row in the window buckets 9 / 17 / 33 (measured: the compute warps' share grows with
+        // the bucket) times the rows the tiling processes per useful row
+        auto bucket_cost = [](int w) { return w <= 9 ? 1.0 : w <= 17 ? 1.25 : 2.0; };
+        const int tp = (g.T + g.dil - 1) / g.dil;
+        const int step = backward ? 128 - (g.win - 1) : 128;
+        const double seg_rows = (double)((tp + step - 1) / step) * step / tp;
+        const double flat = bucket_cost((g.win - 1) * g.dil + 1), seg = bucket_cost(g.win) * seg_rows;
+        pick = seg < 0.9 * flat ? 2 : 1;
+    } else if (flat_ok) {
+        pick = 1;
+    } else if (seg_ok) {
+        pick = 2;
+    }
+    if (forced == 1 && pick == 0) return NA1D_ERR_UNSUPPORTED;
+    return pick;
 }
 
 int na1d_fused_kernel_family(int64_t N, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil, int dtype,
+                             int backward) {
+    na1d::Geometry g;
+    if (int s = check_geometry(N, 1, T, C, win, left, dil, dtype, 1.f, g)) return s;
+    const int fam = pick_family(g, backward);
+    return fam == 2 ? 1 : fam;
+}
+
+int na1d_fused_kernel_tiling(int64_t N, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil, int dtype,
                              int backward) {
     na1d::Geometry g;
     if (int s = check_geometry(N, 1, T, C, win, left, dil, dtype, 1.f, g)) return s;
@@ -114,16 +144,26 @@ int na1d_fused_kernel_family(int64_t N, int64_t T, int64_t C, int64_t win, int64
 }
 
 int na1d_set_kernel_family(int family) {
-    if (family < -1 || family > 1) family = -1;
+    if (family < -1 || family > 2) family = -1;
     return g_family_override.exchange(family);
 }
 
+int na1d_tensor_map_cache_stats(int64_t* hits, int64_t* misses) {
+    NA1D_REQUIRE_PTR(hits); NA1D_REQUIRE_PTR(misses);
+    long long h = 0, m = 0;
+    na1d::tensor_map_cache_stats(&h, &m);
+    *hits = h; *misses = m;
+    return NA1D_OK;
+}
+
 int na1d_device_status(void) {
-    // both words are read (and cleared) before anything is reported; an expired wait in either kernel wins over a failed read
-    const int v = na1d::tc_read_status();
-    const int w = na1d::tc_bwd_read_status();
-    if (v > 0 || w > 0) return NA1D_ERR_DEVICE_TIMEOUT;
-    if (v < 0 || w < 0) {
+    // every word is read (and cleared) before anything is reported; an expired wait in any kernel wins over a failed read
+    const int words[4] = {na1d::tc_read_status(), na1d::tc_bwd_read_status(), na1d::tc_seg_read_status(),
+                          na1d::tc_bwd_seg_read_status()};
+    int v = 0, w = 0;
+    for (int x : words) { if (x > 0) v = x; if (x < 0) w = x; }
+    if (v > 0) return NA1D_ERR_DEVICE_TIMEOUT;
+    if (w < 0) {
         const cudaError_t e = cudaGetLastError();
         return cuda_status(e == cudaSuccess ? cudaErrorUnknown : e);
     }
@@ -140,7 +180,75 @@ int na1d_fused_forward(void* o, float* lse, const void* q, const void* k, const 
     const int fam = pick_family(g, 0);
     if (fam < 0) return fam;
     if (fam == 1) return cuda_status(na1d::tc_fused_fwd(o, lse, q, k, v, rpb, valid_len, g, dtype, (cudaStream_t)stream));
+    if (fam == 2) {
+        const na1d::Strides d = na1d::dense_strides(g.H, g.T, g.C);
+        return cuda_status(na1d::tc_fused_fwd_seg(o, lse, q, k, v, rpb, valid_len, d, d, d, d, g, dtype, (cudaStream_t)stream));
+    }
     return cuda_status(na1d::simt_fused_fwd(o, lse, q, k, v, rpb, valid_len, g, dtype, (cudaStream_t)stream));
+}
+
+namespace {
+// element strides (batch, head, token) given by the caller as three int64 on the host
+int read_strides(const int64_t* p, int64_t batch, int64_t heads, int64_t T, int64_t C, na1d::Strides& out) {
+    if (p == nullptr) return NA1D_ERR_NULL_POINTER;
+    for (int i = 0; i < 3; ++i)
+        if (p[i] <= 0 || p[i] % 8 != 0) return NA1D_ERR_BAD_STRIDE;
+    if (p[2] < C) return NA1D_ERR_BAD_STRIDE;
+    // the largest element offset must stay far inside int64 and inside what a tensor map can address (2^40 bytes per stride)
+    const long double span = (long double)p[0] * (batch - 1) + (long double)p[1] * (heads - 1) + (long double)p[2] * (T - 1) + C;
+    if (span > 4.0e12L || p[0] >= (1ll << 38) || p[1] >= (1ll << 38) || p[2] >= (1ll << 38)) return NA1D_ERR_BAD_STRIDE;
+    out = na1d::Strides{(long long)p[0], (long long)p[1], (long long)p[2]};
+    return NA1D_OK;
+}
+}  // namespace
+
+int na1d_fused_strided_supported(int64_t heads, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil, int dtype,
+                                 int has_bias, int wants_bias_grad) {
+    na1d::Geometry g;
+    if (int s = check_geometry(heads, heads, T, C, win, left, dil, dtype, 1.f, g)) return s;
+    return (na1d::tc_seg_supports(g) && na1d::tc_bwd_seg_supports(g, has_bias != 0, wants_bias_grad != 0)) ? 1 : 0;
+}
+
+int na1d_fused_forward_strided(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
+                               const int32_t* valid_len, const int64_t* o_strides, const int64_t* q_strides,
+                               const int64_t* k_strides, const int64_t* v_strides, int64_t N, int64_t heads, int64_t T,
+                               int64_t C, int64_t win, int64_t left, int64_t dil, float scale, int dtype, void* stream) {
+    NA1D_REQUIRE_PTR(o); NA1D_REQUIRE_PTR(q); NA1D_REQUIRE_PTR(k); NA1D_REQUIRE_PTR(v);
+    NA1D_REQUIRE_ALIGNED(o); NA1D_REQUIRE_ALIGNED(q); NA1D_REQUIRE_ALIGNED(k); NA1D_REQUIRE_ALIGNED(v);
+    na1d::Geometry g;
+    if (int s = check_geometry(N, heads, T, C, win, left, dil, dtype, scale, g)) return s;
+    na1d::Strides so, sq, sk, sv;
+    const int64_t batch = N / heads;
+    if (int s = read_strides(o_strides, batch, heads, T, C, so)) return s;
+    if (int s = read_strides(q_strides, batch, heads, T, C, sq)) return s;
+    if (int s = read_strides(k_strides, batch, heads, T, C, sk)) return s;
+    if (int s = read_strides(v_strides, batch, heads, T, C, sv)) return s;
+    if (!na1d::tc_seg_supports(g)) return NA1D_ERR_UNSUPPORTED;
+    return cuda_status(na1d::tc_fused_fwd_seg(o, lse, q, k, v, rpb, valid_len, sq, sk, sv, so, g, dtype, (cudaStream_t)stream));
+}
+
+int na1d_fused_backward_strided(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
+                                const void* v, const float* lse, const float* rpb, const int32_t* valid_len, float* scratch,
+                                int64_t scratch_floats, const int64_t* dq_strides, const int64_t* dk_strides,
+                                const int64_t* dv_strides, const int64_t* d_o_strides, const int64_t* q_strides,
+                                const int64_t* k_strides, const int64_t* v_strides, int64_t N, int64_t heads, int64_t T,
+                                int64_t C, int64_t win, int64_t left, int64_t dil, float scale, int dtype, void* stream) {
+    NA1D_REQUIRE_PTR(dq); NA1D_REQUIRE_PTR(dk); NA1D_REQUIRE_PTR(dv); NA1D_REQUIRE_PTR(d_o); NA1D_REQUIRE_PTR(q);
+    NA1D_REQUIRE_PTR(k); NA1D_REQUIRE_PTR(v); NA1D_REQUIRE_PTR(lse);
+    NA1D_REQUIRE_ALIGNED(dq); NA1D_REQUIRE_ALIGNED(dk); NA1D_REQUIRE_ALIGNED(dv); NA1D_REQUIRE_ALIGNED(d_o);
+    NA1D_REQUIRE_ALIGNED(q); NA1D_REQUIRE_ALIGNED(k); NA1D_REQUIRE_ALIGNED(v);
+    na1d::Geometry g;
+    if (int s = check_geometry(N, heads, T, C, win, left, dil, dtype, scale, g)) return s;
+    if (d_rpb && heads * win * 4 > 48 * 1024) return NA1D_ERR_TOO_LARGE;
+    if (scratch_floats < 0 || (scratch == nullptr && scratch_floats != 0)) return NA1D_ERR_NULL_POINTER;
+    na1d::Strides s7[7];
+    const int64_t* in[7] = {dq_strides, dk_strides, dv_strides, d_o_strides, q_strides, k_strides, v_strides};
+    const int64_t batch = N / heads;
+    for (int i = 0; i < 7; ++i)
+        if (int s = read_strides(in[i], batch, heads, T, C, s7[i])) return s;
+    if (!na1d::tc_bwd_seg_supports(g, rpb != nullptr, d_rpb != nullptr)) return NA1D_ERR_UNSUPPORTED;
+    return cuda_status(na1d::tc_fused_bwd_seg(dq, dk, dv, d_rpb, d_o, q, k, v, lse, rpb, valid_len, scratch, (size_t)scratch_floats,
+                                              s7[0], s7[1], s7[2], s7[3], s7[4], s7[5], s7[6], g, dtype, (cudaStream_t)stream));
 }
 
 int na1d_fused_backward(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
@@ -161,6 +269,11 @@ int na1d_fused_backward(void* dq, void* dk, void* dv, float* d_rpb, const void* 
                    // per-CTA partial sums of the bias gradient
         return cuda_status(na1d::tc_fused_bwd(dq, dk, dv, d_rpb, d_o, q, k, v, lse, rpb, valid_len, delta_ws,
                                               (size_t)g.N * (size_t)g.T, g, dtype, st));
+    if (fam == 2) {
+        const na1d::Strides d = na1d::dense_strides(g.H, g.T, g.C);
+        return cuda_status(na1d::tc_fused_bwd_seg(dq, dk, dv, d_rpb, d_o, q, k, v, lse, rpb, valid_len, delta_ws,
+                                                  (size_t)g.N * (size_t)g.T, d, d, d, d, d, d, d, g, dtype, st));
+    }
     if (int s = cuda_status(na1d::simt_delta(delta_ws, d_o, o, g.N * g.T, g.C, dtype, st))) return s;
     return cuda_status(na1d::simt_fused_bwd(dq, dk, dv, d_rpb, d_o, q, k, v, lse, delta_ws, rpb, valid_len, g, dtype, st));
 }

@@ -26,6 +26,26 @@ struct Geometry {
     float scale;
 };
 
+// Element strides of a 16-bit tensor addressed as [batch][head][token][channel] (channel stride 1). A dense (N, T, C)
+// tensor with n = batch * H + head has {H*T*C, T*C, C}; the q/k/v slices of a packed (batch, T, 3, H, C) projection
+// output have {T*3*H*C, C, 3*H*C}.
+struct Strides {
+    long long batch, head, token;
+};
+__host__ __device__ inline Strides dense_strides(int H, int T, int C) {
+    return Strides{(long long)H * T * C, (long long)T * C, (long long)C};
+}
+
+// Segmented tiling: the rows t = r (mod d) of one (batch, head) sequence form a residue sequence of Tp or Tp - 1 tokens
+// on which a window of dilation d is an ordinary window of dilation 1; tiles never leave their residue sequence.
+struct SegGeom {
+    int d;     // residue classes per sequence (the dilation), >= 1
+    int ra;    // residues r < ra have Tp tokens, the others Tp - 1 (ra = d when d divides T)
+    int Tp;    // ceil(T / d)
+    int tps;   // tiles per residue sequence
+    int step;  // rows between the first rows of consecutive tiles of a sequence
+};
+
 // 8 consecutive 16-bit elements (one 16-byte chunk) <-> 8 floats
 template <typename E> struct Cvt;
 template <> struct Cvt<__nv_bfloat16> {

@@ -1,844 +1,37 @@
-// Fused NA1D backward on the Blackwell tensor path (sm_100a): persistent, warp-specialised.
-//
-// Tiling. Rows are tiled over the FLATTENED (sequence, token) axis, so tiles are full whatever T is; a neighbour that
-// falls outside the query's own sequence is the reference's zero-padded row and is excluded per element.
-// A tile is a window W of 128 consecutive flattened rows; consecutive tiles start
-// `stride = 128-(win-1)` rows apart, so they overlap by win-1 rows. All 128 rows act as queries
-// (their band needs keys [w0-left, w0+127+right]; K and V are staged as KT = round16(128+win-1) rows
-// starting at w0-left). A key row is "interior" when every query that attends it lies in W, which
-// holds for rows [right, 128-left) of W -- exactly `stride` rows, and these are the rows whose dQ, dK
-// and dV this tile stores. Every (query,key) pair of the
-// band is thus seen with both rows inside one tile: no atomics, no second key-owned recomputation,
-// deterministic results.
-//
-// Per tile (one CTA per SM, 384 threads):
-//   warp 8  : TMA producer -- Q[W], dO[W], K[KT], V[KT] into a 2-stage ring (plain tile loads,
-//             out-of-range rows arrive as zeros = the reference's zero padding).
-//   warps 9-11: MMA issuers -- batch 1: S = Q.K^T, dP = dO.V^T (TMEM, N=KT);
-//                            batch 2: dQ = dS.K, dV = P^T.dO, dK = dS^T.Q. One warp per accumulator chain.
-//             Batch 1 of the NEXT tile is issued before batch 2 of the current one, so the compute warps
-//             work on tile i+1 while the tensor pipe finishes tile i.
-//   warps0-3: compute. Warp w owns query rows 32w..32w+31 (its TMEM lanes) as two 16-row blocks, read as
-//             accumulator fragments (see na1d_tc_common.cuh). P = exp(S - lse) from the saved
-//             log-sum-exp, delta = sum P.dP over the row (equal to dot(dO,O), so neither O nor a separate
-//             delta pass is needed; two quad shuffles), dS = P(dP - delta). P and dS go to shared memory with
-//             stmatrix as 16-bit row-major [query][key] matrices in 8x8 core-matrix order; the same bytes
-//             serve as the K-major A operand of dQ = dS.K and as the MN-major A operand of
-//             dK = dS^T.Q / dV = P^T.dO, so no transpose is ever materialised.
-//   warps4-7: epilogue. Read dQ/dK/dV from TMEM (row m of dQ is query w0+m, row m of dK/dV is key
-//             w0-left+m), round to 16 bits, stage the `stride` owned rows in the tile's idle Q/dO/K buffers
-//             in the TMA swizzle and issue three TMA tile stores (rows >= T are clipped by the tensor map).
-// Replaces the four backward launches of the reference (na1d_tensorcore/nattn.py:46-54, 69-78) and
-// the eager softmax backward between them.
-#include "na1d_internal.h"
-#include <type_traits>
-#include "na1d_tc_common.cuh"
+// tcgen05 backward, flat tiling over the dense (N*T, C) matrix: host entry points and the bfloat16 instantiations
+// (the float16 ones are compiled in na1d_tc_bwd_fp16.cu, in parallel).
+#include "na1d_tc_bwd_kernel.cuh"
 
 namespace na1d {
 
-// Device status word of this translation unit (device symbols are per file without relocatable device code).
-__device__ int g_tc_bwd_status = 0;
+cudaError_t tc_bwd_flat_fp16(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k, const void* v,
+                             const float* lse, const float* rpb, const int* valid_len, float* scratch, size_t scratch_floats,
+                             const Geometry& gm, cudaStream_t st);
+int tc_bwd_fp16_read_status();
 
-namespace {
+}  // namespace na1d
+#include "na1d_tc_bwd_flat.inl"
 
-using tc::kTileM;
-using tc::round_up;
-using tc::RowSwizzle;
-using tc::Fmt;
-constexpr int kThreads = 384;
-constexpr int kProducerWarp = 8, kMmaWarp = 9;  // warps 9, 10, 11 issue MMAs
-constexpr int kQ = 0, kDO = 1, kK = 2, kV = 3;  // buffers of a stage
-constexpr int kTmemCols = 512;
-constexpr int kColDP = 160, kColDQ = 320, kColDK = 384, kColDV = 448;
-constexpr int kBiasPad = 16;  // bias table index = kk + kBiasPad; fragment neighbour indices start at -15
-
-struct BwdSmemLayout {
-    int stage_q, stage_do, stage_k, stage_v, stage_bytes;  // offsets inside one stage
-    int ds, p, out, misc, total;
-    bool own_out;  // a dedicated 128-row staging buffer for the outputs fits next to everything else
-};
-constexpr int kBiasRowB = 16 + 48;  // per-head table: log2e * rpb[h][kk] at index kk + 16, kk in [-16, 48)
-// Depth of the operand ring: 64-channel tiles fill shared memory with two stages; narrower rows leave room for a third, which
-// takes the TMA load latency (about 3 k cycles under load) out of the loop "batch 2 retires -> refill -> batch 1 -> compute".
-__host__ __device__ constexpr int bwd_stages(int C) { return C == 64 ? 2 : 3; }
-__host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT, int bias_heads, int acc_floats) {
-    BwdSmemLayout L;
-    L.stage_q = 0;
-    L.stage_do = L.stage_q + round_up(kTileM * C * 2, 1024);
-    L.stage_k = L.stage_do + round_up(kTileM * C * 2, 1024);
-    L.stage_v = L.stage_k + round_up(KT * C * 2, 1024);
-    L.stage_bytes = L.stage_v + round_up(KT * C * 2, 1024);
-    L.ds = bwd_stages(C) * L.stage_bytes;  // dS [128 queries][KT keys]
-    L.p = L.ds + kTileM * KT * 2;       // P  [128 queries][KT keys]
-    L.out = L.p + kTileM * KT * 2;
-    // misc block, bias table, bias-gradient accumulator, alignment slack
-    const int tail = 512 + round_up(bias_heads * kBiasRowB * 4, 256) + round_up(acc_floats * 4, 256) + 1008;
-    L.own_out = L.out + round_up(kTileM * C * 2, 1024) + tail <= 227 * 1024;
-    L.misc = L.out + (L.own_out ? round_up(kTileM * C * 2, 1024) : 0);
-    L.total = L.misc + tail;
-    return L;
-}
-
-// Bias gradient of neighbours outside the query's own sequence (rare: only padded query rows next to a sequence end have
-// a non-zero probability there). Not inlined, to keep the many call sites of the unrolled loops small.
-// row = this head's row of d_rpb, off = window offset of g0 (g1: off + 1); a non-zero gradient implies an offset that is a
-// neighbour (a multiple of the dilation, 1 << dshift).
-__device__ __noinline__ void bias_grad_outside(float* row, int off, int dshift, float g0, float g1) {
-    if (g0 != 0.f) atomicAdd(row + (off >> dshift), g0);
-    if (g1 != 0.f) atomicAdd(row + ((off + 1) >> dshift), g1);
-}
-
-// Bias gradient of one tile, one warp: column sums of dS over the warp's owned query rows (hr = the row's head, -1 for a row
-// this tile does not own). Lane r has the address of row r of the dS operand (16-bit, scaled); a shuffle butterfly leaves the
-// sum of window offset i on lane i * (32 / NV), which adds it to the warp's own accumulator (no atomics: lanes hold distinct
-// offsets). Rows of different heads (a warp spans at most two sequences) take one pass per head. NV = 8, 16 or 32 offsets go
-// through the butterfly; offset NV exists only when the window fills its bucket. Not inlined: it keeps the tile loop short.
-template <typename E, int NV>
-__device__ __noinline__ void bias_grad_tile(const uint8_t* row, int r, int lane, int hr, int win, int ref_win, int dmask,
-                                            int dshift, float inv_scale, float* acc) {
-    // Every step below is a dependent chain in one warp (measured 1150 cycles for 8 offsets when written with conditional
-    // generic loads, integer reductions for the head range and a synchronised second accumulator update), so: unconditional
-    // shared-space loads, votes instead of reductions in the common one-head case, one accumulator update.
-    const unsigned owned = __ballot_sync(0xffffffffu, hr >= 0);
-    if (owned == 0) return;
-    const uint32_t row_s = ptx::smem_u32(row);
-    int hsel = __shfl_sync(0xffffffffu, hr, __ffs(owned) - 1);           // head of the first owned row
-    unsigned todo = owned;
-    for (;;) {
-        const bool mine = hr == hsel;
-        todo &= ~__ballot_sync(0xffffffffu, mine);
-        float x[NV];
-#pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int col = r + i;
-            unsigned short raw;
-            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(raw) : "r"(row_s + (uint32_t)((col >> 3) * 128 + (col & 7) * 2)));
-            const float v = Cvt<E>::from_bits(raw);
-            x[i] = (mine && i < win) ? v : 0.f;
-        }
-        float last = 0.f;
-        if (win > NV) {  // offset NV: only when the window fills its bucket
-            const int col = r + NV;
-            unsigned short raw;
-            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(raw) : "r"(row_s + (uint32_t)((col >> 3) * 128 + (col & 7) * 2)));
-            last = mine ? Cvt<E>::from_bits(raw) : 0.f;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) last += __shfl_xor_sync(0xffffffffu, last, o);
-        }
-        const float v = tc::column_sums<NV>(x, lane);
-        const int off = lane / (32 / NV);
-        float* acc_row = acc + hsel * ref_win;
-        // distinct lanes hold distinct offsets, and offset NV maps to an entry of its own: no two writes meet
-        if (lane % (32 / NV) == 0 && off < win && (off & dmask) == 0) acc_row[off >> dshift] += v * inv_scale;
-        if (win > NV && lane == 0) acc_row[NV >> dshift] += last * inv_scale;
-        if (todo == 0) break;
-        __syncwarp();
-        hsel = __shfl_sync(0xffffffffu, hr, __ffs(todo) - 1);
-    }
-}
-
-// The layout as both the launcher and the kernel compute it (one function, so they cannot disagree): bias table for every
-// head when there is a bias, four per-warp (H, win) accumulators when its gradient is wanted.
-__host__ __device__ inline BwdSmemLayout bwd_layout_for(int C, int KT, const Geometry& gm, bool has_bias, bool wants_bias_grad) {
-    return bwd_layout(C, KT, has_bias ? gm.H : 0, wants_bias_grad ? 4 * gm.H * gm.win : 0);
-}
-
-struct alignas(8) BwdMisc {
-    // ring barriers per stage and per buffer (kQ, kDO, kK, kV): each buffer is refilled as soon as its last reader retires
-    uint64_t full[3][4], empty[3][4];
-    uint64_t s_ready, s_free, p_ready, o_ready;
-    uint64_t o_free[3];  // per accumulator (dQ, dV, dK): its MMA chain restarts as soon as the epilogue has drained it
-    uint64_t acc_done;   // all compute threads have added their last tile to the bias-gradient accumulator
-    uint32_t tmem_base;
-    int abort;
-};
-
-template <typename E, int C, int WB, bool OWN_OUT>
-__global__ void __launch_bounds__(kThreads, 1)
-tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-              const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-              const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk,
-              const __grid_constant__ CUtensorMap tm_dv, float* __restrict__ d_rpb, int drpb_direct,
-              const float* __restrict__ lse,
-              const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, int stride, int KT,
-              int total_tiles) {
-    constexpr int NG = tc::band_groups(WB);  // 8-column groups holding the band of a 16-row block
-    constexpr int NS = bwd_stages(C);         // ring depth: tile `it` uses stage it % NS in ring round it / NS
-    constexpr int kRowBytes = C * 2;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int n_bias = gm.H * gm.win;  // entries of the bias gradient
-    const BwdSmemLayout L = bwd_layout_for(C, KT, gm, rpb != nullptr, d_rpb != nullptr);
-    uint8_t* sDS = smem + L.ds;
-    uint8_t* sP = smem + L.p;
-    BwdMisc* misc = reinterpret_cast<BwdMisc*>(smem + L.misc);
-    float* bias_tab = reinterpret_cast<float*>(smem + L.misc + 512);
-    // accumulators of the bias gradient, one (H, win) array per compute warp: global atomics on the result -- one cache line
-    // for the usual sizes -- serialise (5x the whole kernel's time when every tile issued them), so each warp adds up its
-    // tiles here without atomics and the CTA hands over one row of partial sums at its end
-    float* bias_acc = bias_tab + round_up((rpb ? gm.H : 0) * kBiasRowB, 64);
-    const int rows_total = gm.N * gm.T;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // effective (dilated) window: neighbour kk of the reference is offset kk * dil of it
-    const int dil = gm.dil, dmask = dil - 1, dshift = 31 - __clz(dil);
-    const int win = tc::eff_window(gm.win, dil), left = gm.left * dil, right = (gm.win - 1 - gm.left) * dil, T = gm.T;
-    const int lboq = KT * 16;  // bytes between 8-query groups of the dS matrix
-
-    // Loads of tile `tile` (iteration `it` of this CTA) into ring stage it % NS, in the order in which the previous user of the
-    // stage releases its buffers: V after batch 1, then K (dQ = dS.K is issued first in batch 2), dO (dV), Q (dK).
-    auto produce = [&](int tile, int it) -> bool {
-        const int s = it % NS, k = it / NS;
-        const int g0 = tile * stride - right;  // first flattened row of the window
-        uint8_t* st = smem + s * L.stage_bytes;
-        bool ok = true;
-        auto refill = [&](int buf, uint8_t* dst, const CUtensorMap* map, int rows, int row0) {
-            if (!ok) return;
-            if (!ptx::mbar_wait_relaxed(&misc->empty[s][buf], (k & 1) ^ 1) || *(volatile int*)&misc->abort) { ok = false; return; }
-            ptx::mbar_expect_tx(&misc->full[s][buf], (uint32_t)(rows * kRowBytes));
-            ptx::tma_load_3d(dst, map, &misc->full[s][buf], 0, row0, 0);
-        };
-        refill(kV, st + L.stage_v, &tm_v, KT, g0 - left);
-        refill(kK, st + L.stage_k, &tm_k, KT, g0 - left);
-        refill(kDO, st + L.stage_do, &tm_do, kTileM, g0);
-        refill(kQ, st + L.stage_q, &tm_q, kTileM, g0);
-        return ok;
-    };
-    bool first_ok = true;
-    if (tid == kProducerWarp * 32) {
-        // The producer thread sets up the barriers and requests the CTA's first tile at once: the loads are in flight while
-        // the other warps clear the operand matrices, allocate tensor memory and meet at the barrier below.
-        for (int s = 0; s < NS; ++s)
-            for (int b = 0; b < 4; ++b) { ptx::mbar_init(&misc->full[s][b], 1); ptx::mbar_init(&misc->empty[s][b], 1); }
-        ptx::mbar_init(&misc->s_ready, 2);   // S chain and dP chain
-        ptx::mbar_init(&misc->s_free, 128);
-        ptx::mbar_init(&misc->p_ready, 128);
-        ptx::mbar_init(&misc->o_ready, 3);   // dQ, dV, dK chains
-        for (int i = 0; i < 3; ++i) ptx::mbar_init(&misc->o_free[i], 128);
-        ptx::mbar_init(&misc->acc_done, 128);
-        misc->abort = 0;
-        ptx::fence_mbar_init();
-        ptx::prefetch_tensormap(&tm_q);
-        ptx::prefetch_tensormap(&tm_do);
-        ptx::prefetch_tensormap(&tm_k);
-        ptx::prefetch_tensormap(&tm_v);
-        ptx::prefetch_tensormap(&tm_dq);
-        ptx::prefetch_tensormap(&tm_dk);
-        ptx::prefetch_tensormap(&tm_dv);
-        // global memory written by the predecessor kernel is read from here on
-        ptx::grid_dependency_wait();
-        first_ok = produce((int)blockIdx.x, 0);
-    }
-    if (warp == 0) {
-        ptx::tmem_alloc(&misc->tmem_base, kTmemCols);
-        ptx::tmem_relinquish();
-    }
-    {   // operand matrices start as zeros; each warp rewrites the slab of its own rows every tile
-        uint4* z = reinterpret_cast<uint4*>(sDS);
-        const int n16 = 2 * kTileM * KT * 2 / 16;
-        for (int i = tid; i < n16; i += kThreads) z[i] = make_uint4(0, 0, 0, 0);
-    }
-    ptx::fence_proxy_async_smem();
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    ptx::tc_fence_after_sync();
-    const uint32_t tmem = misc->tmem_base;
-    volatile int* abort_flag = &misc->abort;
-    // Outputs are written from here on: wait for the predecessor, and let the successor start its own set-up as this
-    // grid drains.
-    ptx::grid_launch_dependents();
-    ptx::grid_dependency_wait();
-
-    if (warp == kProducerWarp) {
-        // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            int it = 1;
-            bool ok = first_ok;
-            for (int tile = blockIdx.x + gridDim.x; ok && tile < total_tiles; tile += gridDim.x, ++it) ok = produce(tile, it);
-            if (!ok) { atomicExch(&g_tc_bwd_status, 11); *abort_flag = 1; }
-        }
-    } else if (warp >= kMmaWarp) {
-        // ------------------------------------------------------------ MMA issuers
-        // One tcgen05.mma costs its issuing thread about 120 cycles whatever its size (measured), far more than the
-        // tensor pipe needs for these small shapes, but issuers in different warps overlap. Three warps therefore issue
-        // the MMAs of the three independent accumulator chains:  role 0: S and dQ,  role 1: dP and dV,  role 2: dK.
-        const int role = warp - kMmaWarp;
-        if (lane == 0) {
-            const uint32_t idesc_s = ptx::instr_desc(Fmt<E>::v, 0, 0, kTileM, (uint32_t)KT);
-            const uint32_t idesc_dq = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);   // A K-major, B MN-major
-            const uint32_t idesc_dkv = ptx::instr_desc(Fmt<E>::v, 1, 1, kTileM, (uint32_t)C);  // A MN-major, B MN-major
-            const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
-            const int nks = KT / 16;
-            // this role's part of batch 1 of tile `jt`: S = Q.K^T -> cols [0,KT) (role 0), dP = dO.V^T -> cols [160,160+KT) (role 1)
-            auto batch1_ready = [&](int jt) -> bool {  // non-blocking: have this role's two operands of tile jt landed?
-                const int s = jt % NS, k = jt / NS;
-                return ptx::mbar_try_wait(&misc->full[s][role == 0 ? kK : kV], k & 1) &&
-                       ptx::mbar_try_wait(&misc->full[s][role == 0 ? kQ : kDO], k & 1);
-            };
-            auto batch1 = [&](int jt) {
-                const int s = jt % NS;
-                const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
-                ptx::tc_fence_after_sync();
-                const uint64_t da0 = ptx::smem_desc(st + (role == 0 ? L.stage_q : L.stage_do), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                const uint64_t db0 = ptx::smem_desc(st + (role == 0 ? L.stage_k : L.stage_v), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                const uint32_t dcol = tmem + (role == 0 ? 0u : (uint32_t)kColDP);
-#pragma unroll
-                for (int ks = 0; ks < C / 16; ++ks)
-                    ptx::mma_ss(dcol, tc::desc_advance(da0, ks * 32), tc::desc_advance(db0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
-                if (role == 1) ptx::mma_commit(&misc->empty[s][kV]);  // nothing else reads V
-                ptx::mma_commit(&misc->s_ready);
-            };
-            // Two job streams per issuer: batch 1 of iteration j (roles 0 and 1; needs the compute warps to have read S/dP of
-            // iteration j-1 and the operands of tile j in shared memory) and batch 2 of iteration i (needs the compute warps'
-            // operand matrices and the drained accumulator). Whichever is ready first is issued first, so a late TMA load never
-            // holds back MMAs whose inputs are already there. Batch 1 runs at most one iteration ahead of batch 2.
-            const int n_it = blockIdx.x < total_tiles ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-            int next_b1 = role < 2 ? 0 : n_it, it = 0;
-            uint32_t polls = 0;
-            bool ok = true;
-            while (it < n_it) {
-                if (next_b1 < n_it && next_b1 <= it + 1 && (next_b1 == 0 || ptx::mbar_try_wait(&misc->s_free, (next_b1 - 1) & 1)) &&
-                    batch1_ready(next_b1)) {
-                    batch1(next_b1);
-                    ++next_b1;
-                    polls = 0;
-                    continue;
-                }
-                if (!(ptx::mbar_try_wait(&misc->p_ready, it & 1) && ptx::mbar_try_wait(&misc->o_free[role], (it & 1) ^ 1))) {
-                    if (++polls > (1u << 22) || *abort_flag) { ok = false; break; }
-                    continue;
-                }
-                polls = 0;
-                const int s = it % NS;
-                const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
-                ptx::tc_fence_after_sync();
-                // batch 2. dS/P matrices: element (q, c) at (q/8)*lboq + (c/8)*128 + (q%8)*16 + (c%8)*2.
-                if (role == 0) {
-                    //   dQ = dS.K : A K-major (M = queries, K = KT keys): K-adjacent core matrices 128 B apart, 8-row groups lboq apart
-                    const uint64_t a_dq = ptx::smem_desc(ds_a, 128, lboq, ptx::kSwizzleNone);
-                    const uint64_t b_k = ptx::smem_desc(st + L.stage_k, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
-#pragma unroll 1
-                    for (int ks = 0; ks < nks; ++ks)
-                        ptx::mma_ss(tmem + kColDQ, tc::desc_advance(a_dq, ks * 256), tc::desc_advance(b_k, ks * 16 * kRowBytes), idesc_dq, ks > 0 ? 1u : 0u);
-                    if constexpr (OWN_OUT) ptx::mma_commit(&misc->empty[s][kK]);   // K was read by S (long done) and dQ
-                } else {
-                    //   dV = P^T.dO (role 1), dK = dS^T.Q (role 2): the same matrices read MN-major (M = first 128 keys of the K
-                    //   window, K = queries): 8-key groups 128 B apart, 8-query groups lboq apart
-                    const uint64_t a_t = ptx::smem_desc(role == 1 ? p_a : ds_a, lboq, 128, ptx::kSwizzleNone);
-                    const uint64_t b_t = ptx::smem_desc(st + (role == 1 ? L.stage_do : L.stage_q), 0, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    const uint32_t dcol = tmem + (role == 1 ? kColDV : kColDK);
-#pragma unroll 1
-                    for (int ks = 0; ks < kTileM / 16; ++ks)
-                        ptx::mma_ss(dcol, tc::desc_advance(a_t, ks * 2 * lboq), tc::desc_advance(b_t, ks * 16 * kRowBytes), idesc_dkv, ks > 0 ? 1u : 0u);
-                    if constexpr (OWN_OUT) ptx::mma_commit(&misc->empty[s][role == 1 ? kDO : kQ]);  // dO: dP and dV done; Q: S and dK done
-                }
-                ptx::mma_commit(&misc->o_ready);
-                ++it;
-            }
-            if (!ok) { atomicExch(&g_tc_bwd_status, 12); *abort_flag = 1; }
-        }
-    } else if (warp < 4) {
-        // ------------------------------------------------------------ compute warps
-        const int r = warp * 32 + lane;                 // row of the 32x32b epilogue loads
-        const int fr = lane >> 2, fc = 2 * (lane & 3);  // fragment row / first column inside an 8x8 block
-        const int fa = fc - fr;                         // neighbour index = 8(n-h) + e + fa
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        const float sc = gm.scale * kLog2e;
-        const float mask2 = kMaskValue * kLog2e;
-        // which of the thread's fragment slots are neighbours: slot (g, hh, e) is window offset 8 (g - hh) + e + fa, the same
-        // for every tile, so the band test is one bit of a per-thread constant (class c = 2 (g - hh + 1) + e)
-        uint32_t band_bits = 0;
-#pragma unroll
-        for (int c = 0; c < 2 * (NG + 1); ++c) {
-            const int kk = 8 * ((c >> 1) - 1) + (c & 1) + fa;
-            if ((unsigned)kk < (unsigned)win && (kk & dmask) == 0) band_bits |= 1u << c;
-        }
-        const float inv_T = 1.f / (float)T, inv_H = 1.f / (float)gm.H;
-        const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
-        if (d_rpb)
-            for (int i = r; i < 4 * n_bias; i += 128) bias_acc[i] = 0.f;
-        if (rpb) {
-            // bias table of every head, once per CTA (barrier among the 4 compute warps only)
-            for (int i = r; i < gm.H * kBiasRowB; i += 128) {
-                const int hh_ = i / kBiasRowB, kk = i - hh_ * kBiasRowB - kBiasPad;
-                bias_tab[i] = (kk >= 0 && kk < win && (kk & dmask) == 0) ? __ldg(rpb + hh_ * gm.win + (kk >> dshift)) * kLog2e : 0.f;
-            }
-        }
-        if (rpb || d_rpb) asm volatile("bar.sync 1, 128;" ::: "memory");
-        int it = 0;
-        // log-sum-exp of the four fragment rows of a tile; loaded one tile ahead so the DRAM latency is hidden
-        auto load_lse = [&](int tile_, float (&dst)[2][2]) {
-            const int g0_ = tile_ * stride - right;
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const int gq = g0_ + warp * 32 + 16 * b + 8 * hh + fr;
-                    dst[b][hh] = (tile_ < total_tiles && gq >= 0 && gq < rows_total) ? __ldg(lse + gq) : 0.f;
-                }
-        };
-        float lse_next[2][2];
-        load_lse(blockIdx.x, lse_next);
-        int prev_hr = -1;
-        tc::RowCursor cur;  // row tile * stride = g0 + right
-        cur.init(blockIdx.x * stride, T, gm.H, gridDim.x * stride);
-        const int batch = gm.N / gm.H;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it, cur.advance()) {
-            const int g0 = tile * stride - right;
-            if constexpr (WB == 33) {
-                // Widest window bucket: the two 16-row blocks of the warp are processed one after the other in a ROLLED loop.
-                // 48 fragment values of S and of dP per block and thread: holding both blocks at once spilled registers, and
-                // the unrolled code of both did not fit the instruction cache (measured: 2-3x more cycles per tile).
-                if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 14); *abort_flag = 1; break; }
-                ptx::tc_fence_after_sync();
-                bool failed = false;
-#pragma unroll 1
-                for (int b = 0; b < 2; ++b) {
-                    // the two rows of this block this thread sees (row half hh): see the comments of the unrolled path below
-                    float lse2[2];
-                    int jb[2], vle[2], hrow[2];
-                    bool need_mask = false;
-                    {
-                        int tq, hq, bq;
-                        cur.row_at(warp * 32 + 16 * b + fr - right, inv_T, inv_H, tq, hq, bq);
-#pragma unroll
-                        for (int hh = 0; hh < 2; ++hh) {
-                            const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
-                            const bool live = gq >= 0 && gq < rows_total;
-                            const int vlr = !live ? 0 : valid_len ? min(T, __ldg(valid_len + min(max(bq, 0), batch - 1))) : T;
-                            hrow[hh] = hq;
-                            jb[hh] = tq - left + fa;
-                            vle[hh] = !live ? -1 : tq >= vlr ? 0 : vlr;
-                            need_mask |= tq < left || tq + right >= vlr;
-                            lse2[hh] = (b ? lse_next[1][hh] : lse_next[0][hh]) * kLog2e;
-                            tc::row_step8(T, gm.H, tq, hq, bq);
-                        }
-                    }
-                    need_mask = __any_sync(0xffffffffu, need_mask);
-                    float s1[4 * NG], d1[4 * NG];
-                    const uint32_t a = lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b);
-                    tc::ld_frag<NG>(a, s1);
-                    tc::ld_frag<NG>(a + kColDP, d1);
-                    ptx::tmem_ld_wait();
-                    if (b == 1) {  // S and dP of this tile are out of tensor memory
-                        ptx::tc_fence_before_sync();
-                        ptx::mbar_arrive(&misc->s_free);
-                    }
-                    float delta[2] = {0.f, 0.f};
-                    auto elements = [&](auto masked_tag) {
-                        constexpr bool kMasked = decltype(masked_tag)::value;
-#pragma unroll
-                        for (int g = 0; g < NG; ++g)
-#pragma unroll
-                            for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-                                for (int e = 0; e < 2; ++e) {
-                                    const int idx = 4 * g + 2 * hh + e;
-                                    const int kc = 8 * (g - hh) + e, kk = kc + fa;
-                                    bool on = (band_bits >> (2 * (g - hh + 1) + e)) & 1u;
-                                    float bias = 0.f;
-                                    if (rpb) bias = bias_tab[hrow[hh] * kBiasRowB + kBiasPad + kk];
-                                    float dot = s1[idx], dpv = d1[idx];
-                                    if constexpr (kMasked) {
-                                        const unsigned j = (unsigned)(jb[hh] + kc);
-                                        if (j >= (unsigned)T) { dot = 0.f; dpv = 0.f; }
-                                        if ((int)j >= vle[hh] || (int)j < 0) bias += mask2;
-                                        on = on && vle[hh] >= 0;
-                                    }
-                                    const float x = fmaf(dot, sc, bias) - lse2[hh];
-                                    const float p = on ? tc::fast_exp2(x) : 0.f;
-                                    s1[idx] = p;
-                                    d1[idx] = dpv;
-                                    delta[hh] = fmaf(p, dpv, delta[hh]);
-                                }
-                    };
-                    if (need_mask) elements(std::true_type{}); else elements(std::false_type{});
-                    delta[0] = tc::quad_sum(delta[0]);
-                    delta[1] = tc::quad_sum(delta[1]);
-                    if (b == 0) {
-                        // batch 2 of the previous tile must have finished reading the operand matrices before they are rewritten
-                        if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { failed = true; break; }
-                        if (d_rpb && it > 0)
-                            bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask,
-                                                      dshift, 1.f / gm.scale, bias_acc + warp * n_bias);
-                    }
-                    uint32_t pk_p[2 * NG], pk_d[2 * NG];
-#pragma unroll
-                    for (int g = 0; g < NG; ++g)
-#pragma unroll
-                        for (int hh = 0; hh < 2; ++hh) {
-                            const int idx = 4 * g + 2 * hh;
-                            float ds0 = s1[idx] * (d1[idx] - delta[hh]);
-                            float ds1 = s1[idx + 1] * (d1[idx + 1] - delta[hh]);
-                            float p0 = s1[idx], p1 = s1[idx + 1];
-                            if (need_mask) {
-                                const int kc = 8 * (g - hh), kk0 = kc + fa;
-                                const int j0 = jb[hh] + kc;
-                                const int row = warp * 32 + 16 * b + 8 * hh + fr;
-                                const bool own = d_rpb && row >= right && row < kTileM - left;
-                                const bool out0 = (unsigned)j0 >= (unsigned)T, out1 = (unsigned)(j0 + 1) >= (unsigned)T;
-                                if (out0 | out1) {
-                                    if (own) bias_grad_outside(bias_acc + warp * n_bias + hrow[hh] * gm.win, kk0, dshift, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
-                                    if (out0) { ds0 = 0.f; p0 = 0.f; }
-                                    if (out1) { ds1 = 0.f; p1 = 0.f; }
-                                }
-                            }
-                            pk_d[2 * g + hh] = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
-                            pk_p[2 * g + hh] = Cvt<E>::pack2(p0, p1);
-                        }
-                    const uint32_t blk = (uint32_t)(4 * warp + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * warp + 2 * b) * 128u;
-                    tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d, lane);
-                    tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
-                }
-                if (failed) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
-            } else {
-                // the four query rows this thread sees in the fragments: block b, row half hh (lse was fetched one tile ahead)
-                // The four rows this thread sees in the fragments (local rows 32 warp + fr + 8k; lse was fetched one tile ahead):
-                //   jb  : key index inside the row's own sequence of neighbour kk is jb + (kk - fa); outside [0, T) it is the
-                //         reference's zero-padded K/V row
-                //   vle : keys >= vle are masked (0 when the query itself is padding);  -1 marks a row outside the tensor
-                float lse2[2][2];
-                int jb[2][2], vle[2][2], hrow[2][2];
-                bool need_mask = false;
-                {
-                    int tq, hq, bq;
-                    cur.row_at(warp * 32 + fr - right, inv_T, inv_H, tq, hq, bq);
-    #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const int gq = g0 + warp * 32 + fr + 8 * k;
-                        const bool live = gq >= 0 && gq < rows_total;
-                        const int vlr = !live ? 0 : valid_len ? min(T, __ldg(valid_len + min(max(bq, 0), batch - 1))) : T;
-                        hrow[k >> 1][k & 1] = hq;
-                        jb[k >> 1][k & 1] = tq - left + fa;
-                        vle[k >> 1][k & 1] = !live ? -1 : tq >= vlr ? 0 : vlr;
-                        need_mask |= tq < left || tq + right >= vlr;
-                        lse2[k >> 1][k & 1] = lse_next[k >> 1][k & 1] * kLog2e;
-                        tc::row_step8(T, gm.H, tq, hq, bq);
-                    }
-                }
-                // masks are needed only when one of the warp's rows touches a sequence end or a padded region
-                need_mask = __any_sync(0xffffffffu, need_mask);
-                if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 14); *abort_flag = 1; break; }
-                ptx::tc_fence_after_sync();
-
-                float s[2][4 * NG], d[2][4 * NG];
-    #pragma unroll
-                for (int b = 0; b < 2; ++b) {
-                    const uint32_t a = lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b);
-                    tc::ld_frag<NG>(a, s[b]);
-                    tc::ld_frag<NG>(a + kColDP, d[b]);
-                }
-                ptx::tmem_ld_wait();
-                ptx::tc_fence_before_sync();
-                ptx::mbar_arrive(&misc->s_free);
-                float delta[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-                // two straight-line copies of the element loop, with and without masks
-                auto elements = [&](auto masked_tag) {
-                    constexpr bool kMasked = decltype(masked_tag)::value;
-    #pragma unroll
-                    for (int b = 0; b < 2; ++b)
-    #pragma unroll
-                        for (int g = 0; g < NG; ++g)
-    #pragma unroll
-                            for (int hh = 0; hh < 2; ++hh)
-    #pragma unroll
-                                for (int e = 0; e < 2; ++e) {
-                                    const int idx = 4 * g + 2 * hh + e;
-                                    const int kc = 8 * (g - hh) + e, kk = kc + fa;
-                                    bool on = (band_bits >> (2 * (g - hh + 1) + e)) & 1u;
-                                    float bias = 0.f;
-                                    if (rpb) bias = bias_tab[hrow[b][hh] * kBiasRowB + kBiasPad + kk];
-                                    float dot = s[b][idx], dpv = d[b][idx];
-                                    if constexpr (kMasked) {
-                                        const unsigned j = (unsigned)(jb[b][hh] + kc);
-                                        if (j >= (unsigned)T) { dot = 0.f; dpv = 0.f; }  // the reference's zero-padded K/V row
-                                        if ((int)j >= vle[b][hh] || (int)j < 0) bias += mask2;
-                                        on = on && vle[b][hh] >= 0;
-                                    }
-                                    const float x = fmaf(dot, sc, bias) - lse2[b][hh];
-                                    const float p = on ? tc::fast_exp2(x) : 0.f;
-                                    s[b][idx] = p;
-                                    d[b][idx] = dpv;
-                                    delta[b][hh] = fmaf(p, dpv, delta[b][hh]);
-                                }
-                };
-                if (need_mask) elements(std::true_type{}); else elements(std::false_type{});
-    #pragma unroll
-                for (int b = 0; b < 2; ++b)
-    #pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) delta[b][hh] = tc::quad_sum(delta[b][hh]);
-                // batch 2 of the previous tile must have finished reading the operand matrices before they are rewritten
-                if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
-                // Bias gradient of the PREVIOUS tile, read back from its dS operand now: while batch 2 runs its operand fetches own
-                // the shared-memory bandwidth and the same read-back took thousands of cycles; here the tensor pipe is done with it.
-                if (d_rpb && it > 0)
-                    bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask, dshift,
-                                              1.f / gm.scale, bias_acc + warp * n_bias);
-    #pragma unroll
-                for (int b = 0; b < 2; ++b) {
-                    uint32_t pk_p[2 * NG], pk_d[2 * NG];
-    #pragma unroll
-                    for (int g = 0; g < NG; ++g)
-    #pragma unroll
-                        for (int hh = 0; hh < 2; ++hh) {
-                            const int idx = 4 * g + 2 * hh;
-                            float ds0 = s[b][idx] * (d[b][idx] - delta[b][hh]);
-                            float ds1 = s[b][idx + 1] * (d[b][idx + 1] - delta[b][hh]);
-                            float p0 = s[b][idx], p1 = s[b][idx + 1];
-                            if (need_mask) {
-                                // a neighbour outside the query's sequence is a zero K/V row in the reference: its logit still has a
-                                // bias gradient, but it must not reach the other sequence's dK/dV nor this query's dQ
-                                const int kc = 8 * (g - hh), kk0 = kc + fa;
-                                const int j0 = jb[b][hh] + kc;
-                                const int row = warp * 32 + 16 * b + 8 * hh + fr;
-                                const bool own = d_rpb && row >= right && row < kTileM - left;
-                                const bool out0 = (unsigned)j0 >= (unsigned)T, out1 = (unsigned)(j0 + 1) >= (unsigned)T;
-                                if (out0 | out1) {
-                                    if (own) bias_grad_outside(bias_acc + warp * n_bias + hrow[b][hh] * gm.win, kk0, dshift, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
-                                    if (out0) { ds0 = 0.f; p0 = 0.f; }
-                                    if (out1) { ds1 = 0.f; p1 = 0.f; }
-                                }
-                            }
-                            pk_d[2 * g + hh] = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
-                            pk_p[2 * g + hh] = Cvt<E>::pack2(p0, p1);
-                        }
-                    // core matrix of the block's first row / first column: row group 4w+2b, column group 4w+2b
-                    const uint32_t blk = (uint32_t)(4 * warp + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * warp + 2 * b) * 128u;
-                    tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d, lane);
-                    tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
-                }
-            }
-            ptx::fence_proxy_async_smem();
-            ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(&misc->p_ready);
-            load_lse(tile + gridDim.x, lse_next);
-            if (d_rpb) {
-                // head of the row this lane will read back (-1: a row this tile does not own)
-                const int gr = g0 + r;
-                prev_hr = -1;
-                if (r >= right && r < kTileM - left && gr >= 0 && gr < rows_total) {
-                    int tr, br;
-                    cur.row_at(r - right, inv_T, inv_H, tr, prev_hr, br);
-                }
-            }
-        }
-        if (d_rpb && it > 0 && ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) && !*abort_flag)  // the last tile's share
-            bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask, dshift,
-                                      1.f / gm.scale, bias_acc + warp * n_bias);
-        if (d_rpb) {
-            // hand over this CTA's partial bias gradient: every compute thread arrives (also after an aborted loop), warp 0
-            // waits for all of them and writes row blockIdx.x of the partial-sum matrix (or adds to the result directly when
-            // the caller's scratch was too small for one row per CTA)
-            ptx::mbar_arrive(&misc->acc_done);
-            if (warp == 0 && ptx::mbar_wait(&misc->acc_done, 0)) {
-                for (int i = lane; i < n_bias; i += 32) {
-                    const float x = (bias_acc[i] + bias_acc[n_bias + i]) + (bias_acc[2 * n_bias + i] + bias_acc[3 * n_bias + i]);
-                    if (drpb_direct) { if (x != 0.f) atomicAdd(d_rpb + i, x); }
-                    else d_rpb[(size_t)blockIdx.x * n_bias + i] = x;
-                }
-            }
-        }
-    } else if (warp < 8) {
-        // ------------------------------------------------------------ epilogue warps (TMEM lanes 32(warp-4)..)
-        const int ew = warp - 4;
-        const int r = ew * 32 + lane;  // accumulator row m
-        const uint32_t lane_base = tmem + ((uint32_t)(ew * 32) << 16);
-        constexpr int CH = C / 8;
-        int it = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-            const int out_row = tile * stride;  // first flattened row this tile stores (dQ, dK and dV alike)
-            uint8_t* st = smem + (it % NS) * L.stage_bytes;
-            if (!ptx::mbar_wait_relaxed(&misc->o_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 15); *abort_flag = 1; break; }
-            ptx::tc_fence_after_sync();
-            // owned rows: dQ rows [right, right+stride), dK/dV rows [win-1, 128); both land on global rows
-            // [out_row, out_row+stride) and are staged from row 0 of the (now idle) Q / dO / K buffers
-            auto stage_rows = [&](uint8_t* buf, const float* acc, int m_first) {
-                const int ms = r - m_first;  // staging row
-                if (ms >= 0 && ms < stride) {
-                    const int swz = (C == 64) ? (ms & 7) : (C == 32) ? ((ms >> 1) & 3) : ((ms >> 2) & 1);
-#pragma unroll
-                    for (int c = 0; c < CH; ++c)
-                        *reinterpret_cast<uint4*>(buf + ms * kRowBytes + ((c ^ swz) * 16)) = Cvt<E>::pack(acc + c * 8);
-                }
-            };
-            if constexpr (OWN_OUT) {
-                // drain all three accumulators to 16-bit registers first so the MMA warp can reuse them, then
-                // one staging buffer, three rounds: stage -> TMA store -> wait until the store has read it
-                uint8_t* buf = smem + L.out;
-                uint4 pk[3][CH];
-#pragma unroll
-                for (int which = 0; which < 3; ++which) {  // 0: dQ, 1: dV, 2: dK = the MMA roles
-                    const uint32_t col = which == 0 ? kColDQ : which == 1 ? kColDV : kColDK;
-                    float acc[C];
-#pragma unroll
-                    for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + col + c, &acc[c]);
-                    ptx::tmem_ld_wait();
-                    ptx::tc_fence_before_sync();
-                    ptx::mbar_arrive(&misc->o_free[which]);
-#pragma unroll
-                    for (int c = 0; c < CH; ++c) pk[which][c] = Cvt<E>::pack(acc + c * 8);
-                }
-#pragma unroll
-                for (int which = 0; which < 3; ++which) {
-                    if (which > 0) asm volatile("bar.sync 2, 128;" ::: "memory");  // previous store has read the buffer
-                    const int ms = r - (which == 0 ? right : win - 1);
-                    if (ms >= 0 && ms < stride) {
-                        const int swz = (C == 64) ? (ms & 7) : (C == 32) ? ((ms >> 1) & 3) : ((ms >> 2) & 1);
-#pragma unroll
-                        for (int c = 0; c < CH; ++c) *reinterpret_cast<uint4*>(buf + ms * kRowBytes + ((c ^ swz) * 16)) = pk[which][c];
-                    }
-                    ptx::fence_proxy_async_smem();
-                    asm volatile("bar.sync 2, 128;" ::: "memory");
-                    if (tid == 128) {
-                        ptx::tma_store_3d(which == 0 ? &tm_dq : which == 1 ? &tm_dv : &tm_dk, buf, 0, out_row, 0);
-                        ptx::tma_store_commit();
-                        ptx::tma_store_wait_read();
-                    }
-                }
-                asm volatile("bar.sync 2, 128;" ::: "memory");
-            } else {
-                // no room for a staging buffer: use the tile's idle Q / dO / K buffers and release the stage afterwards
-                float acc[C];
-#pragma unroll
-                for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + kColDQ + c, &acc[c]);
-                ptx::tmem_ld_wait();
-                stage_rows(st + L.stage_q, acc, right);
-#pragma unroll
-                for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + kColDK + c, &acc[c]);
-                ptx::tmem_ld_wait();
-                stage_rows(st + L.stage_do, acc, win - 1);
-#pragma unroll
-                for (int c = 0; c < C; c += 8) ptx::tmem_ld8(lane_base + kColDV + c, &acc[c]);
-                ptx::tmem_ld_wait();
-                ptx::tc_fence_before_sync();
-                for (int i = 0; i < 3; ++i) ptx::mbar_arrive(&misc->o_free[i]);
-                stage_rows(st + L.stage_k, acc, win - 1);
-                ptx::fence_proxy_async_smem();
-                asm volatile("bar.sync 2, 128;" ::: "memory");
-                if (tid == 128) {
-                    ptx::tma_store_3d(&tm_dq, st + L.stage_q, 0, out_row, 0);
-                    ptx::tma_store_3d(&tm_dk, st + L.stage_do, 0, out_row, 0);
-                    ptx::tma_store_3d(&tm_dv, st + L.stage_k, 0, out_row, 0);
-                    ptx::tma_store_commit();
-                    ptx::tma_store_wait_read();
-                    // the staging used the tile's Q, dO and K buffers: only now may the producer refill them
-                    ptx::mbar_arrive(&misc->empty[it % NS][kQ]);
-                    ptx::mbar_arrive(&misc->empty[it % NS][kDO]);
-                    ptx::mbar_arrive(&misc->empty[it % NS][kK]);
-                }
-            }
-        }
-        if (tid == 128) ptx::tma_store_wait_all();
-    }
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    if (warp == 0) {
-        __syncwarp();
-        ptx::tmem_dealloc(tmem, kTmemCols);
-    }
-}
-
-// d_rpb[i] += sum over the CTAs' partial rows (column i of a (rows, n) matrix). One warp per entry: the lanes split the
-// rows (a single thread walking 148 dependent-latency loads made this tiny kernel cost 20 us), then a shuffle reduction.
-__global__ void bias_grad_reduce_kernel(float* __restrict__ d_rpb, const float* __restrict__ partial, int rows, int n) {
-    const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (i >= n) return;
-    float acc = 0.f;
-    for (int r = lane; r < rows; r += 32) acc += partial[(size_t)r * n + i];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) d_rpb[i] += acc;
-}
-
-template <typename E, int C, int WB>
-cudaError_t launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUtensorMap& mk, const CUtensorMap& mv,
-                       const CUtensorMap& mdq, const CUtensorMap& mdk, const CUtensorMap& mdv, float* d_rpb, float* scratch, size_t scratch_floats,
-                       const float* lse, const float* rpb, const int* valid_len, const Geometry& gm, int stride, int KT, int sm_count,
-                       cudaStream_t st) {
-    const int n_bias = gm.H * gm.win;
-    const BwdSmemLayout L = bwd_layout_for(C, KT, gm, rpb != nullptr, d_rpb != nullptr);
-    const int smem = L.total;
-    // only 64-channel rows can be too large for the dedicated output staging buffer
-    if constexpr (C != 64) {
-        if (!L.own_out) return cudaErrorInvalidValue;
-    }
-    auto kern = (C == 64 && !L.own_out) ? tc_bwd_kernel<E, C, WB, C != 64> : tc_bwd_kernel<E, C, WB, true>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    const int total = (gm.N * gm.T + stride - 1) / stride;
-    const int grid = total < sm_count ? total : sm_count;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = (size_t)smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = (pdl_mode() == 1 || pdl_mode() == 3) ? 1 : 0;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    // bias gradient: one partial row per CTA in the caller's scratch, summed by a second tiny kernel; if the scratch cannot
-    // hold grid rows the CTAs add their row to the result with atomics instead
-    const bool partial_rows = d_rpb && scratch && scratch_floats >= (size_t)grid * n_bias;
-    float* bias_out = !d_rpb ? nullptr : partial_rows ? scratch : d_rpb;
-    e = cudaLaunchKernelEx(&cfg, kern, mq, mdo, mk, mv, mdq, mdk, mdv, bias_out, partial_rows ? 0 : 1, lse, rpb, valid_len, gm,
-                           stride, KT, total);
-    if (e != cudaSuccess || !partial_rows) return e;
-    bias_grad_reduce_kernel<<<(n_bias + 7) / 8, 256, 0, st>>>(d_rpb, scratch, grid, n_bias);
-    return cudaGetLastError();
-}
-
-}  // namespace
+namespace na1d {
 
 bool tc_bwd_supports(const Geometry& gm, bool has_bias, bool wants_bias_grad) {
     if (!(tc::pow2(gm.dil) && (gm.C == 64 || gm.C == 32 || gm.C == 16) && tc::eff_window(gm.win, gm.dil) <= 33 && gm.H <= 32 &&
           gm.T >= 32 && gm.T < (1 << 21)))
         return false;
-    // 64-channel rows with the widest window bucket leave 1.5 KB of shared memory: a bias table of more than 4 heads or the
-    // bias-gradient accumulators do not fit there, and the call goes to the CUDA-core kernels
-    const int KT = round_up(kTileM + tc::eff_window(gm.win, gm.dil) - 1, 16);
-    return bwd_layout_for(gm.C, KT, gm, has_bias, wants_bias_grad).total <= 227 * 1024;
-}
-
-// Reads and clears the backward kernels' status word (synchronises the device).
-int tc_bwd_read_status() {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_tc_bwd_status, sizeof(int)) != cudaSuccess) return -1;
-    if (v != 0) cudaMemcpyToSymbol(g_tc_bwd_status, &zero, sizeof(int));
-    return v;
+    return bwd_smem_fits(gm, tc::eff_window(gm.win, gm.dil), has_bias, wants_bias_grad);
 }
 
 cudaError_t tc_fused_bwd(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
                          const void* v, const float* lse, const float* rpb, const int* valid_len, float* scratch,
                          size_t scratch_floats, const Geometry& gm, int dtype, cudaStream_t st) {
     if (!tc_bwd_supports(gm, rpb != nullptr, d_rpb != nullptr)) return cudaErrorInvalidValue;
-    bind_primary_context();
-    const int weff = tc::eff_window(gm.win, gm.dil);
-    const int KT = round_up(kTileM + weff - 1, 16);
-    const int stride = kTileM - (weff - 1);
-    const int rows = gm.N * gm.T;  // the tensors are tiled as one (N*T, C) matrix
-    CUtensorMap mq, mdo, mk, mv, mdq, mdk, mdv;
-    if (!make_row_tile_map(&mdq, dq, dtype, 1, rows, gm.C, stride) || !make_row_tile_map(&mdk, dk, dtype, 1, rows, gm.C, stride) ||
-        !make_row_tile_map(&mdv, dv, dtype, 1, rows, gm.C, stride))
-        return cudaErrorInvalidValue;
-    if (!make_row_tile_map(&mq, q, dtype, 1, rows, gm.C, kTileM) || !make_row_tile_map(&mdo, d_o, dtype, 1, rows, gm.C, kTileM) ||
-        !make_row_tile_map(&mk, k, dtype, 1, rows, gm.C, KT) || !make_row_tile_map(&mv, v, dtype, 1, rows, gm.C, KT))
-        return cudaErrorInvalidValue;
-    const int sms = device_sm_count();
-#define NA1D_TC_BWD(E, C, WB) \
-    return launch_bwd<E, C, WB>(mq, mdo, mk, mv, mdq, mdk, mdv, d_rpb, scratch, scratch_floats, lse, rpb, valid_len, gm, stride, KT, sms, st)
-#define NA1D_TC_BWD_W(E, C)                          \
-    if (weff <= 9) { NA1D_TC_BWD(E, C, 9); }       \
-    else if (weff <= 17) { NA1D_TC_BWD(E, C, 17); } \
-    else { NA1D_TC_BWD(E, C, 33); }
-#define NA1D_TC_BWD_C(E)                         \
-    if (gm.C == 64) { NA1D_TC_BWD_W(E, 64) }     \
-    else if (gm.C == 32) { NA1D_TC_BWD_W(E, 32) } \
-    else { NA1D_TC_BWD_W(E, 16) }
-    if (dtype == 0) { NA1D_TC_BWD_C(__nv_bfloat16) } else { NA1D_TC_BWD_C(__half) }
-#undef NA1D_TC_BWD
-#undef NA1D_TC_BWD_W
-#undef NA1D_TC_BWD_C
+    if (dtype != 0) return tc_bwd_flat_fp16(dq, dk, dv, d_rpb, d_o, q, k, v, lse, rpb, valid_len, scratch, scratch_floats, gm, st);
+    return run_flat<__nv_bfloat16>(dq, dk, dv, d_rpb, d_o, q, k, v, lse, rpb, valid_len, scratch, scratch_floats, gm, 0, st);
+}
+
+int tc_bwd_read_status() {
+    const int a = read_status_word(), b = tc_bwd_fp16_read_status();
+    return (a > 0 || b > 0) ? (a > 0 ? a : b) : (a < 0 || b < 0) ? -1 : 0;
 }
 
 }  // namespace na1d

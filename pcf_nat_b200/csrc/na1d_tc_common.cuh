@@ -194,6 +194,41 @@ __device__ __forceinline__ void row_step8(int T, int H, int& tq, int& hq, int& b
     }
 }
 
+// Position of a tile in the segmented tiling as a mixed-radix counter (tile in sequence, residue, head, batch): two
+// divisions at the start; afterwards a persistent CTA moves from tile to tile with adds and compares only.
+struct SegCursor {
+    int i, r, h, b;
+    int si, sr, sh, sb;   // digits of the step between two tiles of this CTA
+    int tps, d, H;
+    __device__ __forceinline__ static void split(int x, int tps, int d, int H, int& i, int& r, int& h, int& b) {
+        int s = x / tps;
+        i = x - s * tps;
+        int hv = s / d;
+        r = s - hv * d;
+        b = hv / H;
+        h = hv - b * H;
+    }
+    __device__ __forceinline__ void init(int tile, int step_tiles, const SegGeom& g, int H_) {
+        tps = g.tps; d = g.d; H = H_;
+        split(tile, tps, d, H, i, r, h, b);
+        split(step_tiles, tps, d, H, si, sr, sh, sb);
+    }
+    __device__ __forceinline__ void advance() {
+        i += si;
+        int c = i >= tps ? 1 : 0;
+        i -= c ? tps : 0;
+        r += sr + c;
+        c = r >= d ? 1 : 0;
+        r -= c ? d : 0;
+        h += sh + c;
+        c = h >= H ? 1 : 0;
+        h -= c ? H : 0;
+        b += sb + c;
+    }
+    // tokens of the tile's residue sequence
+    __device__ __forceinline__ int rows(const SegGeom& g) const { return g.Tp - (r >= g.ra ? 1 : 0); }
+};
+
 // Column sums of a 32 x NV matrix held one row per lane (NV = 8, 16 or 32): a butterfly in which every step halves the
 // number of columns a lane still carries, NV - 1 + log2(32 / NV) shuffles in all instead of 5 NV. Returns the sum of column
 // lane / (32 / NV); each column's sum is replicated on the 32 / NV lanes that share that quotient.
@@ -230,6 +265,11 @@ __device__ __forceinline__ float quad_max(float x) {
 
 // Tensor map over a dense (N, T, C) 16-bit tensor viewed as dims (C, T, N), box (C, rows, 1).
 bool make_row_tile_map(CUtensorMap* map, const void* base, int dtype, int N, int T, int C, int box_rows);
+// The pair of 5-D tensor maps (channel, token-in-residue, residue, head, batch) of the segmented tiling over a tensor with
+// the given strides: maps[0] covers the residues r < ra (Tp tokens each), maps[1] the residues r >= ra (Tp - 1 tokens,
+// residue coordinate r - ra); with ra == d the second is a copy of the first. Box (C, box_rows, 1, 1, 1).
+bool make_seg_tile_maps(CUtensorMap* maps, const void* base, int dtype, int batch, int H, int T, int C, const Strides& st,
+                        const SegGeom& sg, int box_rows);
 int device_sm_count();
 void bind_primary_context();
 bool pdl_enabled();

@@ -1,452 +1,11 @@
-// Fused NA1D forward on the Blackwell tensor path (sm_100a): persistent, warp-specialised,
-// TMA-staged tiles, tcgen05 MMAs with accumulators (and the probability operand) in tensor memory.
-//
-// Rows are tiled over the FLATTENED (sequence, token) axis: tile i is rows g0 = 128 i .. g0+127 of the (N*T, C) matrix,
-// so every tile is full whatever T is. A tile may span several sequences; a neighbour outside the query's own sequence is
-// what the reference reads as a zero-padded row (na1d_tensorcore/bf16_ana1d_kernel.cu:99-112): its logit is rpb - 100 and
-// it contributes nothing to the output, which is enforced per element.
-// Per tile (224 threads, up to two CTAs per SM):
-//   warp 4  : TMA producer -- Q[128 x C] and K, V rows [g0-left, g0-left+KT), KT = round16(128+win-1),
-//             into a 2-stage ring. Plain (non-multicast) tile loads; rows outside [0,T) arrive as
-//             zeros, which is the reference's zero padding of K and V
-//             (na1d_tensorcore/bf16_ana1d_kernel.cu:99-112).
-//   warps 5,6: MMA issuers -- S = Q.K^T (C/16 steps, M=128, N=KT) into TMEM columns [0,KT);
-//             O = P.V (KT/16 steps, N=C) with P read from TMEM and V as an MN-major operand straight
-//             from the TMA tile. A tcgen05.mma costs its issuing thread ~120 cycles whatever its size, so
-//             the key steps of P.V are split between two issuers with an accumulator each (even / odd
-//             steps); the epilogue adds the two.
-//   warps0-3: softmax on the band only. Warp w owns rows 32w..32w+31 as two 16-row accumulator
-//             fragments (see na1d_tc_common.cuh): scale, + rpb, + (-100) mask, row max / sum with two
-//             quad shuffles each, normalise, round to 16 bits -- the reference rounds probabilities to
-//             16 bits before its A.V product too (bf16_ana1d_kernel.cu:301-306) -- and store P over the
-//             S columns of TMEM (zeros outside the band). Later the same warps read O from TMEM, stage it
-//             in the tile's idle V buffer and one thread issues a TMA tile store (rows >= T are clipped).
-// Every wait is bounded; on expiry the CTA records a code in a device status word and unwinds
-// (TMEM is always released).
-#include "na1d_internal.h"
-#include <type_traits>
-#include "na1d_tc_common.cuh"
+// tcgen05 forward, flat tiling over the dense (N*T, C) matrix: instantiations and host entry points.
+#include "na1d_tc_fwd_kernel.cuh"
 
 namespace na1d {
 
-__device__ int g_tc_status = 0;
-
-namespace {
-
-using tc::kTileM;
-using tc::round_up;
-using tc::RowSwizzle;
-using tc::Fmt;
-constexpr int kThreads = 224;  // 4 softmax warps, producer/store warp, two MMA issuer warps
-constexpr int kTmemCols = 256;
-constexpr int kOCol = 192;   // O accumulator of the even key steps; S (fp32) and then P (16-bit pairs) use [0, KT), KT <= 160
-constexpr int kOColB = 96;   // O accumulator of the odd key steps: inside the S columns, which are dead once softmax has read
-                             // them (P only needs the packed columns [0, KT/2 <= 80))
-constexpr int kBiasPad = 16;
-
-struct FwdSmemLayout {
-    int q, ring, stage_k, stage_v, stage_bytes, misc, total;  // q: the single Q buffer; ring: first K/V stage
-};
-__host__ __device__ inline FwdSmemLayout fwd_layout(int C, int KT, int bias_heads) {
-    FwdSmemLayout L;
-    // Q is needed only by the S MMAs at the start of a tile, so one buffer serves both stages: it is refilled as soon as
-    // those MMAs retire. K and V live in a 2-stage ring; the finished O is staged in the tile's V buffer (idle once the
-    // P.V MMAs have retired). 16 KB less than a Q buffer per stage: two CTAs per SM also for the widest window bucket.
-    L.q = 0;
-    L.ring = round_up(kTileM * C * 2, 1024);
-    L.stage_k = 0;
-    L.stage_v = round_up(KT * C * 2, 1024);
-    L.stage_bytes = 2 * round_up(KT * C * 2, 1024);
-    L.misc = L.ring + 2 * L.stage_bytes;
-    L.total = L.misc + 256 + round_up(2 * bias_heads * (kBiasPad + 48) * 4, 256) + 1008;  // misc, two bias tables, alignment slack
-    return L;
-}
-
-struct alignas(8) FwdMisc {
-    uint64_t full[2], empty[2];  // K/V ring
-    uint64_t full_q, empty_q;    // the single Q buffer
-    uint64_t s_ready, p_ready, o_ready, o_free, o_staged;
-    uint32_t tmem_base;
-    int abort;
-};
-constexpr int kBiasRow = kBiasPad + 48;  // per-head table: log2e * rpb[h][kk] at index kk + kBiasPad, kk in [-16, 48)
-
-template <typename E, int C, int WB>
-__global__ void __launch_bounds__(kThreads, 2)
-tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, float* __restrict__ lse,
-              const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, int KT, int total_tiles) {
-    constexpr int NG = tc::band_groups(WB);
-    constexpr int kRowBytes = C * 2;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const FwdSmemLayout L = fwd_layout(C, KT, rpb ? gm.H : 0);
-    FwdMisc* misc = reinterpret_cast<FwdMisc*>(smem + L.misc);
-    float* bias_tab = reinterpret_cast<float*>(smem + L.misc + 256);
-    const int rows_total = gm.N * gm.T;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // effective (dilated) window: neighbour kk of the reference is offset kk * dil of it
-    const int dil = gm.dil, dmask = dil - 1, dshift = 31 - __clz(dil);
-    const int win = tc::eff_window(gm.win, dil), left = gm.left * dil, T = gm.T;
-    const int stage_tx = 2 * KT * kRowBytes;
-
-    // Loads of tile `tile` (iteration `it` of this CTA): Q into the single Q buffer, K and V into ring stage it % 2.
-    auto produce = [&](int tile, int it) -> bool {
-        const int s = it & 1, k = it >> 1;
-        const int g0 = tile * kTileM;
-        // Q: free once the S MMAs of the previous tile have retired
-        if (!ptx::mbar_wait_relaxed(&misc->empty_q, (it & 1) ^ 1) || *(volatile int*)&misc->abort) return false;
-        // At the start every CTA of the grid loads at once and DRAM is the limit: let the first tile land before the
-        // second is requested, so that all CTAs start computing (and storing) early instead of at the end of the burst.
-        if (it == 1 && !ptx::mbar_wait_relaxed(&misc->full[0], 0)) return false;
-        ptx::mbar_expect_tx(&misc->full_q, (uint32_t)(kTileM * kRowBytes));
-        ptx::tma_load_3d(smem + L.q, &tm_q, &misc->full_q, 0, g0, 0);
-        // K, V: free once the tile two back has stored its output (staged in its V buffer)
-        if (!ptx::mbar_wait_relaxed(&misc->empty[s], (k & 1) ^ 1) || *(volatile int*)&misc->abort) return false;
-        uint8_t* st = smem + L.ring + s * L.stage_bytes;
-        ptx::mbar_expect_tx(&misc->full[s], (uint32_t)stage_tx);
-        ptx::tma_load_3d(st + L.stage_k, &tm_k, &misc->full[s], 0, g0 - left, 0);
-        ptx::tma_load_3d(st + L.stage_v, &tm_v, &misc->full[s], 0, g0 - left, 0);
-        return true;
-    };
-    bool first_ok = true;
-    if (tid == 4 * 32) {
-        // The producer thread sets up the barriers and requests the CTA's first tile at once: the loads are in flight
-        // while the other warps allocate tensor memory and meet at the barrier below.
-        for (int s = 0; s < 2; ++s) { ptx::mbar_init(&misc->full[s], 1); ptx::mbar_init(&misc->empty[s], 1); }
-        ptx::mbar_init(&misc->full_q, 1);
-        ptx::mbar_init(&misc->empty_q, 1);
-        ptx::mbar_init(&misc->s_ready, 1);
-        ptx::mbar_init(&misc->p_ready, 128);
-        ptx::mbar_init(&misc->o_ready, 2);  // one commit per MMA issuer
-        ptx::mbar_init(&misc->o_free, 128);
-        ptx::mbar_init(&misc->o_staged, 128);
-        misc->abort = 0;
-        ptx::fence_mbar_init();
-        ptx::prefetch_tensormap(&tm_q);
-        ptx::prefetch_tensormap(&tm_k);
-        ptx::prefetch_tensormap(&tm_v);
-        ptx::prefetch_tensormap(&tm_o);
-        // global memory written by the predecessor kernel is read from here on
-        ptx::grid_dependency_wait();
-        first_ok = produce((int)blockIdx.x, 0);
-    }
-    if (warp == 0) {
-        ptx::tmem_alloc(&misc->tmem_base, kTmemCols);
-        ptx::tmem_relinquish();
-    }
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    ptx::tc_fence_after_sync();
-    const uint32_t tmem = misc->tmem_base;
-    volatile int* abort_flag = &misc->abort;
-    // Outputs are written from here on: wait for the predecessor, and let the successor start its own set-up as this
-    // grid drains.
-    ptx::grid_launch_dependents();
-    ptx::grid_dependency_wait();
-
-    if (warp == 4) {
-        // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            int it = 1;
-            bool ok = first_ok;
-            for (int tile = blockIdx.x + gridDim.x; ok && tile < total_tiles; tile += gridDim.x, ++it) ok = produce(tile, it);
-            if (!ok) { atomicExch(&g_tc_status, 1); *abort_flag = 1; }
-        } else if (lane == 1) {
-            // ---------------------------------------------------------- output store thread: waits until the softmax warps
-            // have staged a tile's O, issues the TMA store, and frees the stage once the store has read shared memory
-            int it = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-                if (!ptx::mbar_wait_relaxed(&misc->o_staged, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 6); *abort_flag = 1; break; }
-                ptx::tma_store_3d(&tm_o, smem + L.ring + (it & 1) * L.stage_bytes + L.stage_v, 0, tile * kTileM, 0);
-                ptx::tma_store_commit();
-                ptx::tma_store_wait_read();
-                ptx::mbar_arrive(&misc->empty[it & 1]);
-            }
-            ptx::tma_store_wait_all();
-        }
-    } else if (warp == 5) {
-        // ------------------------------------------------------------ MMA issuer A: S, and the even key steps of P.V
-        if (lane == 0) {
-            const uint32_t idesc_s = ptx::instr_desc(Fmt<E>::v, 0, 0, kTileM, (uint32_t)KT);
-            const uint32_t idesc_o = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);
-            const int nks = KT / 16;
-            int it = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-                const int s = it & 1, k = it >> 1;
-                const uint32_t st = ptx::smem_u32(smem + L.ring + s * L.stage_bytes);
-                // S overwrites the columns that held the previous tile's P and odd-step accumulator: both must be drained
-                if (!ptx::mbar_wait(&misc->full[s], k & 1) || !ptx::mbar_wait(&misc->full_q, it & 1) ||
-                    !ptx::mbar_wait(&misc->o_free, (it & 1) ^ 1) || *abort_flag) {
-                    atomicExch(&g_tc_status, 2); *abort_flag = 1; break;
-                }
-                ptx::tc_fence_after_sync();
-                {
-                    const uint64_t a0 = ptx::smem_desc(ptx::smem_u32(smem + L.q), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                    const uint64_t b0 = ptx::smem_desc(st + L.stage_k, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-#pragma unroll
-                    for (int ks = 0; ks < C / 16; ++ks)
-                        ptx::mma_ss(tmem, tc::desc_advance(a0, ks * 32), tc::desc_advance(b0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
-                }
-                ptx::mma_commit(&misc->empty_q);  // Q is read by nothing else
-                ptx::mma_commit(&misc->s_ready);
-                if (!ptx::mbar_wait(&misc->p_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 3); *abort_flag = 1; break; }
-                ptx::tc_fence_after_sync();
-                {
-                    const uint64_t b0 = ptx::smem_desc(st + L.stage_v, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
-#pragma unroll 1
-                    for (int ks = 0; ks < nks; ks += 2)
-                        ptx::mma_ts(tmem + kOCol, tmem + ks * 8, tc::desc_advance(b0, ks * 16 * kRowBytes), idesc_o, ks > 0 ? 1u : 0u);
-                }
-                ptx::mma_commit(&misc->o_ready);
-            }
-        }
-    } else if (warp == 6) {
-        // ------------------------------------------------------------ MMA issuer B: the odd key steps of P.V
-        if (lane == 0) {
-            const uint32_t idesc_o = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);
-            const int nks = KT / 16;
-            int it = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-                const int s = it & 1, k = it >> 1;
-                const uint32_t st = ptx::smem_u32(smem + L.ring + s * L.stage_bytes);
-                if (!ptx::mbar_wait(&misc->full[s], k & 1) || !ptx::mbar_wait(&misc->p_ready, it & 1) || *abort_flag) {
-                    atomicExch(&g_tc_status, 7); *abort_flag = 1; break;
-                }
-                ptx::tc_fence_after_sync();
-                const uint64_t b0 = ptx::smem_desc(st + L.stage_v, 0, 8 * kRowBytes, RowSwizzle<C>::umma);
-#pragma unroll 1
-                for (int ks = 1; ks < nks; ks += 2)
-                    ptx::mma_ts(tmem + kOColB, tmem + ks * 8, tc::desc_advance(b0, ks * 16 * kRowBytes), idesc_o, ks > 1 ? 1u : 0u);
-                ptx::mma_commit(&misc->o_ready);
-            }
-        }
-    } else {
-        // ------------------------------------------------------------ softmax / epilogue warps
-        const int r = warp * 32 + lane;
-        const int fr = lane >> 2, fc = 2 * (lane & 3);
-        const int fa = fc - fr;
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        const float sc = gm.scale * kLog2e;
-        const float mask2 = kMaskValue * kLog2e;
-        // which of the thread's fragment slots are neighbours: slot (g, hh, e) is window offset 8 (g - hh) + e + fa, the same
-        // for every tile, so the band test is one bit of a per-thread constant (class c = 2 (g - hh + 1) + e)
-        uint32_t band_bits = 0;
-#pragma unroll
-        for (int c = 0; c < 2 * (NG + 1); ++c) {
-            const int kk = 8 * ((c >> 1) - 1) + (c & 1) + fa;
-            if ((unsigned)kk < (unsigned)win && (kk & dmask) == 0) band_bits |= 1u << c;
-        }
-        const float inv_T = 1.f / (float)T, inv_H = 1.f / (float)gm.H;
-        if (rpb) {
-            // bias table of every head, once per CTA (barrier among the 4 softmax warps only)
-            // two copies, the second shifted by one entry: a thread reads the biases of its two adjacent columns with one
-            // 8-byte load whatever the parity of its first offset
-            for (int i = r; i < 2 * gm.H * kBiasRow; i += 128) {
-                const int copy = i / (gm.H * kBiasRow), j = i - copy * gm.H * kBiasRow;
-                const int hh_ = j / kBiasRow, kk = j - hh_ * kBiasRow - kBiasPad + copy;
-                bias_tab[i] = (kk >= 0 && kk < win && (kk & dmask) == 0) ? __ldg(rpb + hh_ * gm.win + (kk >> dshift)) * kLog2e : 0.f;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-        }
-        int it = 0;
-        tc::RowCursor cur;
-        cur.init(blockIdx.x * kTileM, T, gm.H, gridDim.x * kTileM);
-        const int batch = gm.N / gm.H;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it, cur.advance()) {
-            const int g0 = tile * kTileM;
-            // The four rows this thread sees in the fragments (block b, row half hh = local rows 32 warp + fr + 8k). Per row:
-            //   jb  : key index inside the row's own sequence of neighbour kk is jb + (kk - fa); outside [0, T) it is the
-            //         reference's zero-padded key row
-            //   vle : keys >= vle are masked (0 when the query itself is padding)
-            int jb[2][2], vle[2][2];
-            const float* brow[2][2];
-            bool need_mask = false;
-            {
-                int tq, hq, bq;
-                cur.row_at(warp * 32 + fr, inv_T, inv_H, tq, hq, bq);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const bool live = g0 + warp * 32 + fr + 8 * k < rows_total;
-                    const int vlr = !live ? 0 : valid_len ? min(T, __ldg(valid_len + min(bq, batch - 1))) : T;
-                    brow[k >> 1][k & 1] = bias_tab + ((fa & 1) ? gm.H * kBiasRow - 1 : 0) + hq * kBiasRow + kBiasPad + fa;
-                    jb[k >> 1][k & 1] = tq - left + fa;
-                    vle[k >> 1][k & 1] = tq >= vlr ? 0 : vlr;
-                    need_mask |= tq < left || tq + (win - 1 - left) >= vlr;
-                    tc::row_step8(T, gm.H, tq, hq, bq);
-                }
-            }
-            // masks are needed only when one of the warp's rows touches a sequence end or a padded region
-            need_mask = __any_sync(0xffffffffu, need_mask);
-            if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 4); *abort_flag = 1; break; }
-            ptx::tc_fence_after_sync();
-
-            float s[2][4 * NG];
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-                tc::ld_frag<NG>(lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b), s[b]);
-            ptx::tmem_ld_wait();
-            // logits on the band (log2 domain), everything else -inf; two straight-line copies, with and without masks
-            float mx[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}};
-            auto logits = [&](auto masked_tag) {
-                constexpr bool kMasked = decltype(masked_tag)::value;
-#pragma unroll
-                for (int b = 0; b < 2; ++b)
-#pragma unroll
-                    for (int g = 0; g < NG; ++g)
-#pragma unroll
-                        for (int hh = 0; hh < 2; ++hh) {
-                            float2 bias2 = make_float2(0.f, 0.f);  // biases of the thread's two adjacent columns of this group
-                            if (rpb) bias2 = *reinterpret_cast<const float2*>(brow[b][hh] + 8 * (g - hh));
-#pragma unroll
-                            for (int e = 0; e < 2; ++e) {
-                                const int idx = 4 * g + 2 * hh + e;
-                                const int kc = 8 * (g - hh) + e;  // window offset minus the lane constant fa
-                                const bool inband = (band_bits >> (2 * (g - hh + 1) + e)) & 1u;
-                                float bias = e ? bias2.y : bias2.x;
-                                float dot = s[b][idx];
-                                if constexpr (kMasked) {
-                                    const unsigned j = (unsigned)(jb[b][hh] + kc);
-                                    if (j >= (unsigned)T) dot = 0.f;  // key outside the query's own sequence: the reference's zero row
-                                    if (j >= (unsigned)vle[b][hh]) bias += mask2;
-                                }
-                                const float x = inband ? fmaf(dot, sc, bias) : -INFINITY;
-                                s[b][idx] = x;
-                                mx[b][hh] = fmaxf(mx[b][hh], x);
-                            }
-                        }
-            };
-            if (need_mask) logits(std::true_type{}); else logits(std::false_type{});
-            float sum[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) mx[b][hh] = tc::quad_max(mx[b][hh]);
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-                for (int g = 0; g < NG; ++g)
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int idx = 4 * g + 2 * hh + e;
-                            const float p = tc::fast_exp2(s[b][idx] - mx[b][hh]);  // exp2(-inf) = 0 outside the band
-                            s[b][idx] = p;
-                            sum[b][hh] += p;
-                        }
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    sum[b][hh] = tc::quad_sum(sum[b][hh]);
-                    const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
-                    if (lse && (lane & 3) == 0 && gq < rows_total) lse[gq] = (mx[b][hh] + tc::fast_log2(sum[b][hh])) * kLn2;
-                    sum[b][hh] = tc::fast_rcp(sum[b][hh]);
-                }
-            // P over the S columns. Per 16-lane block the band occupies NGP 8-key groups starting at the block's own
-            // first row; every other 16-key chunk of the row range is zeroed. The two sets are disjoint, so one wait.
-            {
-                constexpr int NGP = NG + (NG & 1);  // band groups padded to whole 16-key chunks
-                const uint32_t zeros[4] = {0, 0, 0, 0};
-#pragma unroll
-                for (int b = 0; b < 2; ++b) {
-                    const uint32_t blk = lane_base + ((uint32_t)(16 * b) << 16);
-                    const int c0 = 2 * warp + b;  // first band chunk (16 keys = 8 packed columns) of this block
-                    for (int ci = 0; ci < KT / 16; ++ci)
-                        if (ci < c0 || ci >= c0 + NGP / 2) tc::st_pack2(blk + ci * 8, zeros);
-                    uint32_t pk[2 * NGP];
-#pragma unroll
-                    for (int g = 0; g < NGP; ++g)
-#pragma unroll
-                        for (int hh = 0; hh < 2; ++hh) {
-                            if (g >= NG) { pk[2 * g + hh] = 0u; continue; }
-                            float p0 = s[b][4 * g + 2 * hh] * sum[b][hh], p1 = s[b][4 * g + 2 * hh + 1] * sum[b][hh];
-                            if (need_mask) {
-                                // a neighbour outside the query's sequence is a zero V row in the reference: it counts in the
-                                // softmax denominator but must not pick up the other sequence's values
-                                const int j0 = jb[b][hh] + 8 * (g - hh);
-                                if ((unsigned)j0 >= (unsigned)T) p0 = 0.f;
-                                if ((unsigned)(j0 + 1) >= (unsigned)T) p1 = 0.f;
-                            }
-                            pk[2 * g + hh] = Cvt<E>::pack2(p0, p1);
-                        }
-                    tc::st_pack<NGP>(blk + c0 * 8, pk);
-                }
-                ptx::tmem_st_wait();
-            }
-            ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(&misc->p_ready);
-
-            // epilogue: O -> 16 bits -> the tile's idle V buffer (same swizzle as the tensor map) -> TMA store
-            if (!ptx::mbar_wait(&misc->o_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 5); *abort_flag = 1; break; }
-            ptx::tc_fence_after_sync();
-            {
-                uint8_t* sO = smem + L.ring + (it & 1) * L.stage_bytes + L.stage_v;  // this tile's V buffer: P.V has retired
-                // row r, 16-byte chunk c at r*rowbytes + ((c ^ swz(r)) * 16): the TMA swizzle of this row size
-                const int swz = (C == 64) ? (r & 7) : (C == 32) ? ((r >> 1) & 3) : ((r >> 2) & 1);
-                constexpr int HALF = C >= 32 ? C / 2 : C;  // columns per round (two rounds keep the register count down)
-#pragma unroll
-                for (int c0 = 0; c0 < C; c0 += HALF) {
-                    float acc[HALF], accb[HALF];
-#pragma unroll
-                    for (int c = 0; c < HALF; c += 8) {
-                        ptx::tmem_ld8(lane_base + kOCol + c0 + c, &acc[c]);
-                        ptx::tmem_ld8(lane_base + kOColB + c0 + c, &accb[c]);
-                    }
-                    ptx::tmem_ld_wait();
-                    if (c0 + HALF >= C) {
-                        ptx::tc_fence_before_sync();
-                        ptx::mbar_arrive(&misc->o_free);
-                    }
-#pragma unroll
-                    for (int c = 0; c < HALF; ++c) acc[c] += accb[c];
-#pragma unroll
-                    for (int c = 0; c < HALF / 8; ++c)
-                        *reinterpret_cast<uint4*>(sO + r * kRowBytes + (((c0 / 8 + c) ^ swz) * 16)) = Cvt<E>::pack(&acc[c * 8]);
-                }
-                ptx::fence_proxy_async_smem();
-                ptx::mbar_arrive(&misc->o_staged);  // the store thread takes it from here
-            }
-        }
-    }
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    if (warp == 0) {
-        __syncwarp();
-        ptx::tmem_dealloc(tmem, kTmemCols);
-    }
-}
-
-template <typename E, int C, int WB>
-cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, float* lse,
-                       const float* rpb, const int* valid_len, const Geometry& gm, int KT, int sm_count, cudaStream_t st) {
-    const int smem = fwd_layout(C, KT, rpb ? gm.H : 0).total;
-    auto kern = tc_fwd_kernel<E, C, WB>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    const int total = (gm.N * gm.T + kTileM - 1) / kTileM;
-    const int per_sm = (2 * (smem + 1024) <= 227 * 1024) ? 2 : 1;
-    const int slots = sm_count * per_sm;
-    const int grid = total < slots ? total : slots;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = (size_t)smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = (pdl_mode() == 1 || pdl_mode() == 2) ? 1 : 0;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mo, lse, rpb, valid_len, gm, KT, total);
-}
-
-}  // namespace
-
 bool tc_fwd_supports(const Geometry& gm) {
-    return tc::pow2(gm.dil) && (gm.C == 64 || gm.C == 32 || gm.C == 16) && tc::eff_window(gm.win, gm.dil) <= 33 && gm.H <= 32 && gm.T >= 32 && gm.T < (1 << 21);
+    return tc::pow2(gm.dil) && (gm.C == 64 || gm.C == 32 || gm.C == 16) && tc::eff_window(gm.win, gm.dil) <= 33 && gm.H <= 32 &&
+           gm.T >= 32 && gm.T < (1 << 21);
 }
 
 cudaError_t tc_fused_fwd(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
@@ -454,34 +13,16 @@ cudaError_t tc_fused_fwd(void* o, float* lse, const void* q, const void* k, cons
     if (!tc_fwd_supports(gm)) return cudaErrorInvalidValue;
     bind_primary_context();
     const int weff = tc::eff_window(gm.win, gm.dil);
-    const int KT = round_up(kTileM + weff - 1, 16);
+    const int KT = tc::round_up(tc::kTileM + weff - 1, 16);
     const int rows = gm.N * gm.T;  // the tensors are tiled as one (N*T, C) matrix
-    CUtensorMap mq, mk, mv, mo;
-    if (!make_row_tile_map(&mq, q, dtype, 1, rows, gm.C, kTileM) || !make_row_tile_map(&mk, k, dtype, 1, rows, gm.C, KT) ||
-        !make_row_tile_map(&mv, v, dtype, 1, rows, gm.C, KT) || !make_row_tile_map(&mo, o, dtype, 1, rows, gm.C, kTileM))
+    FwdMaps<1> maps;
+    if (!make_row_tile_map(&maps.q[0], q, dtype, 1, rows, gm.C, tc::kTileM) || !make_row_tile_map(&maps.k[0], k, dtype, 1, rows, gm.C, KT) ||
+        !make_row_tile_map(&maps.v[0], v, dtype, 1, rows, gm.C, KT) || !make_row_tile_map(&maps.o[0], o, dtype, 1, rows, gm.C, tc::kTileM))
         return cudaErrorInvalidValue;
-    const int sms = device_sm_count();
-#define NA1D_TC_FWD(E, C, WB) return launch_fwd<E, C, WB>(mq, mk, mv, mo, lse, rpb, valid_len, gm, KT, sms, st)
-#define NA1D_TC_FWD_W(E, C)                          \
-    if (weff <= 9) { NA1D_TC_FWD(E, C, 9); }       \
-    else if (weff <= 17) { NA1D_TC_FWD(E, C, 17); } \
-    else { NA1D_TC_FWD(E, C, 33); }
-#define NA1D_TC_FWD_C(E)                         \
-    if (gm.C == 64) { NA1D_TC_FWD_W(E, 64) }     \
-    else if (gm.C == 32) { NA1D_TC_FWD_W(E, 32) } \
-    else { NA1D_TC_FWD_W(E, 16) }
-    if (dtype == 0) { NA1D_TC_FWD_C(__nv_bfloat16) } else { NA1D_TC_FWD_C(__half) }
-#undef NA1D_TC_FWD
-#undef NA1D_TC_FWD_W
-#undef NA1D_TC_FWD_C
+    const int total = (rows + tc::kTileM - 1) / tc::kTileM;
+    return dispatch_fwd<false>(maps, lse, rpb, valid_len, gm, SegGeom{1, 1, gm.T, 0, tc::kTileM}, KT, total, weff, dtype, st);
 }
 
-// Reads and clears the device status word (synchronises the device). 0 = no bounded wait expired.
-int tc_read_status() {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
-    if (v != 0) cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
-    return v;
-}
+int tc_read_status() { return read_status_word(); }
 
 }  // namespace na1d

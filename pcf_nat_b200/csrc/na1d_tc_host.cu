@@ -3,6 +3,9 @@
 #include "na1d_tc_common.cuh"
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
 
 namespace na1d {
 namespace {
@@ -25,20 +28,104 @@ EncodeTiledFn encode_fn() {
 
 }  // namespace
 
+// ---- cache of encoded tensor maps ---------------------------------------------------------------------------------
+// A CUtensorMap is a pure function of the arguments of cuTensorMapEncodeTiled, so the encoded 128 bytes are memoised under
+// those arguments (pointer, data type, rank, extents, strides, box, swizzle): a training loop that calls a layer with the
+// same buffers every step -- or replays a pool of them -- pays the driver call once. Bounded; cleared when full.
+namespace {
+
+struct MapKey {
+    uint64_t v[16];
+    bool operator==(const MapKey& o) const { return memcmp(v, o.v, sizeof(v)) == 0; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        uint64_t h = 1469598103934665603ull;
+        for (uint64_t x : k.v) { h ^= x; h *= 1099511628211ull; }
+        return (size_t)h;
+    }
+};
+struct MapValue { CUtensorMap map; };
+
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, MapValue, MapKeyHash>& map_cache() {
+    static auto* m = new std::unordered_map<MapKey, MapValue, MapKeyHash>();  // never destroyed: safe at process exit
+    return *m;
+}
+std::atomic<long long> g_map_hits{0}, g_map_misses{0};
+constexpr size_t kMaxCachedMaps = 4096;
+
+bool encode_cached(CUtensorMap* out, const void* base, int dtype, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+                   const cuuint32_t* box, CUtensorMapSwizzle sw) {
+    MapKey key;
+    memset(&key, 0, sizeof(key));
+    int dev = 0;
+    cudaGetDevice(&dev);
+    key.v[0] = reinterpret_cast<uint64_t>(base);
+    key.v[1] = (uint64_t)dtype | ((uint64_t)rank << 8) | ((uint64_t)sw << 16) | ((uint64_t)dev << 32);
+    for (int i = 0; i < rank; ++i) key.v[2 + i] = dims[i];
+    for (int i = 0; i + 1 < rank; ++i) key.v[7 + i] = strides[i];
+    for (int i = 0; i < rank; ++i) key.v[11 + i] = box[i];
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        auto it = map_cache().find(key);
+        if (it != map_cache().end()) {
+            *out = it->second.map;
+            g_map_hits.fetch_add(1, std::memory_order_relaxed);
+            return true;
+        }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    const CUtensorMapDataType dt = dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    MapValue val;
+    if (fn(&val.map, dt, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    g_map_misses.fetch_add(1, std::memory_order_relaxed);
+    *out = val.map;
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (map_cache().size() >= kMaxCachedMaps) map_cache().clear();
+    map_cache().emplace(key, val);
+    return true;
+}
+
+CUtensorMapSwizzle row_swizzle(int C) {
+    return C == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : C == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+}
+
+}  // namespace
+
+void tensor_map_cache_stats(long long* hits, long long* misses) {
+    *hits = g_map_hits.load();
+    *misses = g_map_misses.load();
+}
+
 // Tensor map over a dense (N, T, C) 16-bit tensor viewed as dims (C, T, N), box (C, box_rows, 1).
 // The swizzle mode follows the row size (128/64/32 bytes) so that a staged tile is directly a
 // canonical tcgen05 operand. Out-of-range rows read as zeros and are skipped on stores.
 bool make_row_tile_map(CUtensorMap* map, const void* base, int dtype, int N, int T, int C, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
     const cuuint64_t dims[3] = {(cuuint64_t)C, (cuuint64_t)T, (cuuint64_t)N};
     const cuuint64_t strides[2] = {(cuuint64_t)C * 2, (cuuint64_t)T * C * 2};
     const cuuint32_t box[3] = {(cuuint32_t)C, (cuuint32_t)box_rows, 1};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    const CUtensorMapSwizzle sw = C == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : C == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
-    const CUtensorMapDataType dt = dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    return fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return encode_cached(map, base, dtype, 3, dims, strides, box, row_swizzle(C));
+}
+
+bool make_seg_tile_maps(CUtensorMap* maps, const void* base, int dtype, int batch, int H, int T, int C, const Strides& st,
+                        const SegGeom& sg, int box_rows) {
+    // every global stride must be a multiple of 16 bytes (element strides a multiple of 8) and the base 16-byte aligned
+    if ((st.token % 8) || (st.head % 8) || (st.batch % 8) || (reinterpret_cast<uintptr_t>(base) & 15u)) return false;
+    const cuuint64_t strides[4] = {(cuuint64_t)st.token * sg.d * 2, (cuuint64_t)st.token * 2, (cuuint64_t)st.head * 2,
+                                   (cuuint64_t)st.batch * 2};
+    const cuuint32_t box[5] = {(cuuint32_t)C, (cuuint32_t)box_rows, 1, 1, 1};
+    const cuuint64_t dims_a[5] = {(cuuint64_t)C, (cuuint64_t)sg.Tp, (cuuint64_t)sg.ra, (cuuint64_t)H, (cuuint64_t)batch};
+    if (!encode_cached(&maps[0], base, dtype, 5, dims_a, strides, box, row_swizzle(C))) return false;
+    if (sg.ra == sg.d) { maps[1] = maps[0]; return true; }
+    if (sg.Tp < 2) return false;
+    const cuuint64_t dims_b[5] = {(cuuint64_t)C, (cuuint64_t)(sg.Tp - 1), (cuuint64_t)(sg.d - sg.ra), (cuuint64_t)H, (cuuint64_t)batch};
+    const uint8_t* base_b = static_cast<const uint8_t*>(base) + (size_t)sg.ra * st.token * 2;
+    return encode_cached(&maps[1], base_b, dtype, 5, dims_b, strides, box, row_swizzle(C));
 }
 
 // Programmatic dependent launch is off unless NA1D_PDL (read once) says otherwise (measured: it shortens back-to-back

@@ -19,6 +19,7 @@ import types
 import torch
 import torch.nn as nn
 
+from . import ops
 from .library_op import na1d_fused
 
 
@@ -84,11 +85,20 @@ def _fused_forward(self, x, padding=None):
         N, T, C = x.shape
     if float(self.attn_drop.p) != 0.0 and self.training:
         raise NotImplementedError("attention dropout > 0 is not fused (the reference's configs use 0)")
-    q, k, v = _split_heads(self.qkv(x), layout, self.num_heads, getattr(self, "groups", 1))
     valid_len = None
     if not self.training and padding is not None:
         # eval: the mask follows the utterance's padding (PCF_NATransformer.py:131-134); training uses the constant mask
         valid_len = (T - padding.to(torch.int64)).clamp_(0, T).to(torch.int32).expand(N).contiguous()
+    qkv = self.qkv(x)
+    hd = C // self.num_heads
+    if (layout == "channels_last" and type(qkv) is torch.Tensor and qkv.is_cuda and not torch.compiler.is_compiling() and
+            ops.packed_supported(self.num_heads, T, hd, self.win_size, self.left, self.dilation, qkv.dtype)):
+        # the kernels read q, k, v straight out of the packed projection output and write the output in the layout
+        # `proj` consumes: no head split / merge copies (MFA_NATransformer.py:127-137, :151-152), forward or backward
+        o = ops.na1d_fused_packed(qkv, self.num_heads, self.win_size, self.left, self.dilation, float(self.scale),
+                                  self.relative_position_bias, valid_len)
+        return self.proj_drop(self.proj(o))
+    q, k, v = _split_heads(qkv, layout, self.num_heads, getattr(self, "groups", 1))
     o = na1d_fused(q, k, v, self.win_size, self.left, self.dilation, float(self.scale), self.relative_position_bias,
                    valid_len, self.num_heads)
     return self.proj_drop(self.proj(_merge_heads(o, layout, N, self.num_heads)))

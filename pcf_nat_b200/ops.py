@@ -161,6 +161,112 @@ def fused_backward(d_o, q, k, v, o, lse, win, left, dil=1, scale=1.0, rpb=None, 
     return dq, dk, dv, d_rpb
 
 
+# ------------------------------------------------------------------ strided (layout-fused) forms
+def _strides3(t, C):
+    """{batch, head, token} element strides of a 4-D view addressed [batch][head][token][channel]."""
+    if t.dim() != 4 or t.stride(3) != 1 or t.shape[3] != C:
+        raise ValueError("expected a (batch, heads, T, C) view with unit channel stride, got shape %s strides %s"
+                         % (tuple(t.shape), t.stride()))
+    return (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def fused_forward_strided(q, k, v, o, win, left, dil=1, scale=1.0, rpb=None, valid_len=None, need_lse=True):
+    """Fused forward on strided views: q, k, v, o are (batch, heads, T, C) VIEWS (any batch/head/token strides that are
+    multiples of 8 elements, channel stride 1), e.g. the slices of a packed projection output and an output buffer laid
+    out (batch, T, heads, C). Writes o in place and returns lse (batch*heads, T) fp32. Raises ``Na1dError`` with status
+    -10 when the tcgen05 kernels cannot take the shape (the caller then makes dense copies)."""
+    _need_cuda(q, k, v, o)
+    B, H, T, C = q.shape
+    assert k.shape == q.shape and v.shape == q.shape and o.shape == q.shape and q.dtype == k.dtype == v.dtype == o.dtype
+    lse = torch.empty((B * H, T), dtype=torch.float32, device=q.device) if need_lse else None
+    r = _prep_rpb(rpb, H, win, q.device)
+    vl = _prep_valid(valid_len, B, q.device)
+    with _on_device(q.device):
+        check(_L.na1d_fused_forward_strided(_p(o), _p(lse), _p(q), _p(k), _p(v), _p(r), _p(vl), _strides3(o, C), _strides3(q, C),
+                                            _strides3(k, C), _strides3(v, C), B * H, H, T, C, win, left, dil, float(scale),
+                                            _dtype_code(q), _stream(q)), "na1d_fused_forward_strided")
+    return lse
+
+
+def fused_backward_strided(d_o, q, k, v, lse, dq, dk, dv, win, left, dil=1, scale=1.0, rpb=None, valid_len=None,
+                           need_d_rpb=False):
+    """Gradients on strided views (all (batch, heads, T, C) views); writes dq, dk, dv in place, returns d_rpb or None."""
+    _need_cuda(d_o, q, k, v, lse, dq, dk, dv)
+    B, H, T, C = q.shape
+    r = _prep_rpb(rpb, H, win, q.device)
+    vl = _prep_valid(valid_len, B, q.device)
+    d_rpb = scratch = None
+    n_scratch = 0
+    if need_d_rpb:
+        d_rpb = torch.zeros((H, win), dtype=torch.float32, device=q.device)
+        n_scratch = 160 * H * win          # one partial row per CTA (one CTA per SM)
+        scratch = torch.empty(n_scratch, dtype=torch.float32, device=q.device)
+    with _on_device(q.device):
+        check(_L.na1d_fused_backward_strided(_p(dq), _p(dk), _p(dv), _p(d_rpb), _p(d_o), _p(q), _p(k), _p(v), _p(lse), _p(r),
+                                             _p(vl), _p(scratch), n_scratch, _strides3(dq, C), _strides3(dk, C),
+                                             _strides3(dv, C), _strides3(d_o, C), _strides3(q, C), _strides3(k, C),
+                                             _strides3(v, C), B * H, H, T, C, win, left, dil, float(scale), _dtype_code(q),
+                                             _stream(q)), "na1d_fused_backward_strided")
+    return d_rpb
+
+
+class NA1dFusedPackedFunction(torch.autograd.Function):
+    """The fused layer core on a PACKED projection output: ``qkv`` is (batch, T, 3*heads*C) as the channels-last ``qkv``
+    projection writes it (models/MFA_NATransformer.py:127: viewed as (batch, T, 3, heads, C)), the result is
+    (batch, T, heads*C) as the output projection reads it (:151-152). The head split, the head merge and their autograd
+    copies do not exist: the kernels address q, k, v, o, d_o, dq, dk, dv through strided tensor maps. Saves (qkv, lse) only
+    -- the tcgen05 backward needs neither o nor the probabilities."""
+
+    @staticmethod
+    def forward(ctx, qkv, heads, win_size, left, dilation=1, scale=1.0, rpb=None, valid_len=None):
+        B, T, C3 = qkv.shape
+        C = C3 // (3 * heads)
+        qkv = qkv.contiguous()
+        p = qkv.view(B, T, 3, heads, C)
+        q, k, v = (p[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        out = torch.empty((B, T, heads * C), dtype=qkv.dtype, device=qkv.device)
+        lse = fused_forward_strided(q, k, v, out.view(B, T, heads, C).permute(0, 2, 1, 3), win_size, left, dilation, scale, rpb,
+                                    valid_len)
+        ctx.save_for_backward(qkv, lse, rpb if rpb is not None else torch.empty(0),
+                              valid_len if isinstance(valid_len, torch.Tensor) else torch.empty(0))
+        ctx.cfg = (heads, win_size, left, dilation, scale, rpb is not None,
+                   valid_len if not isinstance(valid_len, torch.Tensor) else "tensor")
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        qkv, lse, rpb, vl_t = ctx.saved_tensors
+        heads, win, left, dil, scale, has_rpb, vl = ctx.cfg
+        valid_len = vl_t if vl == "tensor" else vl
+        B, T, C3 = qkv.shape
+        C = C3 // (3 * heads)
+        p = qkv.view(B, T, 3, heads, C)
+        q, k, v = (p[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        d_qkv = torch.empty_like(qkv)
+        g = d_qkv.view(B, T, 3, heads, C)
+        dq, dk, dv = (g[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        d_o = d_out.contiguous().view(B, T, heads, C).permute(0, 2, 1, 3)
+        need_rpb = has_rpb and ctx.needs_input_grad[6]
+        d_rpb = fused_backward_strided(d_o, q, k, v, lse, dq, dk, dv, win, left, dil, scale, rpb if has_rpb else None, valid_len,
+                                       need_d_rpb=need_rpb)
+        if d_rpb is not None:
+            d_rpb = d_rpb.reshape(rpb.shape).to(rpb.dtype)
+        return d_qkv, None, None, None, None, None, d_rpb, None
+
+
+def na1d_fused_packed(qkv, heads, win_size, left, dilation=1, scale=1.0, rpb=None, valid_len=None):
+    """``(batch, T, 3*heads*C)`` packed projection output -> ``(batch, T, heads*C)`` attention output, no layout copies."""
+    return NA1dFusedPackedFunction.apply(qkv, int(heads), int(win_size), int(left), int(dilation), float(scale), rpb, valid_len)
+
+
+def packed_supported(heads, T, C, win, left, dil, dtype, has_bias=True, wants_bias_grad=True):
+    """Whether ``na1d_fused_packed`` can take this shape, forward and backward (host-only query of the library)."""
+    if dtype not in (torch.bfloat16, torch.float16):
+        return False
+    code = _lib.NA1D_BF16 if dtype == torch.bfloat16 else _lib.NA1D_FP16
+    return _L.na1d_fused_strided_supported(heads, T, C, win, left, dil, code, int(has_bias), int(wants_bias_grad)) == 1
+
+
 class NA1dFusedFunction(torch.autograd.Function):
     """o = softmax(scale*q.k^T + rpb + mask) . v over each query's window, as one op.
 
@@ -205,7 +311,7 @@ def window_index(T, win, left, dil=1, device="cuda"):
     return j, inr.bool()
 
 
-FAMILY_AUTO, FAMILY_CUDA_CORE, FAMILY_TCGEN05 = -1, 0, 1
+FAMILY_AUTO, FAMILY_CUDA_CORE, FAMILY_TCGEN05, FAMILY_TCGEN05_SEGMENTED = -1, 0, 1, 2
 
 
 def set_kernel_family(family):
@@ -217,6 +323,19 @@ def kernel_family(N, T, C, win, left, dil, dtype, backward=False):
     """0 = CUDA-core kernels, 1 = tcgen05/TMA kernels, negative = status code (forced family unsupported)."""
     code = _lib.NA1D_BF16 if dtype == torch.bfloat16 else _lib.NA1D_FP16
     return _L.na1d_fused_kernel_family(N, T, C, win, left, dil, code, 1 if backward else 0)
+
+
+def kernel_tiling(N, T, C, win, left, dil, dtype, backward=False):
+    """0 = CUDA-core kernels, 1 = tcgen05 on the flat tiling, 2 = tcgen05 on the segmented tiling, negative = status code."""
+    code = _lib.NA1D_BF16 if dtype == torch.bfloat16 else _lib.NA1D_FP16
+    return _L.na1d_fused_kernel_tiling(N, T, C, win, left, dil, code, 1 if backward else 0)
+
+
+def tensor_map_cache_stats():
+    """(hits, misses) of the library's cache of encoded TMA tensor maps."""
+    h, m = ctypes.c_int64(0), ctypes.c_int64(0)
+    check(_L.na1d_tensor_map_cache_stats(ctypes.byref(h), ctypes.byref(m)), "na1d_tensor_map_cache_stats")
+    return h.value, m.value
 
 
 def device_status():

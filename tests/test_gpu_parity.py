@@ -298,12 +298,15 @@ def test_tcgen05_forward_backward_shapes(dtype):
             assert_close(dk, dk_r, dtype, tag + "dk")
             assert_close(dv, dv_r, dtype, tag + "dv")
             assert_close(drpb, drpb_r, dtype, tag + "drpb", factor=2.0)
-        # shapes outside the family are refused when it is forced, and taken by the CUDA-core kernels otherwise
-        assert ops.kernel_family(2, 64, 64, 7, 3, 3, dtype) == -10    # dilation not a power of two
-        assert ops.kernel_family(2, 64, 64, 15, 7, 4, dtype) == -10   # dilated window wider than 33
+        # with the tcgen05 family forced: dilations and short sequences the flat tiling cannot take go to the segmented tiling,
+        # channel counts outside {16, 32, 64} are refused (and taken by the CUDA-core kernels otherwise)
+        assert ops.kernel_tiling(2, 64, 64, 7, 3, 3, dtype) == 2     # dilation not a power of two
+        assert ops.kernel_tiling(2, 64, 64, 15, 7, 4, dtype) == 2    # dilated window wider than 33
+        assert ops.kernel_tiling(2, 16, 64, 7, 3, 1, dtype) == 2     # sequences shorter than 32 tokens
+        assert ops.kernel_tiling(2, 200, 64, 7, 3, 1, dtype) == 1
         assert ops.kernel_family(2, 64, 24, 7, 3, 1, dtype) == -10
-        assert ops.kernel_family(2, 16, 64, 7, 3, 1, dtype) == -10    # sequences shorter than 32 tokens
+        assert ops.kernel_family(2, 64, 64, 40, 20, 1, dtype) == -10  # window wider than the widest band bucket
     finally:
         ops.set_kernel_family(old)
-    assert ops.kernel_family(2, 64, 64, 7, 3, 3, dtype) == 0
-    assert ops.kernel_family(2, 16, 64, 7, 3, 1, dtype) == 0
+    assert ops.kernel_family(2, 64, 24, 7, 3, 1, dtype) == 0
+    assert ops.kernel_family(2, 64, 64, 40, 20, 1, dtype) == 0
