@@ -111,14 +111,15 @@ static int pick_family(const na1d::Geometry& g, int backward, bool has_bias = fa
     if (forced == 2) return seg_ok ? 2 : NA1D_ERR_UNSUPPORTED;
     int pick = 0;
     if (flat_ok && seg_ok && g.dil > 1) {
-        // relative cost of a tile row in the window buckets 9 / 17 / 33 (measured: the compute warps' share grows with
-        // the bucket) times the rows the tiling processes per useful row
-        auto bucket_cost = [](int w) { return w <= 9 ? 1.0 : w <= 17 ? 1.25 : 2.0; };
+        // relative cost of a tile row in the window buckets 9 / 17 / 33 (measured at 64 utterances x 4 heads, 200 to 1000
+        // tokens: the two narrow buckets cost about the same, the widest is bound by its compute warps), times the rows the
+        // tiling processes per useful row, plus 10 % for the segmented tiling's shorter runs of tiles
+        auto bucket_cost = [](int w) { return w <= 9 ? 1.0 : w <= 17 ? 1.05 : 1.5; };
         const int tp = (g.T + g.dil - 1) / g.dil;
         const int step = backward ? 128 - (g.win - 1) : 128;
         const double seg_rows = (double)((tp + step - 1) / step) * step / tp;
-        const double flat = bucket_cost((g.win - 1) * g.dil + 1), seg = bucket_cost(g.win) * seg_rows;
-        pick = seg < 0.9 * flat ? 2 : 1;
+        const double flat = bucket_cost((g.win - 1) * g.dil + 1), seg = 1.1 * bucket_cost(g.win) * seg_rows;
+        pick = seg < flat ? 2 : 1;
     } else if (flat_ok) {
         pick = 1;
     } else if (seg_ok) {
