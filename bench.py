@@ -623,6 +623,8 @@ def main():
     ap.add_argument("--quick", action="store_true", help="with --sweep: a bf16, D=64 subset")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"], help="model workloads: split or replicate the batch")
     ap.add_argument("--attention", default="fused", choices=["fused", "unfused"], help="model workloads: operator variant")
+    ap.add_argument("--precision", default="autocast", choices=["bf16", "autocast"],
+                    help="model workloads: bf16 weights/activations with fp32 master weights, or bf16 autocast over fp32 parameters")
     args = ap.parse_args()
     if args.sweep:
         return run_sweep(args)

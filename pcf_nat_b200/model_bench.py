@@ -65,25 +65,67 @@ def _timed_steps(step, n, dev, world):
     return parallel.max_over_ranks(e0.elapsed_time(e1), dev)
 
 
-class TrainStep:
-    """forward + backward + gradient all-reduce + AdamW of the extractor on one rank's share of the batch."""
+def _bf16_body(model, dev):
+    """Mixed precision without autocast: the body of the network (front end, attention stages, fusion, pooling) gets bf16
+    weights that are views into ONE flat bf16 buffer, refreshed after every update from an fp32 master copy; the small tail
+    (batch norm, embedding, loss) stays fp32 as views into the same master. Returns (master fp32 flat parameter, flat bf16
+    body weights, number of body elements, body parameters, tail parameters)."""
+    tail_mods = (model.bn, model.embed, model.loss)
+    tail_ids = {id(p) for m in tail_mods for p in m.parameters()}
+    body = [p for p in model.parameters() if id(p) not in tail_ids]
+    tail = [p for p in model.parameters() if id(p) in tail_ids]
+    master = torch.cat([p.detach().float().reshape(-1) for p in body + tail]).to(dev)
+    nb = sum(p.numel() for p in body)
+    flat_w = master[:nb].to(torch.bfloat16)
+    off = 0
+    for p in body:
+        p.data = flat_w[off:off + p.numel()].view_as(p)
+        off += p.numel()
+    for p in tail:
+        p.data = master[off:off + p.numel()].view_as(p)
+        off += p.numel()
+    return torch.nn.Parameter(master), flat_w, nb, body, tail
 
-    def __init__(self, per_gpu, dev, world, rank, attention="fused", frames=FRAMES, use_graphs=True):
+
+class TrainStep:
+    """forward + backward + gradient all-reduce + AdamW of the extractor on one rank's share of the batch.
+
+    precision "bf16" (default): bf16 weights and activations in the body with fp32 master weights, fp32 gradients for the
+    all-reduce and the update (no autocast: no per-call weight and activation casts); "autocast": fp32 parameters under
+    ``torch.autocast(bfloat16)`` as the reference's ``train_main.py`` runs."""
+
+    def __init__(self, per_gpu, dev, world, rank, attention="fused", frames=FRAMES, use_graphs=True, precision="autocast"):
         import torch.distributed as dist
+        from . import parallel
         from .model import PCFNATExtractor
-        self.dist, self.world, self.dev = dist, world, dev
+        self.dist, self.world, self.dev, self.parallel, self.precision = dist, world, dev, parallel, precision
         torch.manual_seed(4)
         self.model = PCFNATExtractor(frames=frames, attention=attention).to(dev)
-        from . import parallel
-        self.parallel = parallel
-        params = [p for p in self.model.parameters() if p.requires_grad]
-        # every gradient is a view into one flat fp32 buffer: one all-reduce per step, no bucketing logic
-        self.flat = parallel.flat_gradient_buffer(params)
-        self.n_params = self.flat.numel()
-        self.opt = torch.optim.AdamW(params, lr=1e-4, fused=True, capturable=True)
         g = torch.Generator(device=dev).manual_seed(4 + rank)
         self.fbank = torch.randn(per_gpu, FEAT, frames, device=dev, generator=g)
         self.labels = torch.randint(0, CLASSES, (per_gpu,), device=dev, generator=g)
+        if precision == "bf16":
+            self.master, self.flat_w, self.nb, body, tail = _bf16_body(self.model, dev)
+            self.n_params = self.master.numel()
+            # gradients: the body's arrive in bf16 (views into one buffer) and are widened into the fp32 buffer that is
+            # all-reduced and handed to the optimizer; the tail's are views into that buffer directly
+            self.flat = torch.zeros(self.n_params, dtype=torch.float32, device=dev)
+            self.body_grad = torch.zeros(self.nb, dtype=torch.bfloat16, device=dev)
+            off = 0
+            for p in body:
+                p.grad = self.body_grad[off:off + p.numel()].view_as(p)
+                off += p.numel()
+            for p in tail:
+                p.grad = self.flat[off:off + p.numel()].view_as(p)
+                off += p.numel()
+            self.master.grad = self.flat
+            self.opt = torch.optim.AdamW([self.master], lr=1e-4, fused=True, capturable=True)
+        else:
+            params = [p for p in self.model.parameters() if p.requires_grad]
+            # every gradient is a view into one flat fp32 buffer: one all-reduce per step, no bucketing logic
+            self.flat = parallel.flat_gradient_buffer(params)
+            self.n_params = self.flat.numel()
+            self.opt = torch.optim.AdamW(params, lr=1e-4, fused=True, capturable=True)
         self.loss = None
         self.graph_a = self.graph_b = None
         # eager warm-up on a side stream (cuBLAS workspaces, autotuning, AdamW state), then capture
@@ -93,7 +135,7 @@ class TrainStep:
             for _ in range(3):
                 self._forward_backward()
                 self._sync_gradients()
-                self.opt.step()
+                self._update()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         self.launch = "eager"
@@ -103,19 +145,30 @@ class TrainStep:
                 self._forward_backward()
             self.graph_b = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph_b):
-                self.opt.step()
+                self._update()
             self.launch = "graph A (zero grads, forward, backward) -> eager NCCL all-reduce -> graph B (AdamW)" if world > 1 else \
                 "graph A (zero grads, forward, backward) -> graph B (AdamW)"
 
     def _forward_backward(self):
         self.flat.zero_()
-        with torch.autocast("cuda", dtype=torch.bfloat16, cache_enabled=False):
-            loss = self.model(self.fbank, self.labels)
-        loss.backward()
+        if self.precision == "bf16":
+            self.body_grad.zero_()
+            loss = self.model(self.fbank.to(torch.bfloat16), self.labels)
+            loss.backward()
+            self.flat[:self.nb].copy_(self.body_grad)
+        else:
+            with torch.autocast("cuda", dtype=torch.bfloat16, cache_enabled=False):
+                loss = self.model(self.fbank, self.labels)
+            loss.backward()
         self.loss = loss.detach()
 
     def _sync_gradients(self):
         self.parallel.all_reduce_mean(self.flat)
+
+    def _update(self):
+        self.opt.step()
+        if self.precision == "bf16":
+            self.flat_w.copy_(self.master.detach()[:self.nb])
 
     def __call__(self):
         if self.graph_a is not None:
@@ -125,7 +178,7 @@ class TrainStep:
         else:
             self._forward_backward()
             self._sync_gradients()
-            self.opt.step()
+            self._update()
         return self.loss
 
     def allreduce_ms(self, n=10):
@@ -152,7 +205,7 @@ def run_train(args):
     global_batch = 256
     lo, hi = parallel.shard_range(global_batch, world, rank) if args.scaling == "strong" else (0, global_batch)
     per_gpu = hi - lo
-    ts = TrainStep(per_gpu, dev, world, rank, attention=args.attention)
+    ts = TrainStep(per_gpu, dev, world, rank, attention=args.attention, precision=args.precision)
     for _ in range(max(args.warmup, 3)):
         ts()
     ops.device_status()
@@ -185,7 +238,9 @@ def run_train(args):
                        "progressive channel fusion, attentive statistics pooling, 192-d embedding, AAM-softmax over 5994 classes",
                        "global_batch": total, "per_gpu_batch": per_gpu, "frames": FRAMES, "attention": args.attention,
                        "parameters": ts.n_params, "launch": ts.launch, "parallelism": "dp%d" % world,
-                       "batchnorm": "per-GPU statistics", "optimizer": "AdamW (fused)", "precision": "bf16 autocast, fp32 master weights and gradients"},
+                       "batchnorm": "per-GPU statistics", "optimizer": "AdamW (fused)",
+                       "precision": "bf16 weights and activations in the body, fp32 master weights, fp32 gradient all-reduce and update"
+                       if args.precision == "bf16" else "bf16 autocast over fp32 parameters"},
             "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak * world, "unit": "TFLOP/s", "frac": tflops / (peak * world),
                          "traffic": None, "peak_kind": peak_kind + " sustained bf16 GEMM x ranks",
                          "note": "matmul FLOPs of the whole model (3x forward); the step is bound by PyTorch's elementwise, "
@@ -202,11 +257,13 @@ def run_train(args):
 class Extractor:
     """Embedding extraction of one rank's share of a set of utterances, in batches of up to `batch` utterances."""
 
-    def __init__(self, n_local, dev, rank, batch=512, frames=FRAMES, attention="fused"):
+    def __init__(self, n_local, dev, rank, batch=512, frames=FRAMES, attention="fused", precision="autocast"):
         from .model import PCFNATExtractor
         torch.manual_seed(4)
         self.model = PCFNATExtractor(frames=frames, attention=attention).to(dev).eval()
-        self.dev, self.frames = dev, frames
+        self.dev, self.frames, self.precision = dev, frames, precision
+        if precision == "bf16":
+            _bf16_body(self.model, dev)
         g = torch.Generator(device=dev).manual_seed(40 + rank)
         self.fbank = torch.randn(n_local, FEAT, frames, device=dev, generator=g)
         # utterance lengths: 2 to 3 s, sorted as the reference's length-bucketed loader delivers them
@@ -237,6 +294,8 @@ class Extractor:
             t = torch.arange(self.frames, device=x.device).view(1, 1, -1)
             mask = (t < lens.view(-1, 1, 1)).to(x.dtype)
             x = x - (x * mask).sum(-1, keepdim=True) / lens.view(-1, 1, 1).to(x.dtype)
+            if self.precision == "bf16":
+                return self.model.embedding(x.to(torch.bfloat16), (self.frames - lens).to(torch.int32)).float()
             with torch.autocast("cuda", dtype=torch.bfloat16, cache_enabled=False):
                 return self.model.embedding(x, (self.frames - lens).to(torch.int32)).float()
 
@@ -260,7 +319,7 @@ def run_embed(args):
     if total % world:
         raise SystemExit("the utterance count %d must divide by the number of ranks" % total)
     n_local = total // world if args.scaling == "strong" else total
-    ex = Extractor(n_local, dev, rank, attention=args.attention)
+    ex = Extractor(n_local, dev, rank, attention=args.attention, precision=args.precision)
     gathered = torch.empty(world * n_local, EMB, device=dev)
 
     def step(source=None):
