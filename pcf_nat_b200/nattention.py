@@ -138,6 +138,47 @@ class NAttention(nn.Module):
     forward = _fused_forward
 
 
+def global_padding_mask(T, padding=None, dtype=torch.float32, device="cpu"):
+    """The additive mask of the dense layers (PCF_NATransformer.py:406-414): -100 where the query or the key is a padded
+    frame, 0 elsewhere; shape ``(N, 1, T, T)``."""
+    if padding is None:
+        padding = torch.zeros(1, dtype=torch.int, device=device)
+    bad = torch.arange(T, device=padding.device).unsqueeze(0) >= (T - padding.unsqueeze(1))     # (N, T)
+    both = bad.unsqueeze(-1) | bad.unsqueeze(-2)
+    return torch.zeros(both.shape, device=padding.device, dtype=dtype).masked_fill(both, -100.0).unsqueeze(1)
+
+
+def _global_forward(self, x, pos_emb, attn_mask=None):
+    N, C, T = x.shape
+    x = x + self.linear_pos(pos_emb)
+    q, k, v = _split_heads(self.qkv(x), "channels_first", self.num_heads, self.groups)
+    hd = C // self.num_heads
+    q, k, v = (t.view(N, self.num_heads, T, hd) for t in (q, k, v))
+    mask = None if attn_mask is None else attn_mask.to(q.dtype)
+    drop = float(self.attn_drop.p) if self.training else 0.0
+    o = torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=mask, dropout_p=drop, scale=float(self.scale))
+    return self.proj_drop(self.proj(_merge_heads(o.reshape(N * self.num_heads, T, hd), "channels_first", N, self.num_heads)))
+
+
+class GlobalAttention(nn.Module):
+    """Drop-in for the reference's dense attention layer (``win_size == 0`` layers; PCF_NATransformer.py:181-225): same
+    arguments, parameter names and state-dict layout (``linear_pos``, ``qkv``, ``proj``). The ``(N, heads, T, T)`` logits,
+    their softmax and the dropout of the reference (:212-221) run as one fused attention call of the framework
+    (``scaled_dot_product_attention``) instead of four kernels with a ``T x T`` fp32 tensor per head in HBM."""
+
+    def __init__(self, dim, num_heads, groups=1, proj_bias=True, qkv_bias=True, qk_scale=None, attn_drop=0., proj_drop=0.):
+        super().__init__()
+        self.dim, self.num_heads, self.groups = dim, num_heads, groups
+        self.scale = qk_scale or (dim // num_heads) ** -0.5
+        self.linear_pos = nn.Conv1d(dim, dim, kernel_size=1, bias=False, groups=groups)
+        self.qkv = nn.Conv1d(dim, dim * 3, kernel_size=1, bias=qkv_bias, groups=groups)
+        self.attn_drop = nn.Dropout(attn_drop)
+        self.proj = nn.Conv1d(dim, dim, kernel_size=1, bias=proj_bias, groups=groups)
+        self.proj_drop = nn.Dropout(proj_drop)
+
+    forward = _global_forward
+
+
 def fuse_nattention(model, layout=None):
     """Rebind ``forward`` of every reference-style attention layer inside ``model`` to the fused path.
 
@@ -146,11 +187,14 @@ def fuse_nattention(model, layout=None):
     Returns the number of layers rebound."""
     n = 0
     for m in model.modules():
-        if isinstance(m, NAttention):
+        if isinstance(m, (NAttention, GlobalAttention)):
             continue
         if all(hasattr(m, a) for a in ("qkv", "proj", "relative_position_bias", "win_size", "left", "num_heads", "attn_drop",
                                        "proj_drop", "scale", "dilation")):
             m._na1d_layout = layout or ("channels_first" if isinstance(m.qkv, nn.Conv1d) else "channels_last")
             m.forward = types.MethodType(_fused_forward, m)
+            n += 1
+        elif all(hasattr(m, a) for a in ("linear_pos", "qkv", "proj", "num_heads", "groups", "attn_drop", "proj_drop", "scale")):
+            m.forward = types.MethodType(_global_forward, m)   # the reference's GlobalAttention
             n += 1
     return n

@@ -134,3 +134,23 @@ def test_backward_is_first_cuda_work_of_its_thread():
         "o.backward(torch.ones_like(o)); torch.cuda.synchronize(); print('ok', float(q.grad.float().abs().sum()) > 0)\n" % ROOT)
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and "ok True" in out.stdout, out.stderr[-2000:]
+
+
+@pytest.mark.parametrize("name", ["module_global_h4", "module_global_g2"])
+def test_global_attention_layer_on_gpu(name):
+    """The dense (win_size == 0) layer on the GPU in bf16 against the reference layer's fp32 output."""
+    from pcf_nat_b200 import GlobalAttention
+    from pcf_nat_b200.nattention import global_padding_mask
+    z = np.load(os.path.join(GOLD, name + ".npz"))
+    heads, groups = (4, 1) if name.endswith("h4") else (2, 2)
+    m = GlobalAttention(z["x"].shape[1], heads, groups=groups).eval()
+    m.load_state_dict({k[3:]: torch.from_numpy(z[k]) for k in z.files if k.startswith("sd_")})
+    m = m.cuda()
+    x = torch.from_numpy(z["x"]).cuda().requires_grad_(True)
+    mask = global_padding_mask(x.shape[-1], torch.from_numpy(z["padding"]).cuda()) if "padding" in z.files else None
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = m(x, torch.from_numpy(z["pos_emb"]).cuda(), mask)
+    y.float().backward(torch.from_numpy(z["gy"]).cuda())
+    ref, dref = torch.from_numpy(z["y"]), torch.from_numpy(z["dx"])
+    assert float((y.float().cpu() - ref).abs().max()) <= 3e-2 * max(1.0, float(ref.abs().max()))
+    assert float((x.grad.cpu() - dref).abs().max()) <= 3e-2 * max(1.0, float(dref.abs().max()))

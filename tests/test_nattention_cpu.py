@@ -99,3 +99,27 @@ def test_argument_errors():
         NAttention(8, 20, 2, 3)          # head_dim 10 is not a multiple of 8
     with pytest.raises(ValueError):
         NAttention(8, 16, 2, 3, layout="channels_last", groups=2)
+
+
+# ------------------------------------------------------------------ dense (global) attention layer
+@pytest.mark.parametrize("name", ["module_global_h4", "module_global_g2"])
+def test_global_attention_matches_reference_layer(name):
+    """The packaged dense layer against outputs of the reference's GlobalAttention (make_golden_global.py)."""
+    import numpy as np
+    from pcf_nat_b200 import GlobalAttention
+    from pcf_nat_b200.nattention import global_padding_mask
+    z = np.load(os.path.join(GOLD, name + ".npz"))
+    heads, groups = (4, 1) if name.endswith("h4") else (2, 2)
+    sd = {k[3:]: torch.from_numpy(z[k]) for k in z.files if k.startswith("sd_")}
+    m = GlobalAttention(z["x"].shape[1], heads, groups=groups).eval()
+    assert set(m.state_dict()) == set(sd)
+    m.load_state_dict(sd)
+    x = torch.from_numpy(z["x"]).requires_grad_(True)
+    mask = None
+    if "padding" in z.files:
+        mask = global_padding_mask(x.shape[-1], torch.from_numpy(z["padding"]))
+        assert torch.equal(mask, torch.from_numpy(z["mask"]))
+    y = m(x, torch.from_numpy(z["pos_emb"]), mask)
+    torch.testing.assert_close(y, torch.from_numpy(z["y"]), rtol=1e-4, atol=1e-5)
+    y.backward(torch.from_numpy(z["gy"]))
+    torch.testing.assert_close(x.grad, torch.from_numpy(z["dx"]), rtol=1e-4, atol=1e-5)
