@@ -47,7 +47,7 @@ DEFAULT = "cfg2_train_B128_H4_L200_D64_w7"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from an `ncu --set full` capture of this
 # command; a constant taken from that capture, not something this run measures (writes still resident in L2 when the
 # kernel ends are not in it)
-NCU_TRAFFIC = {"cfg2_train_B128_H4_L200_D64_w7": 52.92e6 + 4.00e6}
+NCU_TRAFFIC = {"cfg2_train_B128_H4_L200_D64_w7": 52.91e6 + 3.63e6}
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -609,6 +609,35 @@ def run_sweep(args):
         f.write("\n".join(lines) + "\n")
 
 
+def run_host_cost(args):
+    """Host time of one forward+backward pair of C-ABI calls at a small shape (32 sequences: the kernels take a few
+    microseconds, the host side dominates), in a tight loop on reused buffers. Run once as is and once with
+    NA1D_TENSOR_MAP_CACHE=0 in the environment to see what the tensor-map cache saves."""
+    from pcf_nat_b200 import _lib, ops
+    L = _lib.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    ob = OpBench(L, dev, 32, 4, 200, 64, 7, 1, torch.bfloat16, True)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    s = ob.sets[0]
+    for _ in range(50):
+        ob._fwd(s, st); ob._bwd(s, st)
+    torch.cuda.synchronize()
+    h0, m0 = ops.tensor_map_cache_stats()
+    n = 2000
+    t0 = time.perf_counter()
+    for _ in range(n):
+        ob._fwd(s, st); ob._bwd(s, st)
+    host_us = (time.perf_counter() - t0) / n * 1e6
+    torch.cuda.synchronize()
+    wall_us = (time.perf_counter() - t0) / n * 1e6
+    h1, m1 = ops.tensor_map_cache_stats()
+    ops.device_status()
+    print(json.dumps({"what": "host time of one na1d_fused_forward + na1d_fused_backward call pair, N=32 T=200 C=64 win=7",
+                      "tensor_map_cache": os.environ.get("NA1D_TENSOR_MAP_CACHE", "1") != "0", "host_us_per_pair": host_us,
+                      "wall_us_per_pair_incl_gpu": wall_us, "cache_hits": h1 - h0, "cache_misses": m1 - m0, "pairs": n}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -625,7 +654,10 @@ def main():
     ap.add_argument("--attention", default="fused", choices=["fused", "unfused"], help="model workloads: operator variant")
     ap.add_argument("--precision", default="autocast", choices=["bf16", "autocast"],
                     help="model workloads: bf16 weights/activations with fp32 master weights, or bf16 autocast over fp32 parameters")
+    ap.add_argument("--host-cost", action="store_true", help="host microseconds per forward+backward C-ABI call pair at a small shape")
     args = ap.parse_args()
+    if args.host_cost:
+        return run_host_cost(args)
     if args.sweep:
         return run_sweep(args)
     if args.workload in MODEL_WORKLOADS:

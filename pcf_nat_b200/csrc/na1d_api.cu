@@ -68,6 +68,8 @@ int na1d_qk_forward(float* attn, const void* q, const void* k, int64_t N, int64_
     NA1D_REQUIRE_ALIGNED(q); NA1D_REQUIRE_ALIGNED(k);
     na1d::Geometry g;
     if (int s = check_geometry(N, 1, T, C, win, left, dil, dtype, 1.f, g)) return s;
+    if (g_family_override.load() != 0 && na1d::tc_unfused_supports(g))
+        return cuda_status(na1d::tc_qk(attn, q, k, g, dtype, (cudaStream_t)stream));
     return cuda_status(na1d::simt_qk(attn, q, k, g, dtype, (cudaStream_t)stream));
 }
 int na1d_a_backward(float* attn_gd, const void* result_gd, const void* v, int64_t N, int64_t T, int64_t C, int64_t win,
@@ -80,6 +82,8 @@ int na1d_q_backward(void* q_gd, const float* attn_gd, const void* k, int64_t N, 
     NA1D_REQUIRE_ALIGNED(q_gd); NA1D_REQUIRE_ALIGNED(k);
     na1d::Geometry g;
     if (int s = check_geometry(N, 1, T, C, win, left, dil, dtype, 1.f, g)) return s;
+    if (g_family_override.load() != 0 && na1d::tc_unfused_supports(g))
+        return cuda_status(na1d::tc_band_x(q_gd, attn_gd, k, g, dtype, (cudaStream_t)stream));
     return cuda_status(na1d::simt_band_x(q_gd, attn_gd, k, g, dtype, (cudaStream_t)stream));
 }
 int na1d_av_forward(void* result, const float* attn, const void* v, int64_t N, int64_t T, int64_t C, int64_t win,
@@ -92,6 +96,8 @@ int na1d_k_backward(void* k_gd, const float* attn_gd, const void* q, int64_t N, 
     NA1D_REQUIRE_ALIGNED(k_gd); NA1D_REQUIRE_ALIGNED(q);
     na1d::Geometry g;
     if (int s = check_geometry(N, 1, T, C, win, left, dil, dtype, 1.f, g)) return s;
+    if (g_family_override.load() != 0 && na1d::tc_unfused_t_supports(g))
+        return cuda_status(na1d::tc_bandT_x(k_gd, attn_gd, q, g, dtype, (cudaStream_t)stream));
     return cuda_status(na1d::simt_bandT_x(k_gd, attn_gd, q, g, dtype, (cudaStream_t)stream));
 }
 int na1d_v_backward(void* v_gd, const float* attn, const void* result_gd, int64_t N, int64_t T, int64_t C, int64_t win,
@@ -159,8 +165,8 @@ int na1d_tensor_map_cache_stats(int64_t* hits, int64_t* misses) {
 
 int na1d_device_status(void) {
     // every word is read (and cleared) before anything is reported; an expired wait in any kernel wins over a failed read
-    const int words[4] = {na1d::tc_read_status(), na1d::tc_bwd_read_status(), na1d::tc_seg_read_status(),
-                          na1d::tc_bwd_seg_read_status()};
+    const int words[6] = {na1d::tc_read_status(), na1d::tc_bwd_read_status(), na1d::tc_seg_read_status(),
+                          na1d::tc_bwd_seg_read_status(), na1d::tc_unfused_read_status(), na1d::tc_unfused_t_read_status()};
     int v = 0, w = 0;
     for (int x : words) { if (x > 0) v = x; if (x < 0) w = x; }
     if (v > 0) return NA1D_ERR_DEVICE_TIMEOUT;

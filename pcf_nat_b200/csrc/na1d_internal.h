@@ -40,6 +40,15 @@ cudaError_t tc_fused_bwd_seg(void* dq, void* dk, void* dv, float* d_rpb, const v
                              size_t scratch_floats, const Strides& sdq, const Strides& sdk, const Strides& sdv, const Strides& sdo,
                              const Strides& sq, const Strides& sk, const Strides& sv, const Geometry& gm, int dtype, cudaStream_t st);
 void tensor_map_cache_stats(long long* hits, long long* misses);
+
+// ---- the unfused pair on the tcgen05 kernels (na1d_tc_unfused.cu): flat tiling, same shape limits as the fused forward
+bool tc_unfused_supports(const Geometry& gm);
+cudaError_t tc_qk(float* attn, const void* a, const void* b, const Geometry& gm, int dtype, cudaStream_t st);
+cudaError_t tc_band_x(void* out, const float* band, const void* x, const Geometry& gm, int dtype, cudaStream_t st);
+int tc_unfused_read_status();
+bool tc_unfused_t_supports(const Geometry& gm);
+cudaError_t tc_bandT_x(void* out, const float* band, const void* x, const Geometry& gm, int dtype, cudaStream_t st);
+int tc_unfused_t_read_status();
 // shape limits of the tcgen05 backward, including whether its shared memory fits with a bias table (has_bias) and the
 // bias-gradient accumulators (wants_bias_grad)
 bool tc_bwd_supports(const Geometry& gm, bool has_bias = false, bool wants_bias_grad = false);

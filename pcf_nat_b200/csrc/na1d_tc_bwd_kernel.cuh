@@ -167,7 +167,15 @@ template <int NSETS> struct BwdMaps {
     CUtensorMap q[NSETS], d_o[NSETS], k[NSETS], v[NSETS], dq[NSETS], dk[NSETS], dv[NSETS];
 };
 
-template <typename E, int C, int WB, bool OWN_OUT, bool SEG>
+// MODE selects what the kernel computes with the same tiles, rings and operand matrices:
+//   kBwdFused : dq, dk, dv (and d_rpb) of the fused operator
+//   kBandT    : out[j] = sum over the (t, kk) whose neighbour is j of band[t, kk] x[t] -- the unfused dK = dS^T.Q and
+//               dV = P^T.dO (na1d_tensorcore/bf16_ana1d_kernel.cu:394-492): the fp32 band comes from global memory through
+//               `lse`'s slot, x through the dO maps, out through the dV maps; only the dV chain of MMAs runs. The band is
+//               rounded to 16 bits before the product, as the reference does (:409-415).
+constexpr int kBwdFused = 0, kBandT = 1;
+
+template <typename E, int C, int WB, bool OWN_OUT, bool SEG, int MODE = kBwdFused>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict__ d_rpb, int drpb_direct,
               const float* __restrict__ lse,
@@ -214,10 +222,12 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
             if constexpr (SEG) ptx::tma_load_5d(dst, map + set, &misc->full[s][buf], 0, row0, rc, pcur.h, pcur.b);
             else ptx::tma_load_3d(dst, map, &misc->full[s][buf], 0, row0, 0);
         };
-        refill(kV, st + L.stage_v, tm.v, KT, g0 - left);
-        refill(kK, st + L.stage_k, tm.k, KT, g0 - left);
+        if constexpr (MODE == kBwdFused) {
+            refill(kV, st + L.stage_v, tm.v, KT, g0 - left);
+            refill(kK, st + L.stage_k, tm.k, KT, g0 - left);
+        }
         refill(kDO, st + L.stage_do, tm.d_o, kTileM, g0);
-        refill(kQ, st + L.stage_q, tm.q, kTileM, g0);
+        if constexpr (MODE == kBwdFused) refill(kQ, st + L.stage_q, tm.q, kTileM, g0);
         if constexpr (SEG) pcur.advance();
         return ok;
     };
@@ -230,7 +240,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
         ptx::mbar_init(&misc->s_ready, 2);   // S chain and dP chain
         ptx::mbar_init(&misc->s_free, 128);
         ptx::mbar_init(&misc->p_ready, 128);
-        ptx::mbar_init(&misc->o_ready, 3);   // dQ, dV, dK chains
+        ptx::mbar_init(&misc->o_ready, MODE == kBwdFused ? 3 : 1);   // dQ, dV, dK chains (only dV in the band-transpose mode)
         for (int i = 0; i < 3; ++i) ptx::mbar_init(&misc->o_free[i], 128);
         ptx::mbar_init(&misc->acc_done, 128);
         misc->abort = 0;
@@ -312,8 +322,10 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
             // iteration j-1 and the operands of tile j in shared memory) and batch 2 of iteration i (needs the compute warps'
             // operand matrices and the drained accumulator). Whichever is ready first is issued first, so a late TMA load never
             // holds back MMAs whose inputs are already there. Batch 1 runs at most one iteration ahead of batch 2.
-            const int n_it = blockIdx.x < total_tiles ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-            int next_b1 = role < 2 ? 0 : n_it, it = 0;
+            // band-transpose mode: no batch 1 at all, and only role 1 (the dV chain) has a batch 2
+            const int n_it = (blockIdx.x < total_tiles && (MODE == kBwdFused || role == 1))
+                                 ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+            int next_b1 = (role < 2 && MODE == kBwdFused) ? 0 : n_it, it = 0;
             uint32_t polls = 0;
             bool ok = true;
             while (it < n_it) {
@@ -324,7 +336,8 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     polls = 0;
                     continue;
                 }
-                if (!(ptx::mbar_try_wait(&misc->p_ready, it & 1) && ptx::mbar_try_wait(&misc->o_free[role], (it & 1) ^ 1))) {
+                if (!(ptx::mbar_try_wait(&misc->p_ready, it & 1) && ptx::mbar_try_wait(&misc->o_free[role], (it & 1) ^ 1) &&
+                      (MODE == kBwdFused || ptx::mbar_try_wait(&misc->full[it % NS][kDO], (it / NS) & 1)))) {
                     if (++polls > (1u << 22) || *abort_flag) { ok = false; break; }
                     continue;
                 }
@@ -405,8 +418,8 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     dst[b][hh] = (tile_ < total_tiles && gq >= 0 && gq < rows_) ? __ldg(base_ + (size_t)gq * mul_) : 0.f;
                 }
         };
-        float lse_next[2][2];
-        load_lse(blockIdx.x, lse_next);
+        float lse_next[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+        if constexpr (MODE == kBwdFused) load_lse(blockIdx.x, lse_next);
         int prev_hr = -1;
         const int batch = gm.N / gm.H;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
@@ -419,7 +432,55 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 const int vl = valid_len ? min(T, __ldg(valid_len + scur.b)) : T;
                 vl_seq = vl > scur.r ? (vl - scur.r + sg.d - 1) / sg.d : 0;
             }
-            if constexpr (WB == 33) {
+            if constexpr (MODE == kBandT) {
+                // the band of the tile's 128 query rows comes from global memory (fp32, `lse` points at it): slot (g, hh, e) of
+                // row (b, hh) is band[row, kk]; 0 outside the band, for rows outside the tensor and for keys outside the row's
+                // own sequence (they belong to another sequence's output rows)
+                int jb[2][2];
+                bool live4[2][2];
+                {
+                    int tq, hq, bq;
+                    cur.row_at(warp * 32 + fr - right, inv_T, inv_H, tq, hq, bq);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int gq = g0 + warp * 32 + fr + 8 * k;
+                        live4[k >> 1][k & 1] = gq >= 0 && gq < rows_total;
+                        jb[k >> 1][k & 1] = tq - left + fa;
+                        tc::row_step8(T, gm.H, tq, hq, bq);
+                    }
+                }
+                uint32_t pk_p[2][2 * NG];
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                    for (int g = 0; g < NG; ++g)
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {
+                            const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
+                            const float* src = lse + (size_t)min(max(gq, 0), rows_total - 1) * gm.win;
+                            float p[2];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int kc = 8 * (g - hh) + e;
+                                const bool on = ((band_bits >> (2 * (g - hh + 1) + e)) & 1u) && live4[b][hh] &&
+                                                (unsigned)(jb[b][hh] + kc) < (unsigned)T;
+                                p[e] = on ? __ldg(src + ((kc + fa) >> dshift)) : 0.f;
+                            }
+                            pk_p[b][2 * g + hh] = Cvt<E>::pack2(p[0], p[1]);
+                        }
+                // the previous tile's MMAs must have finished reading the operand matrix before it is rewritten
+                if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    const uint32_t blk = (uint32_t)(4 * warp + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * warp + 2 * b) * 128u;
+                    tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p[b], lane);
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(&misc->p_ready);
+                cur.advance();
+                continue;
+            } else if constexpr (WB == 33) {
                 // Widest window bucket: the two 16-row blocks of the warp are processed one after the other in a ROLLED loop.
                 // 48 fragment values of S and of dP per block and thread: holding both blocks at once spilled registers, and
                 // the unrolled code of both did not fit the instruction cache (measured: 2-3x more cycles per tile).
@@ -660,7 +721,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 }
             }
             if constexpr (SEG) scur.advance(); else cur.advance();
-            load_lse(tile + gridDim.x, lse_next);
+            if constexpr (MODE == kBwdFused) load_lse(tile + gridDim.x, lse_next);
         }
         if (d_rpb && it > 0 && ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) && !*abort_flag)  // the last tile's share
             bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask, dshift,
@@ -720,6 +781,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 uint4 pk[3][CH];
 #pragma unroll
                 for (int which = 0; which < 3; ++which) {  // 0: dQ, 1: dV, 2: dK = the MMA roles
+                    if (MODE == kBandT && which != 1) continue;
                     const uint32_t col = which == 0 ? kColDQ : which == 1 ? kColDV : kColDK;
                     float acc[C];
 #pragma unroll
@@ -732,7 +794,8 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 }
 #pragma unroll
                 for (int which = 0; which < 3; ++which) {
-                    if (which > 0) asm volatile("bar.sync 2, 128;" ::: "memory");  // previous store has read the buffer
+                    if (MODE == kBandT && which != 1) continue;
+                    if (which > 0 && MODE == kBwdFused) asm volatile("bar.sync 2, 128;" ::: "memory");  // previous store has read the buffer
                     const int ms = r - (which == 0 ? right : win - 1);
                     if (ms >= 0 && ms < stride) {
                         const int swz = (C == 64) ? (ms & 7) : (C == 32) ? ((ms >> 1) & 3) : ((ms >> 2) & 1);
@@ -803,7 +866,7 @@ __global__ void bias_grad_reduce_kernel(float* __restrict__ d_rpb, const float* 
     if (lane == 0) d_rpb[i] += acc;
 }
 
-template <typename E, int C, int WB, bool SEG>
+template <typename E, int C, int WB, bool SEG, int MODE = kBwdFused>
 cudaError_t launch_bwd(const BwdMaps<SEG ? 2 : 1>& maps, float* d_rpb, float* scratch, size_t scratch_floats,
                        const float* lse, const float* rpb, const int* valid_len, const Geometry& gm, const SegGeom& sg, int stride, int KT,
                        int total, int sm_count, bool pdl, cudaStream_t st) {
@@ -814,7 +877,11 @@ cudaError_t launch_bwd(const BwdMaps<SEG ? 2 : 1>& maps, float* d_rpb, float* sc
     if constexpr (C != 64) {
         if (!L.own_out) return cudaErrorInvalidValue;
     }
-    auto kern = (C == 64 && !L.own_out) ? tc_bwd_kernel<E, C, WB, C != 64, SEG> : tc_bwd_kernel<E, C, WB, true, SEG>;
+    if constexpr (MODE != kBwdFused) {
+        if (!L.own_out) return cudaErrorInvalidValue;   // the band-transpose mode exists only with the dedicated staging buffer
+    }
+    auto kern = (MODE == kBwdFused && C == 64 && !L.own_out) ? tc_bwd_kernel<E, C, WB, C != 64 || MODE != kBwdFused, SEG, MODE>
+                                                             : tc_bwd_kernel<E, C, WB, true, SEG, MODE>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     const int grid = total < sm_count ? total : sm_count;
@@ -839,14 +906,14 @@ cudaError_t launch_bwd(const BwdMaps<SEG ? 2 : 1>& maps, float* d_rpb, float* sc
 }
 
 // Picks the instantiation for (channels, window bucket) of element type E; `wb` is the window the band fragments must hold.
-template <typename E, bool SEG>
+template <typename E, bool SEG, int MODE = kBwdFused>
 cudaError_t dispatch_bwd(const BwdMaps<SEG ? 2 : 1>& maps, float* d_rpb, float* scratch, size_t scratch_floats, const float* lse,
                          const float* rpb, const int* valid_len, const Geometry& gm, const SegGeom& sg, int stride, int KT, int total,
                          int wb, cudaStream_t st) {
     const int sms = device_sm_count();
     const bool pdl = pdl_mode() == 1 || pdl_mode() == 3;
 #define NA1D_TC_BWD(C, WB) \
-    return launch_bwd<E, C, WB, SEG>(maps, d_rpb, scratch, scratch_floats, lse, rpb, valid_len, gm, sg, stride, KT, total, sms, pdl, st)
+    return launch_bwd<E, C, WB, SEG, MODE>(maps, d_rpb, scratch, scratch_floats, lse, rpb, valid_len, gm, sg, stride, KT, total, sms, pdl, st)
 #define NA1D_TC_BWD_W(C)                       \
     if (wb <= 9) { NA1D_TC_BWD(C, 9); }        \
     else if (wb <= 17) { NA1D_TC_BWD(C, 17); } \

@@ -20,7 +20,7 @@ cudaError_t tc_fused_fwd(void* o, float* lse, const void* q, const void* k, cons
         !make_row_tile_map(&maps.v[0], v, dtype, 1, rows, gm.C, KT) || !make_row_tile_map(&maps.o[0], o, dtype, 1, rows, gm.C, tc::kTileM))
         return cudaErrorInvalidValue;
     const int total = (rows + tc::kTileM - 1) / tc::kTileM;
-    return dispatch_fwd<false>(maps, lse, rpb, valid_len, gm, SegGeom{1, 1, gm.T, 0, tc::kTileM}, KT, total, weff, dtype, st);
+    return dispatch_fwd<false>(maps, lse, nullptr, rpb, valid_len, gm, SegGeom{1, 1, gm.T, 0, tc::kTileM}, KT, total, weff, dtype, st);
 }
 
 int tc_read_status() { return read_status_word(); }

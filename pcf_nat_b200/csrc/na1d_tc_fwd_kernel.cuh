@@ -88,10 +88,20 @@ template <int NSETS> struct FwdMaps {
     CUtensorMap q[NSETS], k[NSETS], v[NSETS], o[NSETS];
 };
 
-template <typename E, int C, int WB, bool SEG>
+// MODE selects what the kernel computes with the same tiles, rings and tensor-memory layout:
+//   kFused  : o = softmax(scale q.k^T + rpb + mask) . v                        (reads q, k, v; writes o, lse)
+//   kBandOut: band[t, kk] = q[t] . k[j(t, kk)], zero-padded keys                 (reads q, k; writes the fp32 band)
+//             -- the unfused QK forward and dA = dO.V^T (na1d_tensorcore/bf16_ana1d_kernel.cu:42-282)
+//   kBandIn : o[t] = sum_kk band[t, kk] v[j(t, kk)], zero-padded values          (reads the fp32 band and v; writes o)
+//             -- the unfused AV forward and dQ = dS.K (na1d_tensorcore/bf16_ana1d_kernel.cu:285-391); the band is rounded
+//             to 16 bits before the product, as the reference does (:301-306)
+constexpr int kFused = 0, kBandOut = 1, kBandIn = 2;
+
+template <typename E, int C, int WB, bool SEG, int MODE = kFused>
 __global__ void __launch_bounds__(kThreads, 2)
-tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict__ lse,
+tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict__ lse, float* __restrict__ band,
               const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, SegGeom sg, int KT, int total_tiles) {
+    static_assert(MODE == kFused || !SEG, "the unfused modes run on the flat tiling");
     constexpr int NG = tc::band_groups(WB);
     constexpr int kRowBytes = C * 2;
     extern __shared__ uint8_t smem_raw[];
@@ -106,22 +116,24 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
     // segmented tiling: the dilation lives in the addressing, the window is the reference's own
     const int dil = SEG ? 1 : gm.dil, dmask = dil - 1, dshift = 31 - __clz(dil);
     const int win = tc::eff_window(gm.win, dil), left = gm.left * dil, T = gm.T;
-    const int stage_tx = 2 * KT * kRowBytes;
+    const int stage_tx = (MODE == kFused ? 2 : 1) * KT * kRowBytes;   // K and V, or only the one the mode reads
     tc::SegCursor pcur = {};  // position of the producer thread's next tile (segmented tiling)
 
     // Loads of tile `tile` (iteration `it` of this CTA): Q into the single Q buffer, K and V into ring stage it % 2.
     auto produce = [&](int tile, int it) -> bool {
         const int s = it & 1, k = it >> 1;
         const int g0 = tile * kTileM;
-        // Q: free once the S MMAs of the previous tile have retired
-        if (!ptx::mbar_wait_relaxed(&misc->empty_q, (it & 1) ^ 1) || *(volatile int*)&misc->abort) return false;
-        // At the start every CTA of the grid loads at once and DRAM is the limit: let the first tile land before the
-        // second is requested, so that all CTAs start computing (and storing) early instead of at the end of the burst.
-        if (it == 1 && !ptx::mbar_wait_relaxed(&misc->full[0], 0)) return false;
-        ptx::mbar_expect_tx(&misc->full_q, (uint32_t)(kTileM * kRowBytes));
         const int set = SEG && pcur.r >= sg.ra ? 1 : 0, rc = pcur.r - (set ? sg.ra : 0), u0 = pcur.i * kTileM;
-        if constexpr (SEG) ptx::tma_load_5d(smem + L.q, &tm.q[set], &misc->full_q, 0, u0, rc, pcur.h, pcur.b);
-        else ptx::tma_load_3d(smem + L.q, &tm.q[0], &misc->full_q, 0, g0, 0);
+        if constexpr (MODE != kBandIn) {
+            // Q: free once the S MMAs of the previous tile have retired
+            if (!ptx::mbar_wait_relaxed(&misc->empty_q, (it & 1) ^ 1) || *(volatile int*)&misc->abort) return false;
+            // At the start every CTA of the grid loads at once and DRAM is the limit: let the first tile land before the
+            // second is requested, so that all CTAs start computing (and storing) early instead of at the end of the burst.
+            if (it == 1 && !ptx::mbar_wait_relaxed(&misc->full[0], 0)) return false;
+            ptx::mbar_expect_tx(&misc->full_q, (uint32_t)(kTileM * kRowBytes));
+            if constexpr (SEG) ptx::tma_load_5d(smem + L.q, &tm.q[set], &misc->full_q, 0, u0, rc, pcur.h, pcur.b);
+            else ptx::tma_load_3d(smem + L.q, &tm.q[0], &misc->full_q, 0, g0, 0);
+        }
         // K, V: free once the tile two back has stored its output (staged in its V buffer)
         if (!ptx::mbar_wait_relaxed(&misc->empty[s], (k & 1) ^ 1) || *(volatile int*)&misc->abort) return false;
         uint8_t* st = smem + L.ring + s * L.stage_bytes;
@@ -131,8 +143,8 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
             ptx::tma_load_5d(st + L.stage_v, &tm.v[set], &misc->full[s], 0, u0 - left, rc, pcur.h, pcur.b);
             pcur.advance();
         } else {
-            ptx::tma_load_3d(st + L.stage_k, &tm.k[0], &misc->full[s], 0, g0 - left, 0);
-            ptx::tma_load_3d(st + L.stage_v, &tm.v[0], &misc->full[s], 0, g0 - left, 0);
+            if constexpr (MODE != kBandIn) ptx::tma_load_3d(st + L.stage_k, &tm.k[0], &misc->full[s], 0, g0 - left, 0);
+            if constexpr (MODE != kBandOut) ptx::tma_load_3d(st + L.stage_v, &tm.v[0], &misc->full[s], 0, g0 - left, 0);
         }
         return true;
     };
@@ -182,7 +194,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
             bool ok = first_ok;
             for (int tile = blockIdx.x + gridDim.x; ok && tile < total_tiles; tile += gridDim.x, ++it) ok = produce(tile, it);
             if (!ok) { atomicExch(&g_tc_status, 1); *abort_flag = 1; }
-        } else if (lane == 1) {
+        } else if (lane == 1 && MODE != kBandOut) {
             // ---------------------------------------------------------- output store thread: waits until the softmax warps
             // have staged a tile's O, issues the TMA store, and frees the stage once the store has read shared memory
             int it = 0;
@@ -215,20 +227,26 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 const int s = it & 1, k = it >> 1;
                 const uint32_t st = ptx::smem_u32(smem + L.ring + s * L.stage_bytes);
                 // S overwrites the columns that held the previous tile's P and odd-step accumulator: both must be drained
-                if (!ptx::mbar_wait(&misc->full[s], k & 1) || !ptx::mbar_wait(&misc->full_q, it & 1) ||
+                if (!ptx::mbar_wait(&misc->full[s], k & 1) || (MODE != kBandIn && !ptx::mbar_wait(&misc->full_q, it & 1)) ||
                     !ptx::mbar_wait(&misc->o_free, (it & 1) ^ 1) || *abort_flag) {
                     atomicExch(&g_tc_status, 2); *abort_flag = 1; break;
                 }
                 ptx::tc_fence_after_sync();
-                {
+                if constexpr (MODE != kBandIn) {
                     const uint64_t a0 = ptx::smem_desc(ptx::smem_u32(smem + L.q), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
                     const uint64_t b0 = ptx::smem_desc(st + L.stage_k, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
 #pragma unroll
                     for (int ks = 0; ks < C / 16; ++ks)
                         ptx::mma_ss(tmem, tc::desc_advance(a0, ks * 32), tc::desc_advance(b0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
                 }
-                ptx::mma_commit(&misc->empty_q);  // Q is read by nothing else
-                ptx::mma_commit(&misc->s_ready);
+                if constexpr (MODE != kBandIn) {
+                    ptx::mma_commit(&misc->empty_q);  // Q is read by nothing else
+                    ptx::mma_commit(&misc->s_ready);
+                }
+                if constexpr (MODE == kBandOut) {
+                    ptx::mma_commit(&misc->empty[s]);  // nothing else reads the K stage in this mode
+                    continue;
+                }
                 if (!ptx::mbar_wait(&misc->p_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 3); *abort_flag = 1; break; }
                 ptx::tc_fence_after_sync();
                 {
@@ -242,7 +260,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
         }
     } else if (warp == 6) {
         // ------------------------------------------------------------ MMA issuer B: the odd key steps of P.V
-        if (lane == 0) {
+        if (lane == 0 && MODE != kBandOut) {
             const uint32_t idesc_o = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);
             const int nks = KT / 16;
             int it = 0;
@@ -335,80 +353,129 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
             }
             // masks are needed only when one of the warp's rows touches a sequence end or a padded region
             need_mask = __any_sync(0xffffffffu, need_mask);
-            if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 4); *abort_flag = 1; break; }
-            ptx::tc_fence_after_sync();
-
             float s[2][4 * NG];
+            if constexpr (MODE != kBandIn) {
+                if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 4); *abort_flag = 1; break; }
+                ptx::tc_fence_after_sync();
 #pragma unroll
-            for (int b = 0; b < 2; ++b)
-                tc::ld_frag<NG>(lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b), s[b]);
-            ptx::tmem_ld_wait();
-            // logits on the band (log2 domain), everything else -inf; two straight-line copies, with and without masks
-            float mx[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}};
-            auto logits = [&](auto masked_tag) {
-                constexpr bool kMasked = decltype(masked_tag)::value;
+                for (int b = 0; b < 2; ++b)
+                    tc::ld_frag<NG>(lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b), s[b]);
+                ptx::tmem_ld_wait();
+            }
+            if constexpr (MODE == kBandOut) {
+                // the dot products of the band go to the fp32 band tensor as they are (a key outside the query's own sequence
+                // is the reference's zero-padded row: 0); the S columns are free for the next tile at once
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(&misc->o_free);
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
+                        if (gq >= rows_total) continue;
+                        float* dst = band + (size_t)gq * gm.win;
+#pragma unroll
+                        for (int g = 0; g < NG; ++g)
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int kc = 8 * (g - hh) + e;
+                                if (!((band_bits >> (2 * (g - hh + 1) + e)) & 1u)) continue;
+                                const unsigned j = (unsigned)(jb[b][hh] + kc);
+                                dst[(kc + fa) >> dshift] = j < (unsigned)Trow ? s[b][4 * g + 2 * hh + e] : 0.f;
+                            }
+                    }
+                if constexpr (SEG) scur.advance(); else cur.advance();
+                continue;
+            }
+            if constexpr (MODE == kBandIn) {
+                // the probabilities come from the fp32 band tensor instead of a softmax: slot (g, hh, e) of row (b, hh) is
+                // band[row, kk]; 0 outside the band, for rows past the tensor and for keys outside the row's own sequence
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
+                        const float* src = band + (size_t)min(gq, rows_total - 1) * gm.win;
+#pragma unroll
+                        for (int g = 0; g < NG; ++g)
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int kc = 8 * (g - hh) + e;
+                                const bool on = ((band_bits >> (2 * (g - hh + 1) + e)) & 1u) && gq < rows_total &&
+                                                (unsigned)(jb[b][hh] + kc) < (unsigned)Trow;
+                                s[b][4 * g + 2 * hh + e] = on ? __ldg(src + ((kc + fa) >> dshift)) : 0.f;
+                            }
+                    }
+            }
+            float sum[2][2] = {{1.f, 1.f}, {1.f, 1.f}};   // factor applied to s[] when it is packed: 1 / row sum (fused), 1 (band input)
+            if constexpr (MODE == kFused) {
+                sum[0][0] = sum[0][1] = sum[1][0] = sum[1][1] = 0.f;
+                // logits on the band (log2 domain), everything else -inf; two straight-line copies, with and without masks
+                float mx[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}};
+                auto logits = [&](auto masked_tag) {
+                    constexpr bool kMasked = decltype(masked_tag)::value;
+#pragma unroll
+                    for (int b = 0; b < 2; ++b)
+#pragma unroll
+                        for (int g = 0; g < NG; ++g)
+#pragma unroll
+                            for (int hh = 0; hh < 2; ++hh) {
+                                float2 bias2 = make_float2(0.f, 0.f);  // biases of the thread's two adjacent columns of this group
+                                if (rpb) bias2 = *reinterpret_cast<const float2*>(brow[b][hh] + 8 * (g - hh));
+#pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const int idx = 4 * g + 2 * hh + e;
+                                    const int kc = 8 * (g - hh) + e;  // window offset minus the lane constant fa
+                                    const bool inband = (band_bits >> (2 * (g - hh + 1) + e)) & 1u;
+                                    float bias = e ? bias2.y : bias2.x;
+                                    float dot = s[b][idx];
+                                    if constexpr (kMasked) {
+                                        const unsigned j = (unsigned)(jb[b][hh] + kc);
+                                        if (j >= (unsigned)Trow) dot = 0.f;  // key outside the query's own sequence: the reference's zero row
+                                        if (j >= (unsigned)vle[b][hh]) bias += mask2;
+                                    }
+                                    const float x = inband ? fmaf(dot, sc, bias) : -INFINITY;
+                                    s[b][idx] = x;
+                                    mx[b][hh] = fmaxf(mx[b][hh], x);
+                                }
+                            }
+                };
+                if (need_mask) logits(std::true_type{}); else logits(std::false_type{});
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) mx[b][hh] = tc::quad_max(mx[b][hh]);
 #pragma unroll
                 for (int b = 0; b < 2; ++b)
 #pragma unroll
                     for (int g = 0; g < NG; ++g)
 #pragma unroll
-                        for (int hh = 0; hh < 2; ++hh) {
-                            float2 bias2 = make_float2(0.f, 0.f);  // biases of the thread's two adjacent columns of this group
-                            if (rpb) bias2 = *reinterpret_cast<const float2*>(brow[b][hh] + 8 * (g - hh));
+                        for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int idx = 4 * g + 2 * hh + e;
-                                const int kc = 8 * (g - hh) + e;  // window offset minus the lane constant fa
-                                const bool inband = (band_bits >> (2 * (g - hh + 1) + e)) & 1u;
-                                float bias = e ? bias2.y : bias2.x;
-                                float dot = s[b][idx];
-                                if constexpr (kMasked) {
-                                    const unsigned j = (unsigned)(jb[b][hh] + kc);
-                                    if (j >= (unsigned)Trow) dot = 0.f;  // key outside the query's own sequence: the reference's zero row
-                                    if (j >= (unsigned)vle[b][hh]) bias += mask2;
-                                }
-                                const float x = inband ? fmaf(dot, sc, bias) : -INFINITY;
-                                s[b][idx] = x;
-                                mx[b][hh] = fmaxf(mx[b][hh], x);
+                                const float p = tc::fast_exp2(s[b][idx] - mx[b][hh]);  // exp2(-inf) = 0 outside the band
+                                s[b][idx] = p;
+                                sum[b][hh] += p;
+                            }
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        sum[b][hh] = tc::quad_sum(sum[b][hh]);
+                        if (lse && (lane & 3) == 0) {
+                            const float val = (mx[b][hh] + tc::fast_log2(sum[b][hh])) * kLn2;
+                            if constexpr (SEG) {
+                                const int tq = scur.i * kTileM + warp * 32 + 16 * b + 8 * hh + fr;
+                                if (tq < Trow) lse[(size_t)(scur.b * gm.H + scur.h) * T + (size_t)tq * sg.d + scur.r] = val;
+                            } else {
+                                const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
+                                if (gq < rows_total) lse[gq] = val;
                             }
                         }
-            };
-            if (need_mask) logits(std::true_type{}); else logits(std::false_type{});
-            float sum[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) mx[b][hh] = tc::quad_max(mx[b][hh]);
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-                for (int g = 0; g < NG; ++g)
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int idx = 4 * g + 2 * hh + e;
-                            const float p = tc::fast_exp2(s[b][idx] - mx[b][hh]);  // exp2(-inf) = 0 outside the band
-                            s[b][idx] = p;
-                            sum[b][hh] += p;
-                        }
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    sum[b][hh] = tc::quad_sum(sum[b][hh]);
-                    if (lse && (lane & 3) == 0) {
-                        const float val = (mx[b][hh] + tc::fast_log2(sum[b][hh])) * kLn2;
-                        if constexpr (SEG) {
-                            const int tq = scur.i * kTileM + warp * 32 + 16 * b + 8 * hh + fr;
-                            if (tq < Trow) lse[(size_t)(scur.b * gm.H + scur.h) * T + (size_t)tq * sg.d + scur.r] = val;
-                        } else {
-                            const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
-                            if (gq < rows_total) lse[gq] = val;
-                        }
+                        sum[b][hh] = tc::fast_rcp(sum[b][hh]);
                     }
-                    sum[b][hh] = tc::fast_rcp(sum[b][hh]);
-                }
+            }
             // P over the S columns. Per 16-lane block the band occupies NGP 8-key groups starting at the block's own
             // first row; every other 16-key chunk of the row range is zeroed. The two sets are disjoint, so one wait.
             {
@@ -484,11 +551,11 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
     }
 }
 
-template <typename E, int C, int WB, bool SEG>
-cudaError_t launch_fwd(const FwdMaps<SEG ? 2 : 1>& maps, float* lse, const float* rpb, const int* valid_len, const Geometry& gm,
-                       const SegGeom& sg, int KT, int total, int sm_count, bool pdl, cudaStream_t st) {
+template <typename E, int C, int WB, bool SEG, int MODE>
+cudaError_t launch_fwd(const FwdMaps<SEG ? 2 : 1>& maps, float* lse, float* band, const float* rpb, const int* valid_len,
+                       const Geometry& gm, const SegGeom& sg, int KT, int total, int sm_count, bool pdl, cudaStream_t st) {
     const int smem = fwd_layout(C, KT, rpb ? gm.H : 0).total;
-    auto kern = tc_fwd_kernel<E, C, WB, SEG>;
+    auto kern = tc_fwd_kernel<E, C, WB, SEG, MODE>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     const int per_sm = (2 * (smem + 1024) <= 227 * 1024) ? 2 : 1;
@@ -504,16 +571,16 @@ cudaError_t launch_fwd(const FwdMaps<SEG ? 2 : 1>& maps, float* lse, const float
     attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, maps, lse, rpb, valid_len, gm, sg, KT, total);
+    return cudaLaunchKernelEx(&cfg, kern, maps, lse, band, rpb, valid_len, gm, sg, KT, total);
 }
 
 // Picks the instantiation for (element type, channels, window bucket); `wb` is the window the band fragments must hold.
-template <bool SEG>
-cudaError_t dispatch_fwd(const FwdMaps<SEG ? 2 : 1>& maps, float* lse, const float* rpb, const int* valid_len, const Geometry& gm,
-                         const SegGeom& sg, int KT, int total, int wb, int dtype, cudaStream_t st) {
+template <bool SEG, int MODE = kFused>
+cudaError_t dispatch_fwd(const FwdMaps<SEG ? 2 : 1>& maps, float* lse, float* band, const float* rpb, const int* valid_len,
+                         const Geometry& gm, const SegGeom& sg, int KT, int total, int wb, int dtype, cudaStream_t st) {
     const int sms = device_sm_count();
     const bool pdl = pdl_mode() == 1 || pdl_mode() == 2;
-#define NA1D_TC_FWD(E, C, WB) return launch_fwd<E, C, WB, SEG>(maps, lse, rpb, valid_len, gm, sg, KT, total, sms, pdl, st)
+#define NA1D_TC_FWD(E, C, WB) return launch_fwd<E, C, WB, SEG, MODE>(maps, lse, band, rpb, valid_len, gm, sg, KT, total, sms, pdl, st)
 #define NA1D_TC_FWD_W(E, C)                        \
     if (wb <= 9) { NA1D_TC_FWD(E, C, 9); }         \
     else if (wb <= 17) { NA1D_TC_FWD(E, C, 17); }  \

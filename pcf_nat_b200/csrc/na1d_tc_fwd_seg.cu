@@ -36,7 +36,7 @@ cudaError_t tc_fused_fwd_seg(void* o, float* lse, const void* q, const void* k, 
         !make_seg_tile_maps(maps.o, o, dtype, batch, gm.H, gm.T, gm.C, so, sg, tc::kTileM))
         return cudaErrorInvalidValue;
     const int total = gm.N * sg.d * sg.tps;
-    return dispatch_fwd<true>(maps, lse, rpb, valid_len, gm, sg, KT, total, gm.win, dtype, st);
+    return dispatch_fwd<true>(maps, lse, nullptr, rpb, valid_len, gm, sg, KT, total, gm.win, dtype, st);
 }
 
 int tc_seg_read_status() { return read_status_word(); }

@@ -57,6 +57,8 @@ constexpr size_t kMaxCachedMaps = 4096;
 
 bool encode_cached(CUtensorMap* out, const void* base, int dtype, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
                    const cuuint32_t* box, CUtensorMapSwizzle sw) {
+    // NA1D_TENSOR_MAP_CACHE=0 (read once) turns the memoisation off, for measuring what it saves
+    static const bool enabled = []() { const char* e = getenv("NA1D_TENSOR_MAP_CACHE"); return !(e && e[0] == '0'); }();
     MapKey key;
     memset(&key, 0, sizeof(key));
     int dev = 0;
@@ -66,7 +68,7 @@ bool encode_cached(CUtensorMap* out, const void* base, int dtype, int rank, cons
     for (int i = 0; i < rank; ++i) key.v[2 + i] = dims[i];
     for (int i = 0; i + 1 < rank; ++i) key.v[7 + i] = strides[i];
     for (int i = 0; i < rank; ++i) key.v[11 + i] = box[i];
-    {
+    if (enabled) {
         std::lock_guard<std::mutex> lock(g_map_mutex);
         auto it = map_cache().find(key);
         if (it != map_cache().end()) {
@@ -85,6 +87,7 @@ bool encode_cached(CUtensorMap* out, const void* base, int dtype, int rank, cons
         return false;
     g_map_misses.fetch_add(1, std::memory_order_relaxed);
     *out = val.map;
+    if (!enabled) return true;
     std::lock_guard<std::mutex> lock(g_map_mutex);
     if (map_cache().size() >= kMaxCachedMaps) map_cache().clear();
     map_cache().emplace(key, val);

@@ -129,7 +129,9 @@ def test_edge_sweep_forward_backward(dtype, family):
 # ------------------------------------------------------------------ unfused pair (reference API)
 @pytest.mark.parametrize("dtype", DTYPES, ids=["bf16", "fp16"])
 @pytest.mark.parametrize("T,C,win,left,dil", [(200, 32, 7, 3, 1), (150, 16, 27, 13, 1), (33, 8, 8, 3, 1),
-                                              (37, 64, 7, 3, 2), (129, 24, 15, 7, 4), (5, 8, 9, 4, 1)])
+                                              (37, 64, 7, 3, 2), (129, 24, 15, 7, 4), (5, 8, 9, 4, 1),
+                                              (300, 64, 15, 7, 1), (1000, 32, 31, 15, 1), (129, 16, 9, 4, 2), (64, 64, 8, 0, 4),
+                                              (257, 32, 33, 32, 1)])
 def test_unfused_pair_forward_and_gradients(T, C, win, left, dil, dtype):
     from pcf_nat_b200.nattn import getNA1dFunction
     QK, AV = getNA1dFunction(C, dil, dtype)
