@@ -30,49 +30,43 @@ EncodeTiledFn encode_fn() {
 
 // ---- cache of encoded tensor maps ---------------------------------------------------------------------------------
 // A CUtensorMap is a pure function of the arguments of cuTensorMapEncodeTiled, so the encoded 128 bytes are memoised under
-// those arguments (pointer, data type, rank, extents, strides, box, swizzle): a training loop that calls a layer with the
-// same buffers every step -- or replays a pool of them -- pays the driver call once. Bounded; cleared when full.
+// those arguments (pointer, data type, rank, extents, strides, box, swizzle, device): a loop that calls a layer with the
+// same buffers every step pays the driver call once. One direct-mapped table per host thread (no lock on the hot path: the
+// library stays re-entrant, and an autograd worker thread gets a table of its own); a colliding entry is overwritten.
 namespace {
 
 struct MapKey {
     uint64_t v[16];
-    bool operator==(const MapKey& o) const { return memcmp(v, o.v, sizeof(v)) == 0; }
 };
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        uint64_t h = 1469598103934665603ull;
-        for (uint64_t x : k.v) { h ^= x; h *= 1099511628211ull; }
-        return (size_t)h;
-    }
+struct MapSlot {
+    MapKey key;
+    CUtensorMap map;
+    bool used;
 };
-struct MapValue { CUtensorMap map; };
-
-std::mutex g_map_mutex;
-std::unordered_map<MapKey, MapValue, MapKeyHash>& map_cache() {
-    static auto* m = new std::unordered_map<MapKey, MapValue, MapKeyHash>();  // never destroyed: safe at process exit
-    return *m;
-}
+constexpr int kMapSlots = 512;
+thread_local MapSlot* t_map_table = nullptr;   // allocated on a thread's first use, freed with the thread
+thread_local struct MapTableOwner { ~MapTableOwner() { delete[] t_map_table; t_map_table = nullptr; } } t_map_owner;
+thread_local int t_device = 0;                 // set by bind_primary_context() at the start of every entry point
 std::atomic<long long> g_map_hits{0}, g_map_misses{0};
-constexpr size_t kMaxCachedMaps = 4096;
 
 bool encode_cached(CUtensorMap* out, const void* base, int dtype, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
                    const cuuint32_t* box, CUtensorMapSwizzle sw) {
     // NA1D_TENSOR_MAP_CACHE=0 (read once) turns the memoisation off, for measuring what it saves
     static const bool enabled = []() { const char* e = getenv("NA1D_TENSOR_MAP_CACHE"); return !(e && e[0] == '0'); }();
-    MapKey key;
-    memset(&key, 0, sizeof(key));
-    int dev = 0;
-    cudaGetDevice(&dev);
-    key.v[0] = reinterpret_cast<uint64_t>(base);
-    key.v[1] = (uint64_t)dtype | ((uint64_t)rank << 8) | ((uint64_t)sw << 16) | ((uint64_t)dev << 32);
-    for (int i = 0; i < rank; ++i) key.v[2 + i] = dims[i];
-    for (int i = 0; i + 1 < rank; ++i) key.v[7 + i] = strides[i];
-    for (int i = 0; i < rank; ++i) key.v[11 + i] = box[i];
+    MapKey key = {};
+    MapSlot* slot = nullptr;
     if (enabled) {
-        std::lock_guard<std::mutex> lock(g_map_mutex);
-        auto it = map_cache().find(key);
-        if (it != map_cache().end()) {
-            *out = it->second.map;
+        key.v[0] = reinterpret_cast<uint64_t>(base);
+        key.v[1] = (uint64_t)dtype | ((uint64_t)rank << 8) | ((uint64_t)sw << 16) | ((uint64_t)t_device << 32);
+        for (int i = 0; i < rank; ++i) key.v[2 + i] = dims[i];
+        for (int i = 0; i + 1 < rank; ++i) key.v[7 + i] = strides[i];
+        for (int i = 0; i < rank; ++i) key.v[11 + i] = box[i];
+        uint64_t h = 1469598103934665603ull;
+        for (uint64_t x : key.v) { h ^= x; h *= 1099511628211ull; }
+        if (!t_map_table) { t_map_table = new MapSlot[kMapSlots](); (void)t_map_owner; }
+        slot = &t_map_table[(h ^ (h >> 29)) % kMapSlots];
+        if (slot->used && memcmp(slot->key.v, key.v, sizeof(key.v)) == 0) {
+            *out = slot->map;
             g_map_hits.fetch_add(1, std::memory_order_relaxed);
             return true;
         }
@@ -81,16 +75,11 @@ bool encode_cached(CUtensorMap* out, const void* base, int dtype, int rank, cons
     if (!fn) return false;
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     const CUtensorMapDataType dt = dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    MapValue val;
-    if (fn(&val.map, dt, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+    if (fn(out, dt, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     g_map_misses.fetch_add(1, std::memory_order_relaxed);
-    *out = val.map;
-    if (!enabled) return true;
-    std::lock_guard<std::mutex> lock(g_map_mutex);
-    if (map_cache().size() >= kMaxCachedMaps) map_cache().clear();
-    map_cache().emplace(key, val);
+    if (slot) { slot->key = key; slot->map = *out; slot->used = true; }
     return true;
 }
 
@@ -146,7 +135,7 @@ bool pdl_enabled() { return pdl_mode() != 0; }
 // has made no runtime call yet (an autograd worker whose first CUDA work is this library) has none: bind it explicitly.
 void bind_primary_context() {
     int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+    if (cudaGetDevice(&dev) == cudaSuccess) { cudaSetDevice(dev); t_device = dev; }
 }
 
 int device_sm_count() {
