@@ -40,6 +40,7 @@ extern "C" {
 #define NA1D_ERR_DEVICE_TIMEOUT (-8) /* a bounded wait inside a kernel expired (reported by na1d_device_status) */
 #define NA1D_ERR_TOO_LARGE (-9)      /* problem exceeds a fixed capacity of the entry point */
 #define NA1D_ERR_UNSUPPORTED (-10)   /* the requested kernel family / tiling cannot run this shape */
+#define NA1D_ERR_BAD_DROPOUT (-12)   /* dropout probability outside [0,1) */
 #define NA1D_ERR_BAD_STRIDE (-11)    /* a stride is not a positive multiple of 8 elements, or the token stride is below C */
 
 #define NA1D_MAX_WINDOW 128 /* the reference asserts win <= 80, models/PCF_NATransformer.py:53 */
@@ -179,6 +180,29 @@ int na1d_fused_backward_strided(void* dq, void* dk, void* dv, float* d_rpb, cons
                                 const int64_t* d_o_strides, const int64_t* q_strides, const int64_t* k_strides,
                                 const int64_t* v_strides, int64_t N, int64_t heads, int64_t T, int64_t C, int64_t win,
                                 int64_t left, int64_t dil, float scale, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused pair with attention dropout: p' = keep ? p / (1 - drop_p) : 0 on the normalised probabilities before the product
+ * with v, as `self.attn_drop(attn)` between softmax and AV (models/PCF_NATransformer.py:149; the reference's configs set
+ * the probability to 0). The keep decision of probability (row, kk) is a hash of (seed, dense row index n*T+t, kk) -- see
+ * drop_hash in pcf_nat_b200/csrc/na1d_common.cuh; the backward re-derives the same mask from the same seed, nothing is
+ * stored. lse is the log-sum-exp of the undropped logits. drop_p in [0,1); drop_p == 0 is the plain forward. Runs on the
+ * tcgen05 kernels (flat tiling) only: NA1D_ERR_UNSUPPORTED for other shapes. `scratch` as in the strided backward.
+ * ---------------------------------------------------------------------------------------- */
+/* The keep decisions the dropout kernels derive, computed on the HOST into a HOST buffer of rows*win bytes
+ * (keep_host[row*win + kk] = 1 if probability kk of dense row `row` = n*T+t is kept), for bit-exact checking of a
+ * restatement of the hash. No device work. No counterpart in the reference (torch's dropout draws from the Philox stream). */
+int na1d_dropout_keep_mask(uint8_t* keep_host, int64_t rows, int64_t win, float drop_p, uint64_t seed);
+
+int na1d_fused_forward_dropout(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
+                               const int32_t* valid_len, int64_t N, int64_t heads, int64_t T, int64_t C, int64_t win,
+                               int64_t left, int64_t dil, float scale, float drop_p, uint64_t seed, int dtype,
+                               void* stream);
+int na1d_fused_backward_dropout(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q,
+                                const void* k, const void* v, const float* lse, const float* rpb,
+                                const int32_t* valid_len, float* scratch, int64_t scratch_floats, int64_t N,
+                                int64_t heads, int64_t T, int64_t C, int64_t win, int64_t left, int64_t dil,
+                                float scale, float drop_p, uint64_t seed, int dtype, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Window index arithmetic as the kernels compute it, for bit-exact checking:

@@ -42,6 +42,7 @@ __all__ = [
     "na1d_logits",
     "na1d_fused",
     "na1d_fused_with_grads",
+    "dropout_keep",
 ]
 
 
@@ -141,14 +142,42 @@ def na1d_logits(q, k, win, left, dilation=1, scale=1.0, rpb=None, valid_len=None
     return s
 
 
+def dropout_keep(rows: int, win: int, drop_p: float, seed: int) -> torch.Tensor:
+    """Keep mask (rows, win), bool, of the attention dropout as the CUDA kernels derive it.
+
+    The reference applies ``nn.Dropout`` to the probabilities (models/PCF_NATransformer.py:149), drawing from torch's
+    random stream; a fused kernel cannot replay that stream, so the library defines the mask as a hash of
+    (seed, dense row index n*T+t, neighbour index kk) -- restated here in 32-bit integer arithmetic: keep iff
+    fmix32(row*2654435761 + kk*0x632BE5AB + seed32) >= floor(p * 2^32), with seed32 = low ^ high half of the 64-bit seed and
+    fmix32 the usual xor-shift / multiply finaliser.
+    """
+    import numpy as np
+    m = np.uint64(0xFFFFFFFF)
+    seed32 = np.uint64((seed ^ (seed >> 32)) & 0xFFFFFFFF)
+    row = np.arange(rows, dtype=np.uint64)[:, None]
+    kk = np.arange(win, dtype=np.uint64)[None, :]
+    x = (row * np.uint64(2654435761) + kk * np.uint64(0x632BE5AB) + seed32) & m
+    x ^= x >> np.uint64(16)
+    x = (x * np.uint64(0x85EBCA6B)) & m
+    x ^= x >> np.uint64(13)
+    x = (x * np.uint64(0xC2B2AE35)) & m
+    x ^= x >> np.uint64(16)
+    th = min(int(float(np.float32(drop_p)) * 4294967296.0), 4294967295)
+    return torch.from_numpy(x >= np.uint64(th))
+
+
 def na1d_fused(q, k, v, win, left, dilation=1, scale=1.0, rpb=None, valid_len=None, heads=1,
-               return_lse=False):
-    """Whole layer core: logits -> softmax -> weighted sum. fp32, (N,T,C) -> (N,T,C).
+               return_lse=False, drop_p=0.0, seed=0):
+    """Whole layer core: logits -> softmax -> (dropout) -> weighted sum. fp32, (N,T,C) -> (N,T,C).
 
     Restates models/PCF_NATransformer.py:141-150 (CUDA branch) == :156-171 (CPU branch).
     """
     s = na1d_logits(q, k, win, left, dilation, scale, rpb, valid_len, heads)
     p = torch.softmax(s, dim=-1)
+    if drop_p > 0:
+        N, T, _ = q.shape
+        keep = dropout_keep(N * T, win, drop_p, seed).reshape(N, T, win)
+        p = p * keep.to(p.dtype) / (1.0 - float(torch.tensor(drop_p, dtype=torch.float32)))
     o = na1d_av(p, v, win, left, dilation)
     if return_lse:
         return o, torch.logsumexp(s, dim=-1)
@@ -156,7 +185,7 @@ def na1d_fused(q, k, v, win, left, dilation=1, scale=1.0, rpb=None, valid_len=No
 
 
 def na1d_fused_with_grads(q, k, v, d_out, win, left, dilation=1, scale=1.0, rpb=None,
-                          valid_len=None, heads=1):
+                          valid_len=None, heads=1, drop_p=0.0, seed=0):
     """Forward plus autograd gradients (dq, dk, dv, drpb-or-None) of ``na1d_fused``."""
     q = q.detach().clone().requires_grad_(True)
     k = k.detach().clone().requires_grad_(True)
@@ -164,6 +193,6 @@ def na1d_fused_with_grads(q, k, v, d_out, win, left, dilation=1, scale=1.0, rpb=
     r = None
     if rpb is not None:
         r = rpb.detach().clone().requires_grad_(True)
-    o = na1d_fused(q, k, v, win, left, dilation, scale, r, valid_len, heads)
+    o = na1d_fused(q, k, v, win, left, dilation, scale, r, valid_len, heads, drop_p=drop_p, seed=seed)
     o.backward(d_out)
     return o.detach(), q.grad, k.grad, v.grad, (r.grad if r is not None else None)

@@ -67,6 +67,13 @@ _lib.na1d_fused_kernel_family.restype = _i32
 _lib.na1d_fused_kernel_family.argtypes = [_i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32]
 _lib.na1d_fused_kernel_tiling.restype = _i32
 _lib.na1d_fused_kernel_tiling.argtypes = [_i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32]
+_u64 = ctypes.c_uint64
+_lib.na1d_dropout_keep_mask.restype = _i32
+_lib.na1d_dropout_keep_mask.argtypes = [_ptr, _i64, _i64, _f32, _u64]
+_lib.na1d_fused_forward_dropout.restype = _i32
+_lib.na1d_fused_forward_dropout.argtypes = [_ptr] * 7 + [_i64] * 7 + [_f32, _f32, _u64, _i32, _ptr]
+_lib.na1d_fused_backward_dropout.restype = _i32
+_lib.na1d_fused_backward_dropout.argtypes = [_ptr] * 12 + [_i64] + [_i64] * 7 + [_f32, _f32, _u64, _i32, _ptr]
 _lib.na1d_fused_strided_supported.restype = _i32
 _lib.na1d_fused_strided_supported.argtypes = [_i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32]
 _lib.na1d_fused_forward_strided.restype = _i32

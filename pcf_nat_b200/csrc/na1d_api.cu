@@ -60,6 +60,7 @@ const char* na1d_status_string(int status) {
         case NA1D_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
         case NA1D_ERR_TOO_LARGE: return "problem exceeds a fixed capacity of this entry point (e.g. N*T above NA1D_STATIC_SCRATCH_ROWS)";
         case NA1D_ERR_UNSUPPORTED: return "the requested kernel family or tiling does not support this shape";
+        case NA1D_ERR_BAD_DROPOUT: return "bad dropout probability: need 0 <= p < 1";
         case NA1D_ERR_BAD_STRIDE: return "bad stride: element strides must be positive multiples of 8, the token stride >= C";
         default: return "unknown status";
     }
@@ -170,8 +171,9 @@ int na1d_tensor_map_cache_stats(int64_t* hits, int64_t* misses) {
 
 int na1d_device_status(void) {
     // every word is read (and cleared) before anything is reported; an expired wait in any kernel wins over a failed read
-    const int words[6] = {na1d::tc_read_status(), na1d::tc_bwd_read_status(), na1d::tc_seg_read_status(),
-                          na1d::tc_bwd_seg_read_status(), na1d::tc_unfused_read_status(), na1d::tc_unfused_t_read_status()};
+    const int words[8] = {na1d::tc_read_status(), na1d::tc_bwd_read_status(), na1d::tc_seg_read_status(),
+                          na1d::tc_bwd_seg_read_status(), na1d::tc_unfused_read_status(), na1d::tc_unfused_t_read_status(),
+                          na1d::tc_drop_read_status(), na1d::tc_bwd_drop_read_status()};
     int v = 0, w = 0;
     for (int x : words) { if (x > 0) v = x; if (x < 0) w = x; }
     if (v > 0) return NA1D_ERR_DEVICE_TIMEOUT;
@@ -288,6 +290,61 @@ int na1d_fused_backward(void* dq, void* dk, void* dv, float* d_rpb, const void* 
     }
     if (int s = cuda_status(na1d::simt_delta(delta_ws, d_o, o, g.N * g.T, g.C, dtype, st))) return s;
     return cuda_status(na1d::simt_fused_bwd(dq, dk, dv, d_rpb, d_o, q, k, v, lse, delta_ws, rpb, valid_len, g, dtype, st));
+}
+
+namespace {
+int dropout_cfg(float drop_p, uint64_t seed, na1d::DropoutCfg& cfg) {
+    if (!(drop_p >= 0.f) || drop_p >= 1.f) return NA1D_ERR_BAD_DROPOUT;
+    const double th = (double)drop_p * 4294967296.0;
+    cfg.threshold = th >= 4294967295.0 ? 4294967295u : (uint32_t)th;
+    cfg.seed = (uint32_t)(seed ^ (seed >> 32));
+    cfg.scale = 1.f / (1.f - drop_p);
+    return NA1D_OK;
+}
+}  // namespace
+
+int na1d_dropout_keep_mask(uint8_t* keep_host, int64_t rows, int64_t win, float drop_p, uint64_t seed) {
+    NA1D_REQUIRE_PTR(keep_host);
+    if (rows <= 0 || win <= 0 || rows > (int64_t)INT_MAX) return NA1D_ERR_BAD_SHAPE;
+    na1d::DropoutCfg cfg;
+    if (int s = dropout_cfg(drop_p, seed, cfg)) return s;
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t kk = 0; kk < win; ++kk)
+            keep_host[r * win + kk] = na1d::drop_hash((uint32_t)r, (uint32_t)kk, cfg.seed) >= cfg.threshold ? 1 : 0;
+    return NA1D_OK;
+}
+
+int na1d_fused_forward_dropout(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
+                               const int32_t* valid_len, int64_t N, int64_t heads, int64_t T, int64_t C, int64_t win,
+                               int64_t left, int64_t dil, float scale, float drop_p, uint64_t seed, int dtype, void* stream) {
+    if (drop_p == 0.f) return na1d_fused_forward(o, lse, q, k, v, rpb, valid_len, N, heads, T, C, win, left, dil, scale, dtype, stream);
+    NA1D_REQUIRE_PTR(o); NA1D_REQUIRE_PTR(q); NA1D_REQUIRE_PTR(k); NA1D_REQUIRE_PTR(v);
+    NA1D_REQUIRE_ALIGNED(o); NA1D_REQUIRE_ALIGNED(q); NA1D_REQUIRE_ALIGNED(k); NA1D_REQUIRE_ALIGNED(v);
+    na1d::Geometry g;
+    if (int s = check_geometry(N, heads, T, C, win, left, dil, dtype, scale, g)) return s;
+    na1d::DropoutCfg cfg;
+    if (int s = dropout_cfg(drop_p, seed, cfg)) return s;
+    if (!na1d::tc_fwd_supports(g)) return NA1D_ERR_UNSUPPORTED;
+    return cuda_status(na1d::tc_fused_fwd_dropout(o, lse, q, k, v, rpb, valid_len, g, dtype, cfg, (cudaStream_t)stream));
+}
+
+int na1d_fused_backward_dropout(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
+                                const void* v, const float* lse, const float* rpb, const int32_t* valid_len, float* scratch,
+                                int64_t scratch_floats, int64_t N, int64_t heads, int64_t T, int64_t C, int64_t win, int64_t left,
+                                int64_t dil, float scale, float drop_p, uint64_t seed, int dtype, void* stream) {
+    NA1D_REQUIRE_PTR(dq); NA1D_REQUIRE_PTR(dk); NA1D_REQUIRE_PTR(dv); NA1D_REQUIRE_PTR(d_o); NA1D_REQUIRE_PTR(q);
+    NA1D_REQUIRE_PTR(k); NA1D_REQUIRE_PTR(v); NA1D_REQUIRE_PTR(lse);
+    NA1D_REQUIRE_ALIGNED(dq); NA1D_REQUIRE_ALIGNED(dk); NA1D_REQUIRE_ALIGNED(dv); NA1D_REQUIRE_ALIGNED(d_o);
+    NA1D_REQUIRE_ALIGNED(q); NA1D_REQUIRE_ALIGNED(k); NA1D_REQUIRE_ALIGNED(v);
+    na1d::Geometry g;
+    if (int s = check_geometry(N, heads, T, C, win, left, dil, dtype, scale, g)) return s;
+    if (d_rpb && heads * win * 4 > 48 * 1024) return NA1D_ERR_TOO_LARGE;
+    if (scratch_floats < 0 || (scratch == nullptr && scratch_floats != 0)) return NA1D_ERR_NULL_POINTER;
+    na1d::DropoutCfg cfg;
+    if (int s = dropout_cfg(drop_p, seed, cfg)) return s;
+    if (!na1d::tc_bwd_supports(g, rpb != nullptr, d_rpb != nullptr)) return NA1D_ERR_UNSUPPORTED;
+    return cuda_status(na1d::tc_fused_bwd_dropout(dq, dk, dv, d_rpb, d_o, q, k, v, lse, rpb, valid_len, scratch, (size_t)scratch_floats,
+                                                  g, dtype, cfg, (cudaStream_t)stream));
 }
 
 int na1d_window_index(int32_t* j_out, uint8_t* in_range, int64_t T, int64_t win, int64_t left, int64_t dil,

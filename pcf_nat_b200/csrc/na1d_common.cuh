@@ -46,6 +46,21 @@ struct SegGeom {
     int step;  // rows between the first rows of consecutive tiles of a sequence
 };
 
+// Attention dropout (models/PCF_NATransformer.py:149: nn.Dropout on the probabilities). The keep decision of probability
+// (row, kk) is a pure function of a 32-bit seed, the dense row index n*T + t and the neighbour index kk, so the forward and
+// the backward kernels (and the CPU oracle, which restates this function) derive the same mask without storing it:
+// keep iff drop_hash(...) >= threshold, threshold = p * 2^32.
+struct DropoutCfg {
+    uint32_t threshold;   // 0 = no dropout
+    uint32_t seed;
+    float scale;          // 1 / (1 - p)
+};
+__host__ __device__ __forceinline__ uint32_t drop_hash(uint32_t row, uint32_t kk, uint32_t seed) {
+    uint32_t x = row * 2654435761u + kk * 0x632BE5ABu + seed;
+    x ^= x >> 16; x *= 0x85EBCA6Bu; x ^= x >> 13; x *= 0xC2B2AE35u; x ^= x >> 16;
+    return x;
+}
+
 // 8 consecutive 16-bit elements (one 16-byte chunk) <-> 8 floats
 template <typename E> struct Cvt;
 template <> struct Cvt<__nv_bfloat16> {

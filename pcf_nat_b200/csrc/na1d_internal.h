@@ -49,6 +49,15 @@ int tc_unfused_read_status();
 bool tc_unfused_t_supports(const Geometry& gm);
 cudaError_t tc_bandT_x(void* out, const float* band, const void* x, const Geometry& gm, int dtype, cudaStream_t st);
 int tc_unfused_t_read_status();
+
+// ---- fused pair with attention dropout (na1d_tc_fwd_drop.cu, na1d_tc_bwd_drop.cu): flat tiling of the tcgen05 kernels
+cudaError_t tc_fused_fwd_dropout(void* o, float* lse, const void* q, const void* k, const void* v, const float* rpb,
+                                 const int* valid_len, const Geometry& gm, int dtype, const DropoutCfg& drop, cudaStream_t st);
+cudaError_t tc_fused_bwd_dropout(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q, const void* k,
+                                 const void* v, const float* lse, const float* rpb, const int* valid_len, float* scratch,
+                                 size_t scratch_floats, const Geometry& gm, int dtype, const DropoutCfg& drop, cudaStream_t st);
+int tc_drop_read_status();
+int tc_bwd_drop_read_status();
 // shape limits of the tcgen05 backward, including whether its shared memory fits with a bias table (has_bias) and the
 // bias-gradient accumulators (wants_bias_grad)
 bool tc_bwd_supports(const Geometry& gm, bool has_bias = false, bool wants_bias_grad = false);

@@ -175,12 +175,15 @@ template <int NSETS> struct BwdMaps {
 //               rounded to 16 bits before the product, as the reference does (:409-415).
 constexpr int kBwdFused = 0, kBandT = 1;
 
-template <typename E, int C, int WB, bool OWN_OUT, bool SEG, int MODE = kBwdFused>
+template <typename E, int C, int WB, bool OWN_OUT, bool SEG, int MODE = kBwdFused, bool DROP = false>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict__ d_rpb, int drpb_direct,
               const float* __restrict__ lse,
               const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, SegGeom sg, int stride, int KT,
-              int total_tiles) {
+              int total_tiles, DropoutCfg drop) {
+    // With attention dropout (DROP) the forward used P' = P * keep / (1 - p): here dP = keep / (1 - p) * (dO.V^T), the P operand
+    // of dV = P'^T.dO carries the same factor, and dS = P (dP - sum P dP) uses the undropped P; the keep decisions are
+    // re-derived from (seed, dense row index, neighbour index), nothing was stored.
     constexpr int NG = tc::band_groups(WB);  // 8-column groups holding the band of a 16-row block
     constexpr int NS = bwd_stages(C);         // ring depth: tile `it` uses stage it % NS in ring round it / NS
     constexpr int kRowBytes = C * 2;
@@ -492,6 +495,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     // the two rows of this block this thread sees (row half hh): see the comments of the unrolled path below
                     float lse2[2];
                     int jb[2], vle[2], hrow[2];
+                    uint32_t drow[2] = {0u, 0u};   // dense row index n*T + t of the two rows (dropout mask key)
                     bool need_mask = false;
                     {
                         int tq = 0, hq = 0, bq = 0;
@@ -507,6 +511,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             vle[hh] = !live ? -1 : tq >= vlr ? 0 : vlr;
                             need_mask |= tq < left || tq + right >= vlr;
                             lse2[hh] = (b ? lse_next[1][hh] : lse_next[0][hh]) * kLog2e;
+                            if constexpr (DROP) drow[hh] = SEG ? (uint32_t)((scur.b * gm.H + scur.h) * T + tq * sg.d + scur.r) : (uint32_t)gq;
                             if constexpr (SEG) tq += 8; else tc::row_step8(T, gm.H, tq, hq, bq);
                         }
                     }
@@ -543,6 +548,8 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                     }
                                     const float x = fmaf(dot, sc, bias) - lse2[hh];
                                     const float p = on ? tc::fast_exp2(x) : 0.f;
+                                    if constexpr (DROP)
+                                        dpv = drop_hash(drow[hh], (uint32_t)(kk >> dshift), drop.seed) >= drop.threshold ? dpv * drop.scale : 0.f;
                                     s1[idx] = p;
                                     d1[idx] = dpv;
                                     delta[hh] = fmaf(p, dpv, delta[hh]);
@@ -580,6 +587,11 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                 }
                             }
                             pk_d[2 * g + hh] = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
+                            if constexpr (DROP) {
+                                const int off = 8 * (g - hh) + fa;
+                                p0 = drop_hash(drow[hh], (uint32_t)(off >> dshift), drop.seed) >= drop.threshold ? p0 * drop.scale : 0.f;
+                                p1 = drop_hash(drow[hh], (uint32_t)((off + 1) >> dshift), drop.seed) >= drop.threshold ? p1 * drop.scale : 0.f;
+                            }
                             pk_p[2 * g + hh] = Cvt<E>::pack2(p0, p1);
                         }
                     const uint32_t blk = (uint32_t)(4 * warp + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * warp + 2 * b) * 128u;
@@ -595,6 +607,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 //   vle : keys >= vle are masked (0 when the query itself is padding);  -1 marks a row outside the tensor
                 float lse2[2][2];
                 int jb[2][2], vle[2][2], hrow[2][2];
+                uint32_t drow[2][2] = {{0u, 0u}, {0u, 0u}};   // dense row index n*T + t of the four rows (dropout mask key)
                 bool need_mask = false;
                 {
                     int tq = 0, hq = 0, bq = 0;
@@ -610,6 +623,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                         vle[k >> 1][k & 1] = !live ? -1 : tq >= vlr ? 0 : vlr;
                         need_mask |= tq < left || tq + right >= vlr;
                         lse2[k >> 1][k & 1] = lse_next[k >> 1][k & 1] * kLog2e;
+                        if constexpr (DROP) drow[k >> 1][k & 1] = SEG ? (uint32_t)((scur.b * gm.H + scur.h) * T + tq * sg.d + scur.r) : (uint32_t)gq;
                         if constexpr (SEG) tq += 8; else tc::row_step8(T, gm.H, tq, hq, bq);
                     }
                 }
@@ -654,6 +668,8 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                     }
                                     const float x = fmaf(dot, sc, bias) - lse2[b][hh];
                                     const float p = on ? tc::fast_exp2(x) : 0.f;
+                                    if constexpr (DROP)
+                                        dpv = drop_hash(drow[b][hh], (uint32_t)(kk >> dshift), drop.seed) >= drop.threshold ? dpv * drop.scale : 0.f;
                                     s[b][idx] = p;
                                     d[b][idx] = dpv;
                                     delta[b][hh] = fmaf(p, dpv, delta[b][hh]);
@@ -697,6 +713,11 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                 }
                             }
                             pk_d[2 * g + hh] = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
+                            if constexpr (DROP) {
+                                const int off = 8 * (g - hh) + fa;
+                                p0 = drop_hash(drow[b][hh], (uint32_t)(off >> dshift), drop.seed) >= drop.threshold ? p0 * drop.scale : 0.f;
+                                p1 = drop_hash(drow[b][hh], (uint32_t)((off + 1) >> dshift), drop.seed) >= drop.threshold ? p1 * drop.scale : 0.f;
+                            }
                             pk_p[2 * g + hh] = Cvt<E>::pack2(p0, p1);
                         }
                     // core matrix of the block's first row / first column: row group 4w+2b, column group 4w+2b
@@ -866,10 +887,10 @@ __global__ void bias_grad_reduce_kernel(float* __restrict__ d_rpb, const float* 
     if (lane == 0) d_rpb[i] += acc;
 }
 
-template <typename E, int C, int WB, bool SEG, int MODE = kBwdFused>
+template <typename E, int C, int WB, bool SEG, int MODE = kBwdFused, bool DROP = false>
 cudaError_t launch_bwd(const BwdMaps<SEG ? 2 : 1>& maps, float* d_rpb, float* scratch, size_t scratch_floats,
                        const float* lse, const float* rpb, const int* valid_len, const Geometry& gm, const SegGeom& sg, int stride, int KT,
-                       int total, int sm_count, bool pdl, cudaStream_t st) {
+                       int total, int sm_count, bool pdl, const DropoutCfg& drop, cudaStream_t st) {
     const int n_bias = gm.H * gm.win;
     const BwdSmemLayout L = bwd_layout_for(C, KT, gm, rpb != nullptr, d_rpb != nullptr);
     const int smem = L.total;
@@ -880,8 +901,8 @@ cudaError_t launch_bwd(const BwdMaps<SEG ? 2 : 1>& maps, float* d_rpb, float* sc
     if constexpr (MODE != kBwdFused) {
         if (!L.own_out) return cudaErrorInvalidValue;   // the band-transpose mode exists only with the dedicated staging buffer
     }
-    auto kern = (MODE == kBwdFused && C == 64 && !L.own_out) ? tc_bwd_kernel<E, C, WB, C != 64 || MODE != kBwdFused, SEG, MODE>
-                                                             : tc_bwd_kernel<E, C, WB, true, SEG, MODE>;
+    auto kern = (MODE == kBwdFused && C == 64 && !L.own_out) ? tc_bwd_kernel<E, C, WB, C != 64 || MODE != kBwdFused, SEG, MODE, DROP>
+                                                             : tc_bwd_kernel<E, C, WB, true, SEG, MODE, DROP>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     const int grid = total < sm_count ? total : sm_count;
@@ -899,21 +920,21 @@ cudaError_t launch_bwd(const BwdMaps<SEG ? 2 : 1>& maps, float* d_rpb, float* sc
     // hold grid rows the CTAs add their row to the result with atomics instead
     const bool partial_rows = d_rpb && scratch && scratch_floats >= (size_t)grid * n_bias;
     float* bias_out = !d_rpb ? nullptr : partial_rows ? scratch : d_rpb;
-    e = cudaLaunchKernelEx(&cfg, kern, maps, bias_out, partial_rows ? 0 : 1, lse, rpb, valid_len, gm, sg, stride, KT, total);
+    e = cudaLaunchKernelEx(&cfg, kern, maps, bias_out, partial_rows ? 0 : 1, lse, rpb, valid_len, gm, sg, stride, KT, total, drop);
     if (e != cudaSuccess || !partial_rows) return e;
     bias_grad_reduce_kernel<<<(n_bias + 7) / 8, 256, 0, st>>>(d_rpb, scratch, grid, n_bias);
     return cudaGetLastError();
 }
 
 // Picks the instantiation for (channels, window bucket) of element type E; `wb` is the window the band fragments must hold.
-template <typename E, bool SEG, int MODE = kBwdFused>
+template <typename E, bool SEG, int MODE = kBwdFused, bool DROP = false>
 cudaError_t dispatch_bwd(const BwdMaps<SEG ? 2 : 1>& maps, float* d_rpb, float* scratch, size_t scratch_floats, const float* lse,
                          const float* rpb, const int* valid_len, const Geometry& gm, const SegGeom& sg, int stride, int KT, int total,
-                         int wb, cudaStream_t st) {
+                         int wb, cudaStream_t st, const DropoutCfg& drop = DropoutCfg{0u, 0u, 1.f}) {
     const int sms = device_sm_count();
     const bool pdl = pdl_mode() == 1 || pdl_mode() == 3;
 #define NA1D_TC_BWD(C, WB) \
-    return launch_bwd<E, C, WB, SEG, MODE>(maps, d_rpb, scratch, scratch_floats, lse, rpb, valid_len, gm, sg, stride, KT, total, sms, pdl, st)
+    return launch_bwd<E, C, WB, SEG, MODE, DROP>(maps, d_rpb, scratch, scratch_floats, lse, rpb, valid_len, gm, sg, stride, KT, total, sms, pdl, drop, st)
 #define NA1D_TC_BWD_W(C)                       \
     if (wb <= 9) { NA1D_TC_BWD(C, 9); }        \
     else if (wb <= 17) { NA1D_TC_BWD(C, 17); } \

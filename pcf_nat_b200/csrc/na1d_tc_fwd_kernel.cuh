@@ -97,10 +97,11 @@ template <int NSETS> struct FwdMaps {
 //             to 16 bits before the product, as the reference does (:301-306)
 constexpr int kFused = 0, kBandOut = 1, kBandIn = 2;
 
-template <typename E, int C, int WB, bool SEG, int MODE = kFused>
+template <typename E, int C, int WB, bool SEG, int MODE = kFused, bool DROP = false>
 __global__ void __launch_bounds__(kThreads, 2)
 tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict__ lse, float* __restrict__ band,
-              const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, SegGeom sg, int KT, int total_tiles) {
+              const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, SegGeom sg, int KT, int total_tiles,
+              DropoutCfg drop) {
     static_assert(MODE == kFused || !SEG, "the unfused modes run on the flat tiling");
     constexpr int NG = tc::band_groups(WB);
     constexpr int kRowBytes = C * 2;
@@ -501,6 +502,14 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                 if ((unsigned)j0 >= (unsigned)Trow) p0 = 0.f;
                                 if ((unsigned)(j0 + 1) >= (unsigned)Trow) p1 = 0.f;
                             }
+                            if constexpr (DROP) {
+                                // attention dropout on the normalised probabilities; the row's log-sum-exp is not affected
+                                const int off = 8 * (g - hh) + fa;
+                                const uint32_t row = SEG ? (uint32_t)((scur.b * gm.H + scur.h) * T + (scur.i * kTileM + warp * 32 + 16 * b + 8 * hh + fr) * sg.d + scur.r)
+                                                         : (uint32_t)(g0 + warp * 32 + 16 * b + 8 * hh + fr);
+                                p0 = drop_hash(row, (uint32_t)(off >> dshift), drop.seed) >= drop.threshold ? p0 * drop.scale : 0.f;
+                                p1 = drop_hash(row, (uint32_t)((off + 1) >> dshift), drop.seed) >= drop.threshold ? p1 * drop.scale : 0.f;
+                            }
                             pk[2 * g + hh] = Cvt<E>::pack2(p0, p1);
                         }
                     tc::st_pack<NGP>(blk + c0 * 8, pk);
@@ -551,11 +560,12 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
     }
 }
 
-template <typename E, int C, int WB, bool SEG, int MODE>
+template <typename E, int C, int WB, bool SEG, int MODE, bool DROP>
 cudaError_t launch_fwd(const FwdMaps<SEG ? 2 : 1>& maps, float* lse, float* band, const float* rpb, const int* valid_len,
-                       const Geometry& gm, const SegGeom& sg, int KT, int total, int sm_count, bool pdl, cudaStream_t st) {
+                       const Geometry& gm, const SegGeom& sg, int KT, int total, int sm_count, bool pdl, const DropoutCfg& drop,
+                       cudaStream_t st) {
     const int smem = fwd_layout(C, KT, rpb ? gm.H : 0).total;
-    auto kern = tc_fwd_kernel<E, C, WB, SEG, MODE>;
+    auto kern = tc_fwd_kernel<E, C, WB, SEG, MODE, DROP>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     const int per_sm = (2 * (smem + 1024) <= 227 * 1024) ? 2 : 1;
@@ -571,16 +581,17 @@ cudaError_t launch_fwd(const FwdMaps<SEG ? 2 : 1>& maps, float* lse, float* band
     attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, maps, lse, band, rpb, valid_len, gm, sg, KT, total);
+    return cudaLaunchKernelEx(&cfg, kern, maps, lse, band, rpb, valid_len, gm, sg, KT, total, drop);
 }
 
 // Picks the instantiation for (element type, channels, window bucket); `wb` is the window the band fragments must hold.
-template <bool SEG, int MODE = kFused>
+template <bool SEG, int MODE = kFused, bool DROP = false>
 cudaError_t dispatch_fwd(const FwdMaps<SEG ? 2 : 1>& maps, float* lse, float* band, const float* rpb, const int* valid_len,
-                         const Geometry& gm, const SegGeom& sg, int KT, int total, int wb, int dtype, cudaStream_t st) {
+                         const Geometry& gm, const SegGeom& sg, int KT, int total, int wb, int dtype, cudaStream_t st,
+                         const DropoutCfg& drop = DropoutCfg{0u, 0u, 1.f}) {
     const int sms = device_sm_count();
     const bool pdl = pdl_mode() == 1 || pdl_mode() == 2;
-#define NA1D_TC_FWD(E, C, WB) return launch_fwd<E, C, WB, SEG, MODE>(maps, lse, band, rpb, valid_len, gm, sg, KT, total, sms, pdl, st)
+#define NA1D_TC_FWD(E, C, WB) return launch_fwd<E, C, WB, SEG, MODE, DROP>(maps, lse, band, rpb, valid_len, gm, sg, KT, total, sms, pdl, drop, st)
 #define NA1D_TC_FWD_W(E, C)                        \
     if (wb <= 9) { NA1D_TC_FWD(E, C, 9); }         \
     else if (wb <= 17) { NA1D_TC_FWD(E, C, 17); }  \

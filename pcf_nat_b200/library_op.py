@@ -70,19 +70,22 @@ def _backward(ctx, d_o, d_lse):
 torch.library.register_autograd("pcf_nat_b200::na1d_fused_fwd", _backward, setup_context=_setup_context)
 
 
-def na1d_fused(q, k, v, win_size, left, dilation=1, scale=1.0, rpb=None, valid_len=None, heads=1):
+def na1d_fused(q, k, v, win_size, left, dilation=1, scale=1.0, rpb=None, valid_len=None, heads=1, drop_p=0.0, seed=0):
     """``softmax(scale q.k^T + rpb + mask) . v`` over each query's window; (N*heads, T, C) in, same shape out.
 
     Under ``torch.compile`` / tracing (fake, functional or otherwise wrapped tensors) the call goes through the registered
     ``torch.library`` ops; on plain eager tensors through ``NA1dFusedFunction``.
 
     ``rpb``: ``(1, heads, 1, win)`` (or any shape with heads*win elements) fp32 parameter or None; ``valid_len``: int tensor
-    or sequence of length N/heads (``T - padding``) or None. Differentiable in q, k, v and rpb."""
+    or sequence of length N/heads (``T - padding``) or None. ``drop_p`` > 0 applies attention dropout (the reference's
+    ``attn_drop``) with the mask that ``seed`` defines. Differentiable in q, k, v and rpb."""
+    if drop_p and (type(q) is not Tensor or torch.compiler.is_compiling()):
+        raise NotImplementedError("attention dropout is available on the eager route only")
     if type(q) is Tensor and not torch.compiler.is_compiling():
         # plain eager tensors: the autograd.Function route skips the dispatcher's generated backward (host time of a
         # forward+backward pair measured 5 to 35 % lower, depending on the host); same kernels, same saved tensors
         return ops.NA1dFusedFunction.apply(q, k, v, int(win_size), int(left), int(dilation), float(scale), rpb, valid_len,
-                                           int(heads))
+                                           int(heads), float(drop_p), int(seed))
     if valid_len is not None and not isinstance(valid_len, Tensor):
         valid_len = torch.as_tensor(valid_len, dtype=torch.int32, device=q.device)
     o, _ = na1d_fused_fwd(q, k, v, rpb, valid_len, int(win_size), int(left), int(dilation), float(scale), int(heads))

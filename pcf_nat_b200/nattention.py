@@ -83,15 +83,22 @@ def _fused_forward(self, x, padding=None):
         N, C, T = x.shape
     else:
         N, T, C = x.shape
-    if float(self.attn_drop.p) != 0.0 and self.training:
-        raise NotImplementedError("attention dropout > 0 is not fused (the reference's configs use 0)")
+    drop_p = float(self.attn_drop.p) if self.training else 0.0
+    seed = 0
+    if drop_p:
+        # attention dropout (PCF_NATransformer.py:149) inside the fused kernels: the mask is a hash of a per-call seed drawn
+        # from torch's CPU generator (reproducible under torch.manual_seed; no device synchronisation)
+        if not ops.dropout_supported(self.num_heads, T, C // self.num_heads, self.win_size, self.dilation):
+            raise NotImplementedError("attention dropout > 0 is fused for head dims 16/32/64, power-of-two dilation and a dilated "
+                                      "window of at most 33 (17 at head dim 64) only")
+        seed = int(torch.randint(0, 2 ** 62, (1,)).item())
     valid_len = None
     if not self.training and padding is not None:
         # eval: the mask follows the utterance's padding (PCF_NATransformer.py:131-134); training uses the constant mask
         valid_len = (T - padding.to(torch.int64)).clamp_(0, T).to(torch.int32).expand(N).contiguous()
     qkv = self.qkv(x)
     hd = C // self.num_heads
-    if (layout == "channels_last" and type(qkv) is torch.Tensor and qkv.is_cuda and not torch.compiler.is_compiling() and
+    if (layout == "channels_last" and not drop_p and type(qkv) is torch.Tensor and qkv.is_cuda and not torch.compiler.is_compiling() and
             ops.packed_supported(self.num_heads, T, hd, self.win_size, self.left, self.dilation, qkv.dtype)):
         # the kernels read q, k, v straight out of the packed projection output and write the output in the layout
         # `proj` consumes: no head split / merge copies (MFA_NATransformer.py:127-137, :151-152), forward or backward
@@ -100,7 +107,7 @@ def _fused_forward(self, x, padding=None):
         return self.proj_drop(self.proj(o))
     q, k, v = _split_heads(qkv, layout, self.num_heads, getattr(self, "groups", 1))
     o = na1d_fused(q, k, v, self.win_size, self.left, self.dilation, float(self.scale), self.relative_position_bias,
-                   valid_len, self.num_heads)
+                   valid_len, self.num_heads, drop_p, seed)
     return self.proj_drop(self.proj(_merge_heads(o, layout, N, self.num_heads)))
 
 

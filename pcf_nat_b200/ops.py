@@ -127,8 +127,9 @@ def _prep_valid(valid_len, batch, dev):
     return v
 
 
-def fused_forward(q, k, v, win, left, dil=1, scale=1.0, rpb=None, valid_len=None, heads=1, need_lse=True):
-    """(o, lse): o (N,T,C) in q's dtype, lse (N,T) fp32."""
+def fused_forward(q, k, v, win, left, dil=1, scale=1.0, rpb=None, valid_len=None, heads=1, need_lse=True, drop_p=0.0, seed=0):
+    """(o, lse): o (N,T,C) in q's dtype, lse (N,T) fp32. ``drop_p`` > 0 applies attention dropout with the mask that
+    ``seed`` defines (tcgen05 shapes only)."""
     _need_cuda(q, k, v)
     assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
     assert q.dtype == k.dtype == v.dtype and q.shape == k.shape == v.shape
@@ -138,14 +139,19 @@ def fused_forward(q, k, v, win, left, dil=1, scale=1.0, rpb=None, valid_len=None
     r = _prep_rpb(rpb, heads, win, q.device)
     vl = _prep_valid(valid_len, N // max(heads, 1), q.device)
     with _on_device(q.device):
-        check(_L.na1d_fused_forward(_p(o), _p(lse), _p(q), _p(k), _p(v), _p(r), _p(vl), N, heads, T, C, win, left,
-                                    dil, float(scale), _dtype_code(q), _stream(q)), "na1d_fused_forward")
+        if drop_p:
+            check(_L.na1d_fused_forward_dropout(_p(o), _p(lse), _p(q), _p(k), _p(v), _p(r), _p(vl), N, heads, T, C, win, left,
+                                                dil, float(scale), float(drop_p), int(seed), _dtype_code(q), _stream(q)),
+                  "na1d_fused_forward_dropout")
+        else:
+            check(_L.na1d_fused_forward(_p(o), _p(lse), _p(q), _p(k), _p(v), _p(r), _p(vl), N, heads, T, C, win, left,
+                                        dil, float(scale), _dtype_code(q), _stream(q)), "na1d_fused_forward")
     return o, lse
 
 
 def fused_backward(d_o, q, k, v, o, lse, win, left, dil=1, scale=1.0, rpb=None, valid_len=None, heads=1,
-                   need_d_rpb=False):
-    """(dq, dk, dv, d_rpb or None)."""
+                   need_d_rpb=False, drop_p=0.0, seed=0):
+    """(dq, dk, dv, d_rpb or None). ``drop_p`` / ``seed`` must be those of the forward call."""
     _need_cuda(d_o, q, k, v, o, lse)
     d_o = d_o.contiguous()
     N, T, C = _shape3(q)
@@ -155,9 +161,15 @@ def fused_backward(d_o, q, k, v, o, lse, win, left, dil=1, scale=1.0, rpb=None, 
     vl = _prep_valid(valid_len, N // max(heads, 1), q.device)
     d_rpb = torch.zeros((heads, win), dtype=torch.float32, device=q.device) if need_d_rpb else None
     with _on_device(q.device):
-        check(_L.na1d_fused_backward(_p(dq), _p(dk), _p(dv), _p(d_rpb), _p(d_o), _p(q), _p(k), _p(v), _p(o), _p(lse),
-                                     _p(r), _p(vl), _p(delta), N, heads, T, C, win, left, dil, float(scale),
-                                     _dtype_code(q), _stream(q)), "na1d_fused_backward")
+        if drop_p:
+            check(_L.na1d_fused_backward_dropout(_p(dq), _p(dk), _p(dv), _p(d_rpb), _p(d_o), _p(q), _p(k), _p(v), _p(lse), _p(r),
+                                                 _p(vl), _p(delta), N * T, N, heads, T, C, win, left, dil, float(scale),
+                                                 float(drop_p), int(seed), _dtype_code(q), _stream(q)),
+                  "na1d_fused_backward_dropout")
+        else:
+            check(_L.na1d_fused_backward(_p(dq), _p(dk), _p(dv), _p(d_rpb), _p(d_o), _p(q), _p(k), _p(v), _p(o), _p(lse),
+                                         _p(r), _p(vl), _p(delta), N, heads, T, C, win, left, dil, float(scale),
+                                         _dtype_code(q), _stream(q)), "na1d_fused_backward")
     return dq, dk, dv, d_rpb
 
 
@@ -276,12 +288,13 @@ class NA1dFusedFunction(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, q, k, v, win_size, left, dilation=1, scale=1.0, rpb=None, valid_len=None, heads=1):
-        o, lse = fused_forward(q, k, v, win_size, left, dilation, scale, rpb, valid_len, heads)
+    def forward(ctx, q, k, v, win_size, left, dilation=1, scale=1.0, rpb=None, valid_len=None, heads=1, drop_p=0.0, seed=0):
+        o, lse = fused_forward(q, k, v, win_size, left, dilation, scale, rpb, valid_len, heads, drop_p=drop_p, seed=seed)
         ctx.save_for_backward(q, k, v, o, lse, rpb if rpb is not None else torch.empty(0),
                               valid_len if isinstance(valid_len, torch.Tensor) else torch.empty(0))
         ctx.cfg = (win_size, left, dilation, scale, heads, rpb is not None,
                    valid_len if not isinstance(valid_len, torch.Tensor) else "tensor")
+        ctx.drop = (drop_p, seed)
         return o
 
     @staticmethod
@@ -291,14 +304,29 @@ class NA1dFusedFunction(torch.autograd.Function):
         valid_len = vl_t if vl == "tensor" else vl
         need_rpb = has_rpb and ctx.needs_input_grad[7]
         dq, dk, dv, d_rpb = fused_backward(d_o, q, k, v, o, lse, win, left, dil, scale, rpb if has_rpb else None,
-                                           valid_len, heads, need_d_rpb=need_rpb)
+                                           valid_len, heads, need_d_rpb=need_rpb, drop_p=ctx.drop[0], seed=ctx.drop[1])
         if d_rpb is not None:
             d_rpb = d_rpb.reshape(rpb.shape).to(rpb.dtype)
-        return dq, dk, dv, None, None, None, None, d_rpb, None, None
+        return dq, dk, dv, None, None, None, None, d_rpb, None, None, None, None
 
 
-def na1d_fused(q, k, v, win_size, left, dilation=1, scale=1.0, rpb=None, valid_len=None, heads=1):
-    return NA1dFusedFunction.apply(q, k, v, win_size, left, dilation, scale, rpb, valid_len, heads)
+def na1d_fused(q, k, v, win_size, left, dilation=1, scale=1.0, rpb=None, valid_len=None, heads=1, drop_p=0.0, seed=0):
+    return NA1dFusedFunction.apply(q, k, v, win_size, left, dilation, scale, rpb, valid_len, heads, drop_p, seed)
+
+
+def dropout_supported(heads, T, C, win, dil):
+    """Whether the fused pair with attention dropout can take this shape (the tcgen05 kernels on the flat tiling, with room
+    for a bias table and its gradient in the backward)."""
+    weff = (win - 1) * dil + 1
+    return C in (16, 32, 64) and dil & (dil - 1) == 0 and weff <= 33 and T >= 32 and heads <= 32 and not (C == 64 and weff > 17)
+
+
+def dropout_keep_mask(rows, win, drop_p, seed):
+    """The keep decisions of the dropout kernels as a (rows, win) bool tensor, computed on the host by the library."""
+    import numpy as np
+    buf = np.empty((rows, win), dtype=np.uint8)
+    check(_L.na1d_dropout_keep_mask(buf.ctypes.data_as(ctypes.c_void_p), rows, win, float(drop_p), int(seed)), "na1d_dropout_keep_mask")
+    return torch.from_numpy(buf.astype(bool))
 
 
 def window_index(T, win, left, dil=1, device="cuda"):

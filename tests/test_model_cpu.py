@@ -13,7 +13,7 @@ def test_extractor_wiring_with_oracle_operator(monkeypatch):
     import pcf_nat_b200.nattention as mod
     from pcf_nat_b200.model import PCFNATExtractor, model_flops_per_utterance
 
-    def oracle_op(q, k, v, win, left, dil, scale, rpb, valid_len, heads):
+    def oracle_op(q, k, v, win, left, dil, scale, rpb, valid_len, heads, drop_p=0.0, seed=0):
         return orc.na1d_fused(q, k, v, win, left, dil, scale, rpb.reshape(heads, win), None, heads)
 
     monkeypatch.setattr(mod, "na1d_fused", oracle_op)

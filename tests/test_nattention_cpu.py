@@ -55,9 +55,9 @@ def test_layer_layout_with_oracle_operator(name, monkeypatch):
     m, g = build(name)
     m.load_state_dict({k[3:]: torch.from_numpy(g[k]) for k in g.files if k.startswith("sd_")})
 
-    def oracle_op(q, k, v, win, left, dil, scale, rpb, valid_len, heads):
+    def oracle_op(q, k, v, win, left, dil, scale, rpb, valid_len, heads, drop_p=0.0, seed=0):
         vl = None if valid_len is None else [int(x) for x in valid_len]
-        return orc.na1d_fused(q, k, v, win, left, dil, scale, rpb.reshape(heads, win), vl, heads)
+        return orc.na1d_fused(q, k, v, win, left, dil, scale, rpb.reshape(heads, win), vl, heads, drop_p=drop_p, seed=seed)
 
     monkeypatch.setattr(mod, "na1d_fused", oracle_op)
     x = torch.from_numpy(g["x"])

@@ -61,3 +61,26 @@ def test_all_masked_row_is_plain_attention():
     assert torch.isfinite(o).all()
     o_nopad = orc.na1d_fused(q, k, v, 3, 1)
     torch.testing.assert_close(o[:, 6:11], o_nopad[:, 6:11])
+
+
+def test_dropout_mask_restatement_matches_the_library_bit_for_bit():
+    """The oracle's numpy restatement of the dropout hash against the library's own host-side function, and the mask's
+    statistics: keep rate 1 - p, no visible structure along rows or neighbours."""
+    from pcf_nat_b200 import ops
+    for p, seed in ((0.1, 12345), (0.5, 2 ** 40 + 7), (0.9, 0), (0.25, 2 ** 63 + 11)):
+        mine = orc.dropout_keep(4000, 27, p, seed)
+        theirs = ops.dropout_keep_mask(4000, 27, p, seed)
+        assert torch.equal(mine, theirs)
+        keep = mine.float()
+        assert abs(float(keep.mean()) - (1 - p)) < 0.01
+        assert float((keep.mean(0) - (1 - p)).abs().max()) < 0.04      # per neighbour index
+        assert float((keep[:-1] * keep[1:]).mean() - (1 - p) ** 2) < 0.01  # adjacent rows are independent
+    assert not torch.equal(orc.dropout_keep(100, 7, 0.5, 1), orc.dropout_keep(100, 7, 0.5, 2))
+
+
+def test_oracle_dropout_is_a_rescaled_masked_softmax():
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn(4, 20, 8, generator=g) for _ in range(3))
+    keep = orc.dropout_keep(4 * 20, 5, 0.3, 99).reshape(4, 20, 5).float()
+    p = torch.softmax(orc.na1d_logits(q, k, 5, 2), -1) * keep / (1 - float(torch.tensor(0.3)))
+    torch.testing.assert_close(orc.na1d_fused(q, k, v, 5, 2, drop_p=0.3, seed=99), orc.na1d_av(p, v, 5, 2))
