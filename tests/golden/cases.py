@@ -13,7 +13,7 @@ import numpy as np
 #   rpb:   True -> random relative position bias, False -> zeros
 #   grads: also store dq/dk/dv/drpb from autograd through the reference
 CASES = {
-    # BASELINE configs[0]: forward only, B=2 heads=4 L=200 head_dim=32 win=7 dil=1, no bias
+    # the forward-only parity configuration: B=2 heads=4 L=200 head_dim=32 win=7 dil=1, no bias
     "cfg1_fwd":        dict(model="mfa", B=2, H=4, T=200, D=32, win=7,      dil=1, valid_len=None,     rpb=False, scale=1.0,  grads=False, seed=0),
     "pcf_w7":          dict(model="pcf", B=2, H=2, T=48,  D=16, win=7,      dil=1, valid_len=None,     rpb=True,  scale=0.25, grads=True,  seed=11),
     "mfa_w7_pad":      dict(model="mfa", B=3, H=2, T=40,  D=16, win=7,      dil=1, valid_len=[40, 29, 3], rpb=True, scale=0.25, grads=True, seed=12),
