@@ -38,6 +38,16 @@ class UnfusedNAttention(NAttention):
         return self.proj_drop(self.proj(_merge_heads(o, layout, N, self.num_heads)))
 
 
+def _layer_norm(x, ln):
+    """LayerNorm on the activation's own dtype. Under autocast PyTorch runs layer_norm in fp32 (a cast of the 16-bit
+    residual stream up, an fp32 kernel, and a cast back down for the next projection); the mixed kernel (16-bit in/out,
+    fp32 parameters and statistics) does the same arithmetic with a third of the traffic."""
+    if x.dtype in (torch.bfloat16, torch.float16) and torch.is_autocast_enabled():
+        with torch.autocast(x.device.type, enabled=False):
+            return F.layer_norm(x, ln.normalized_shape, ln.weight, ln.bias, ln.eps)
+    return ln(x)
+
+
 class NABlock(nn.Module):
     """x + NA(LN(x)); x + MLP(LN(x)) on (N, T, C)."""
 
@@ -51,8 +61,8 @@ class NABlock(nn.Module):
         self.fc2 = nn.Linear(dim * mlp_ratio, dim)
 
     def forward(self, x, padding=None):
-        x = x + self.attn(self.norm1(x), padding)
-        return x + self.fc2(F.gelu(self.fc1(self.norm2(x))))
+        x = x + self.attn(_layer_norm(x, self.norm1), padding)
+        return x + self.fc2(F.gelu(self.fc1(_layer_norm(x, self.norm2))))
 
 
 class AttentiveStatsPool(nn.Module):

@@ -72,3 +72,37 @@ def test_compat_surface_matches_reference_names():
     nattn.install_as_na1d_tensorcore()
     from na1d_tensorcore.nattn import getNA1dFunction
     assert getNA1dFunction is nattn.getNA1dFunction
+
+
+def test_strided_entry_points_validate_on_the_host():
+    """Bad strides, dropout probabilities and shapes are refused before any device work (no GPU is needed here)."""
+    good = (ctypes.c_int64 * 3)(2 * 64 * 32, 64 * 32, 32)
+    common = (4, 2, 64, 32, 7, 3, 1, 1.0, 0, None)
+    for bad in ((0, 2048, 32), (4096, 2048, 20), (4096, 2052, 32), (-8, 2048, 32), (4096, 2048, 24)):
+        b = (ctypes.c_int64 * 3)(*bad)
+        assert L.na1d_fused_forward_strided(P, None, P, P, P, None, None, good, b, good, good, *common) == -11, bad
+    assert L.na1d_fused_forward_strided(P, None, P, P, P, None, None, good, None, good, good, *common) == -1
+    assert L.na1d_fused_forward_strided(P, None, P, P, P, None, None, good, good, good, good, 4, 2, 64, 24, 7, 3, 1, 1.0, 0, None) in (-10, -11)
+    # dropout probability outside [0, 1)
+    args = (P, None, P, P, P, None, None, 4, 2, 64, 32, 7, 3, 1, 1.0)
+    assert L.na1d_fused_forward_dropout(*args, 1.0, 5, 0, None) == -12
+    assert L.na1d_fused_forward_dropout(*args, -0.1, 5, 0, None) == -12
+    assert L.na1d_fused_forward_dropout(P, None, P, P, P, None, None, 4, 2, 64, 24, 7, 3, 1, 1.0, 0.1, 5, 0, None) == -10
+
+
+def test_kernel_tiling_choice_is_a_host_side_query():
+    """0 = CUDA cores, 1 = tcgen05 flat tiling, 2 = tcgen05 segmented tiling (no device work)."""
+    t = lambda N, T, C, win, left, dil, bw=0: L.na1d_fused_kernel_tiling(N, T, C, win, left, dil, 0, bw)
+    assert t(512, 200, 64, 7, 3, 1) == 1 and t(512, 200, 64, 7, 3, 1, 1) == 1
+    assert t(128, 3000, 64, 15, 7, 1) == 1
+    assert t(256, 1000, 64, 31, 15, 4) == 2 and t(256, 1000, 64, 31, 15, 4, 1) == 2   # dilated window beyond the flat limit
+    assert t(256, 400, 32, 15, 7, 4) == 2
+    assert t(256, 200, 64, 7, 3, 3) == 2                                             # dilation not a power of two
+    assert t(256, 200, 64, 3, 1, 4) == 1                                             # narrow dilated window: flat tiling
+    assert t(256, 1000, 64, 7, 3, 4) == 2 and t(256, 200, 64, 7, 3, 4) == 1          # bucket cost against tile utilisation
+    assert t(4, 16, 64, 7, 3, 1) == 2                                                # shorter than 32 tokens
+    assert t(4, 200, 24, 7, 3, 1) == 0 and t(4, 200, 64, 41, 20, 1) == 0 and t(4, 1, 64, 3, 1, 1) == 0
+    assert L.na1d_fused_kernel_family(256, 1000, 64, 31, 15, 4, 0, 0) == 1
+    assert L.na1d_fused_strided_supported(4, 300, 64, 7, 3, 1, 0, 1, 1) == 1
+    assert L.na1d_fused_strided_supported(4, 300, 24, 7, 3, 1, 0, 1, 1) < 0 or L.na1d_fused_strided_supported(4, 300, 24, 7, 3, 1, 0, 1, 1) == 0
+    assert L.na1d_fused_strided_supported(4, 300, 64, 31, 15, 1, 0, 1, 1) == 0        # no room for the bias tables of 4 heads

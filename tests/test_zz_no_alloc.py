@@ -76,3 +76,38 @@ def test_static_backward_rejects_more_rows_than_the_workspace_holds():
     assert s == -9
     assert b"capacity" in L.na1d_status_string(s)
     # the check is host-side: no device is needed and nothing was launched
+
+
+@pytest.mark.gpu
+def test_static_backward_allocates_nothing_and_handles_padding():
+    """Repeated calls leave the device's free memory unchanged, and a padded batch gives the regular entry point's bits."""
+    from pcf_nat_b200 import _lib, ops
+    L = _lib.lib()
+    N, H, T, C, win, left = 8, 2, 77, 32, 7, 3
+    dtype, code = torch.bfloat16, 0
+    q, k, v, d_o = (randn16((N, T, C), dtype, 820 + i).cuda() for i in range(4))
+    vl = torch.tensor([77, 40, 3, 60], dtype=torch.int32, device="cuda")
+    o, lse = ops.fused_forward(q, k, v, win, left, 1, 0.2, None, vl, H)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    got = [torch.empty_like(q) for _ in range(3)]
+    ref = [torch.empty_like(q) for _ in range(3)]
+    delta = torch.empty(N, T, device="cuda")
+    call = lambda out: L.na1d_fused_backward_static(_p(out[0]), _p(out[1]), _p(out[2]), None, _p(d_o), _p(q), _p(k), _p(v), _p(o),
+                                                    _p(lse), None, _p(vl), N, H, T, C, win, left, 1, 0.2, code, st)
+    assert call(got) == 0           # the first call on a device looks the array's address up
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        assert call(got) == 0
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, "the static entry point changed the device's free memory"
+    old = ops.set_kernel_family(ops.FAMILY_CUDA_CORE)
+    try:
+        assert L.na1d_fused_backward(_p(ref[0]), _p(ref[1]), _p(ref[2]), None, _p(d_o), _p(q), _p(k), _p(v), _p(o), _p(lse), None,
+                                     _p(vl), _p(delta), N, H, T, C, win, left, 1, 0.2, code, st) == 0
+    finally:
+        ops.set_kernel_family(old)
+    torch.cuda.synchronize()
+    for a, b in zip(got, ref):
+        assert torch.equal(a, b)
