@@ -40,11 +40,11 @@ class UnfusedNAttention(NAttention):
 
 def _layer_norm(x, ln):
     """LayerNorm on the activation's own dtype. Under autocast PyTorch runs layer_norm in fp32 (a cast of the 16-bit
-    residual stream up, an fp32 kernel, and a cast back down for the next projection); the mixed kernel (16-bit in/out,
-    fp32 parameters and statistics) does the same arithmetic with a third of the traffic."""
+    residual stream up, an fp32 kernel, and a cast back down for the next projection); the 16-bit kernel (16-bit in/out and
+    parameters, fp32 statistics) does the same arithmetic with a third of the traffic."""
     if x.dtype in (torch.bfloat16, torch.float16) and torch.is_autocast_enabled():
         with torch.autocast(x.device.type, enabled=False):
-            return F.layer_norm(x, ln.normalized_shape, ln.weight, ln.bias, ln.eps)
+            return F.layer_norm(x, ln.normalized_shape, ln.weight.to(x.dtype), ln.bias.to(x.dtype), ln.eps)
     return ln(x)
 
 
