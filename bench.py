@@ -654,6 +654,8 @@ def main():
     ap.add_argument("--attention", default="fused", choices=["fused", "unfused"], help="model workloads: operator variant")
     ap.add_argument("--precision", default="autocast", choices=["bf16", "autocast"],
                     help="model workloads: bf16 weights/activations with fp32 master weights, or bf16 autocast over fp32 parameters")
+    ap.add_argument("--crop-batches", action="store_true",
+                    help="cfg5_embed: cut every length-sorted batch to its own longest utterance (the reference's length-bucketed loader)")
     ap.add_argument("--host-cost", action="store_true", help="host microseconds per forward+backward C-ABI call pair at a small shape")
     args = ap.parse_args()
     if args.host_cost:

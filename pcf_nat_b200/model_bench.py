@@ -255,9 +255,13 @@ def run_train(args):
 
 
 class Extractor:
-    """Embedding extraction of one rank's share of a set of utterances, in batches of up to `batch` utterances."""
+    """Embedding extraction of one rank's share of a set of utterances, in batches of up to `batch` utterances.
 
-    def __init__(self, n_local, dev, rank, batch=512, frames=FRAMES, attention="fused", precision="autocast"):
+    `crop` follows the reference's length-bucketed loader (``evaluate_main.py:36-57, 118-123``: utterances sorted by length,
+    every batch padded only to its own longest member): a batch is cut to its longest utterance, rounded up to 8 frames,
+    before it enters the network, instead of carrying the padding of the longest utterance of the whole set."""
+
+    def __init__(self, n_local, dev, rank, batch=512, frames=FRAMES, attention="fused", precision="autocast", crop=False):
         from .model import PCFNATExtractor
         torch.manual_seed(4)
         self.model = PCFNATExtractor(frames=frames, attention=attention).to(dev).eval()
@@ -270,40 +274,43 @@ class Extractor:
         self.lens = torch.sort(torch.randint(2 * frames // 3, frames + 1, (n_local,), device=dev, generator=g))[0]
         self.emb = torch.empty(n_local, EMB, device=dev)
         self.chunks = [(a, min(a + batch, n_local)) for a in range(0, n_local, batch)]
-        self.static = {}   # batch size -> (fbank buffer, lens buffer, output, graph)
+        # frames each batch is run at: its longest utterance (the lengths are sorted), or the whole padded length
+        self.batch_frames = [min(frames, -(-int(self.lens[b - 1]) // 8) * 8) if crop else frames for a, b in self.chunks]
+        self.static = {}   # (batch size, frames) -> (fbank buffer, lens buffer, output, graph)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for a, b in self.chunks[:1] + self.chunks[-1:]:
-                self._embed(self.fbank[a:b], self.lens[a:b])
+            for (a, b), tb in list(zip(self.chunks, self.batch_frames))[:1] + list(zip(self.chunks, self.batch_frames))[-1:]:
+                self._embed(self.fbank[a:b, :, :tb], self.lens[a:b])
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        for a, b in self.chunks:
-            n = b - a
-            if n in self.static:
+        for (a, b), tb in zip(self.chunks, self.batch_frames):
+            key = (b - a, tb)
+            if key in self.static:
                 continue
-            x, ln = self.fbank[a:b].clone(), self.lens[a:b].clone()
+            x, ln = self.fbank[a:b, :, :tb].clone(), self.lens[a:b].clone()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 out = self._embed(x, ln)
-            self.static[n] = (x, ln, out, graph)
+            self.static[key] = (x, ln, out, graph)
 
     def _embed(self, x, lens):
         with torch.no_grad():
             # mean normalisation over the valid frames (evaluate_main.py:78-82), then the network with padding masks
-            t = torch.arange(self.frames, device=x.device).view(1, 1, -1)
+            frames = x.shape[-1]
+            t = torch.arange(frames, device=x.device).view(1, 1, -1)
             mask = (t < lens.view(-1, 1, 1)).to(x.dtype)
-            x = x - (x * mask).sum(-1, keepdim=True) / lens.view(-1, 1, 1).to(x.dtype)
+            x = (x - (x * mask).sum(-1, keepdim=True) / lens.view(-1, 1, 1).to(x.dtype)) * mask   # padded frames are zeros
             if self.precision == "bf16":
-                return self.model.embedding(x.to(torch.bfloat16), (self.frames - lens).to(torch.int32)).float()
+                return self.model.embedding(x.to(torch.bfloat16), (frames - lens).to(torch.int32)).float()
             with torch.autocast("cuda", dtype=torch.bfloat16, cache_enabled=False):
-                return self.model.embedding(x, (self.frames - lens).to(torch.int32)).float()
+                return self.model.embedding(x, (frames - lens).to(torch.int32)).float()
 
     def run(self, source=None):
         """One pass over the local utterances; `source` = pinned host features to upload batch by batch (end to end)."""
-        for a, b in self.chunks:
-            x, ln, out, graph = self.static[b - a]
-            x.copy_(self.fbank[a:b] if source is None else source[a:b], non_blocking=True)
+        for (a, b), tb in zip(self.chunks, self.batch_frames):
+            x, ln, out, graph = self.static[(b - a, tb)]
+            x.copy_((self.fbank if source is None else source)[a:b, :, :tb], non_blocking=True)
             ln.copy_(self.lens[a:b], non_blocking=True)
             graph.replay()
             self.emb[a:b].copy_(out, non_blocking=True)
@@ -319,7 +326,7 @@ def run_embed(args):
     if total % world:
         raise SystemExit("the utterance count %d must divide by the number of ranks" % total)
     n_local = total // world if args.scaling == "strong" else total
-    ex = Extractor(n_local, dev, rank, attention=args.attention, precision=args.precision)
+    ex = Extractor(n_local, dev, rank, attention=args.attention, precision=args.precision, crop=args.crop_batches)
     gathered = torch.empty(world * n_local, EMB, device=dev)
 
     def step(source=None):
@@ -352,7 +359,8 @@ def run_embed(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "cfg5_embed", "utterances": n_all, "per_gpu_utterances": n_local, "batch": 512, "frames": FRAMES,
-                       "lengths": "2-3 s, sorted; padding masks inside the attention layers", "attention": args.attention,
+                       "lengths": "2-3 s, sorted; padding masks inside the attention layers" +
+                       ("; every batch cut to its own longest utterance" if args.crop_batches else ""), "attention": args.attention,
                        "launch": "one CUDA graph per batch size, then one all-gather of the (utterances/ranks, 192) embeddings",
                        "parallelism": "dp%d" % world, "finite": finite},
             "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak * world, "unit": "TFLOP/s", "frac": tflops / (peak * world),
