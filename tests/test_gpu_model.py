@@ -23,7 +23,7 @@ def test_fused_and_unfused_networks_agree():
         with torch.autocast("cuda", dtype=torch.bfloat16):
             loss = m(x, y)
         loss.backward()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
         grads.append(torch.cat([p.grad.reshape(-1).float() for p in m.parameters()]))
     assert abs(losses[0] - losses[1]) < 2e-2 * max(1.0, abs(losses[1])), losses
     rel = float((grads[0] - grads[1]).norm() / grads[1].norm())
