@@ -638,6 +638,41 @@ def run_host_cost(args):
                       "wall_us_per_pair_incl_gpu": wall_us, "cache_hits": h1 - h0, "cache_misses": m1 - m0, "pairs": n}), flush=True)
 
 
+def run_layer_cost(args):
+    """Forward+backward time of one whole attention layer at the reference's own layer shape (512 utterances, 150 frames,
+    dim 256, 16 heads, window 27, groups 8; models/PCF_NATransformer.py:44-178 and the MFA twin), bf16 autocast, for both
+    layouts: through the strided tensor maps (no head split / merge copies) and with the copies around the dense operator."""
+    import pcf_nat_b200.nattention as mod
+    from pcf_nat_b200 import NAttention, ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    N, T, dim, heads, win = 512, 150, 256, 16, 27
+    out = {"what": "one NAttention layer forward+backward, N=512 T=150 dim=256 heads=16 win=27, bf16 autocast, us per call"}
+    real_supported = ops.packed_supported
+    for layout, groups in (("channels_first", 8), ("channels_last", 1)):
+        torch.manual_seed(0)
+        layer = NAttention(T, dim, heads, win, groups=groups, layout=layout).to(dev)
+        x = torch.randn((N, dim, T) if layout == "channels_first" else (N, T, dim), device=dev, requires_grad=True)
+
+        def step():
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                y = layer(x)
+            y.backward(torch.ones_like(y))
+        for name, fn in (("strided", real_supported), ("copies", lambda *a, **k: False)):
+            ops.packed_supported = fn
+            mod.ops.packed_supported = fn
+            g = torch.cuda.CUDAGraph()
+            for _ in range(3):
+                step()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g):
+                step()
+            out["%s_%s" % (layout, name)] = _time_fn(g.replay, 50)
+    ops.packed_supported = real_supported
+    ops.device_status()
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -656,10 +691,13 @@ def main():
                     help="model workloads: bf16 weights/activations with fp32 master weights, or bf16 autocast over fp32 parameters")
     ap.add_argument("--crop-batches", action="store_true",
                     help="cfg5_embed: cut every length-sorted batch to its own longest utterance (the reference's length-bucketed loader)")
+    ap.add_argument("--layer-cost", action="store_true", help="whole attention layer, strided route against the copying route")
     ap.add_argument("--host-cost", action="store_true", help="host microseconds per forward+backward C-ABI call pair at a small shape")
     args = ap.parse_args()
     if args.host_cost:
         return run_host_cost(args)
+    if args.layer_cost:
+        return run_layer_cost(args)
     if args.sweep:
         return run_sweep(args)
     if args.workload in MODEL_WORKLOADS:

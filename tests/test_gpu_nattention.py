@@ -154,3 +154,26 @@ def test_global_attention_layer_on_gpu(name):
     ref, dref = torch.from_numpy(z["y"]), torch.from_numpy(z["dx"])
     assert float((y.detach().float().cpu() - ref).abs().max()) <= 3e-2 * max(1.0, float(ref.abs().max()))
     assert float((x.grad.cpu() - dref).abs().max()) <= 3e-2 * max(1.0, float(dref.abs().max()))
+
+
+@pytest.mark.parametrize("name", ["module_pcf_w7", "module_pcf_g2_asym", "module_mfa_w7"])
+def test_layer_routes_make_no_layout_copies(name, monkeypatch):
+    """Both layouts reach the kernels through strided tensor maps: the head split / merge copies are never made."""
+    import pcf_nat_b200.nattention as mod
+
+    def boom(*a, **k):
+        raise AssertionError("a head split / merge copy was made")
+
+    monkeypatch.setattr(mod, "_split_heads", boom)
+    monkeypatch.setattr(mod, "_merge_heads", boom)
+    m, g = _layer(name, torch.bfloat16)
+    x = torch.from_numpy(g["x"]).cuda().to(torch.bfloat16).requires_grad_(True)
+    y = m.eval()(x, torch.from_numpy(g["padding"]).cuda())
+    y.backward(torch.from_numpy(g["gy"]).cuda().to(torch.bfloat16))
+    _close(y, g["y_eval"], torch.bfloat16, name + " y_eval")
+    _close(x.grad, g["dx_eval"], torch.bfloat16, name + " dx")
+    # and under autocast with fp32 parameters and input, as a training script runs it
+    m32, _ = _layer(name, torch.float32)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y32 = m32.eval()(torch.from_numpy(g["x"]).cuda(), torch.from_numpy(g["padding"]).cuda())
+    _close(y32, g["y_eval"], torch.bfloat16, name + " y_eval under autocast")
