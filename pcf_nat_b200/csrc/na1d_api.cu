@@ -124,9 +124,10 @@ static int pick_family(const na1d::Geometry& g, int backward, bool has_bias = fa
     int pick = 0;
     if (flat_ok && seg_ok && g.dil > 1) {
         // relative cost of a tile row in the window buckets 9 / 17 / 33 (measured at 64 utterances x 4 heads, 200 to 1000
-        // tokens: the two narrow buckets cost about the same, the widest is bound by its compute warps), times the rows the
+        // tokens: the two narrow buckets cost about the same, the widest is bound by its compute warps, more so in the backward
+        // with its two fragment sets per block), times the rows the
         // tiling processes per useful row, plus 10 % for the segmented tiling's shorter runs of tiles
-        auto bucket_cost = [](int w) { return w <= 9 ? 1.0 : w <= 17 ? 1.05 : 1.5; };
+        auto bucket_cost = [backward](int w) { return w <= 9 ? 1.0 : w <= 17 ? 1.05 : backward ? 2.0 : 1.5; };
         const int tp = (g.T + g.dil - 1) / g.dil;
         const int step = backward ? 128 - (g.win - 1) : 128;
         const double seg_rows = (double)((tp + step - 1) / step) * step / tp;

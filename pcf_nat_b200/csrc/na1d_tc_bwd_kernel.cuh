@@ -465,7 +465,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int kc = 8 * (g - hh) + e;
-                                const bool on = ((band_bits >> (2 * (g - hh + 1) + e)) & 1u) && live4[b][hh] &&
+                                const bool on = !tc::dead_slot(g, hh, NG) && ((band_bits >> (2 * (g - hh + 1) + e)) & 1u) && live4[b][hh] &&
                                                 (unsigned)(jb[b][hh] + kc) < (unsigned)T;
                                 p[e] = on ? __ldg(src + ((kc + fa) >> dshift)) : 0.f;
                             }
@@ -535,6 +535,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
 #pragma unroll
                                 for (int e = 0; e < 2; ++e) {
                                     const int idx = 4 * g + 2 * hh + e;
+                                    if (tc::dead_slot(g, hh, NG)) { s1[idx] = 0.f; d1[idx] = 0.f; continue; }
                                     const int kc = 8 * (g - hh) + e, kk = kc + fa;
                                     bool on = (band_bits >> (2 * (g - hh + 1) + e)) & 1u;
                                     float bias = 0.f;
@@ -571,6 +572,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
 #pragma unroll
                         for (int hh = 0; hh < 2; ++hh) {
                             const int idx = 4 * g + 2 * hh;
+                            if (tc::dead_slot(g, hh, NG)) { pk_d[2 * g + hh] = 0u; pk_p[2 * g + hh] = 0u; continue; }
                             float ds0 = s1[idx] * (d1[idx] - delta[hh]);
                             float ds1 = s1[idx + 1] * (d1[idx + 1] - delta[hh]);
                             float p0 = s1[idx], p1 = s1[idx + 1];
@@ -655,6 +657,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
     #pragma unroll
                                 for (int e = 0; e < 2; ++e) {
                                     const int idx = 4 * g + 2 * hh + e;
+                                    if (tc::dead_slot(g, hh, NG)) { s[b][idx] = 0.f; d[b][idx] = 0.f; continue; }
                                     const int kc = 8 * (g - hh) + e, kk = kc + fa;
                                     bool on = (band_bits >> (2 * (g - hh + 1) + e)) & 1u;
                                     float bias = 0.f;
@@ -695,6 +698,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
     #pragma unroll
                         for (int hh = 0; hh < 2; ++hh) {
                             const int idx = 4 * g + 2 * hh;
+                            if (tc::dead_slot(g, hh, NG)) { pk_d[2 * g + hh] = 0u; pk_p[2 * g + hh] = 0u; continue; }
                             float ds0 = s[b][idx] * (d[b][idx] - delta[b][hh]);
                             float ds1 = s[b][idx + 1] * (d[b][idx + 1] - delta[b][hh]);
                             float p0 = s[b][idx], p1 = s[b][idx + 1];

@@ -30,6 +30,12 @@ __host__ __device__ constexpr int round_up(int x, int m) { return (x + m - 1) / 
 // column groups of 8 that can hold band entries of a 16-row block
 __host__ __device__ constexpr int band_groups(int win_max) { return (15 + win_max + 7) / 8; }
 
+// Fragment slot (g, hh, e) of a thread holds window offset 8 (g - hh) + e + fa with fa in [-7, 6]. The slots with
+// g - hh == -1 (offsets below 0) and g - hh == NG - 1 (offsets of at least 8 NG - 15 >= the bucket's widest window) can
+// never be band entries: a third of the slots in the narrowest bucket, a sixth in the widest. Loops over (g, hh) are fully
+// unrolled, so this test is resolved at compile time and the arithmetic of those slots disappears.
+__host__ __device__ constexpr bool dead_slot(int g, int hh, int ng) { return g - hh == -1 || g - hh == ng - 1; }
+
 // Dilation d (a power of two) is handled as a window of (win-1) d + 1 consecutive keys of which every d-th is a neighbour:
 // tiles, halos and masks use the effective window, the band test adds `offset % d == 0`.
 __host__ __device__ constexpr int eff_window(int win, int dil) { return (win - 1) * dil + 1; }

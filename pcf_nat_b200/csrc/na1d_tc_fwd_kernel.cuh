@@ -380,7 +380,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int kc = 8 * (g - hh) + e;
-                                if (!((band_bits >> (2 * (g - hh + 1) + e)) & 1u)) continue;
+                                if (tc::dead_slot(g, hh, NG) || !((band_bits >> (2 * (g - hh + 1) + e)) & 1u)) continue;
                                 const unsigned j = (unsigned)(jb[b][hh] + kc);
                                 dst[(kc + fa) >> dshift] = j < (unsigned)Trow ? s[b][4 * g + 2 * hh + e] : 0.f;
                             }
@@ -402,8 +402,8 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int kc = 8 * (g - hh) + e;
-                                const bool on = ((band_bits >> (2 * (g - hh + 1) + e)) & 1u) && gq < rows_total &&
-                                                (unsigned)(jb[b][hh] + kc) < (unsigned)Trow;
+                                const bool on = !tc::dead_slot(g, hh, NG) && ((band_bits >> (2 * (g - hh + 1) + e)) & 1u) &&
+                                                gq < rows_total && (unsigned)(jb[b][hh] + kc) < (unsigned)Trow;
                                 s[b][4 * g + 2 * hh + e] = on ? __ldg(src + ((kc + fa) >> dshift)) : 0.f;
                             }
                     }
@@ -421,6 +421,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                         for (int g = 0; g < NG; ++g)
 #pragma unroll
                             for (int hh = 0; hh < 2; ++hh) {
+                                if (tc::dead_slot(g, hh, NG)) { s[b][4 * g + 2 * hh] = s[b][4 * g + 2 * hh + 1] = -INFINITY; continue; }
                                 float2 bias2 = make_float2(0.f, 0.f);  // biases of the thread's two adjacent columns of this group
                                 if (rpb) bias2 = *reinterpret_cast<const float2*>(brow[b][hh] + 8 * (g - hh));
 #pragma unroll
@@ -455,6 +456,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int idx = 4 * g + 2 * hh + e;
+                                if (tc::dead_slot(g, hh, NG)) { s[b][idx] = 0.f; continue; }
                                 const float p = tc::fast_exp2(s[b][idx] - mx[b][hh]);  // exp2(-inf) = 0 outside the band
                                 s[b][idx] = p;
                                 sum[b][hh] += p;
@@ -493,7 +495,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     for (int g = 0; g < NGP; ++g)
 #pragma unroll
                         for (int hh = 0; hh < 2; ++hh) {
-                            if (g >= NG) { pk[2 * g + hh] = 0u; continue; }
+                            if (g >= NG || tc::dead_slot(g, hh, NG)) { pk[2 * g + hh] = 0u; continue; }
                             float p0 = s[b][4 * g + 2 * hh] * sum[b][hh], p1 = s[b][4 * g + 2 * hh + 1] * sum[b][hh];
                             if (need_mask) {
                                 // a neighbour outside the query's sequence is a zero V row in the reference: it counts in the
