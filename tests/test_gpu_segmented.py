@@ -22,6 +22,8 @@ SEG_SHAPES = [
     (4, 2, 131, 32, 7, 3, 3), (2, 2, 257, 64, 7, 3, 5), (3, 1, 1000, 16, 15, 7, 4), (2, 1, 1001, 32, 31, 15, 4),
     (8, 4, 50, 64, 3, 1, 2), (2, 2, 300, 64, 7, 3, 1), (4, 2, 77, 32, 9, 0, 3), (4, 2, 77, 16, 9, 8, 6),
     (2, 1, 640, 64, 17, 8, 2), (2, 2, 129, 32, 33, 16, 2), (4, 4, 64, 16, 8, 3, 7),
+    # residue sequences of two or three tokens, windows wider than a residue sequence
+    (4, 2, 10, 32, 3, 1, 5), (4, 2, 11, 32, 9, 4, 5), (2, 1, 23, 16, 7, 3, 11), (64, 32, 40, 16, 5, 2, 3),
 ]
 
 
