@@ -64,6 +64,8 @@ struct BwdSmemLayout {
     int stage_q, stage_do, stage_k, stage_v, stage_bytes;  // offsets inside one stage
     int ds, p, out, misc, total;
     bool own_out;  // a dedicated 128-row staging buffer for the outputs fits next to everything else
+    int out_bufs;  // how many of them: 3 (one per output: the three TMA stores of a tile go out together and are only waited
+                   // for when the next tile needs the buffers), 1 (three rounds through one buffer) or 0
 };
 constexpr int kBiasRowB = 16 + 48;  // per-head table: log2e * rpb[h][kk] at index kk + 16, kk in [-16, 48)
 // Depth of the operand ring: 64-channel tiles fill shared memory with two stages; narrower rows leave room for a third, which
@@ -81,8 +83,10 @@ __host__ __device__ inline BwdSmemLayout bwd_layout(int C, int KT, int bias_head
     L.out = L.p + kTileM * KT * 2;
     // misc block, bias table, bias-gradient accumulator, alignment slack
     const int tail = 512 + round_up(bias_heads * kBiasRowB * 4, 256) + round_up(acc_floats * 4, 256) + 1008;
-    L.own_out = L.out + round_up(kTileM * C * 2, 1024) + tail <= 227 * 1024;
-    L.misc = L.out + (L.own_out ? round_up(kTileM * C * 2, 1024) : 0);
+    const int out_buf = round_up(kTileM * C * 2, 1024);
+    L.out_bufs = L.out + 3 * out_buf + tail <= 227 * 1024 ? 3 : L.out + out_buf + tail <= 227 * 1024 ? 1 : 0;
+    L.own_out = L.out_bufs > 0;
+    L.misc = L.out + L.out_bufs * out_buf;
     L.total = L.misc + tail;
     return L;
 }
@@ -816,6 +820,36 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     ptx::mbar_arrive(&misc->o_free[which]);
 #pragma unroll
                     for (int c = 0; c < CH; ++c) pk[which][c] = Cvt<E>::pack(acc + c * 8);
+                }
+                if (L.out_bufs == 3) {
+                    // one buffer per output: wait (only now) until the previous tile's stores have read them, stage all three,
+                    // issue the three stores together
+                    if (tid == 128) ptx::tma_store_wait_read();
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                    constexpr int kOutBuf = round_up(kTileM * C * 2, 1024);
+#pragma unroll
+                    for (int which = 0; which < 3; ++which) {
+                        if (MODE == kBandT && which != 1) continue;
+                        const int ms = r - (which == 0 ? right : win - 1);
+                        if (ms >= 0 && ms < stride) {
+                            const int swz = (C == 64) ? (ms & 7) : (C == 32) ? ((ms >> 1) & 3) : ((ms >> 2) & 1);
+#pragma unroll
+                            for (int c = 0; c < CH; ++c)
+                                *reinterpret_cast<uint4*>(buf + which * kOutBuf + ms * kRowBytes + ((c ^ swz) * 16)) = pk[which][c];
+                        }
+                    }
+                    ptx::fence_proxy_async_smem();
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                    if (tid == 128) {
+#pragma unroll
+                        for (int which = 0; which < 3; ++which) {
+                            if (MODE == kBandT && which != 1) continue;
+                            store_rows(which == 0 ? tm.dq : which == 1 ? tm.dv : tm.dk, buf + which * kOutBuf, out_row);
+                        }
+                        ptx::tma_store_commit();
+                    }
+                    if constexpr (SEG) ocur.advance();
+                    continue;
                 }
 #pragma unroll
                 for (int which = 0; which < 3; ++which) {
