@@ -53,8 +53,13 @@ using tc::kTileM;
 using tc::round_up;
 using tc::RowSwizzle;
 using tc::Fmt;
-constexpr int kThreads = 384;
-constexpr int kProducerWarp = 8, kMmaWarp = 9;  // warps 9, 10, 11 issue MMAs
+// Warp roles: NCW compute warps (0 .. NCW-1), four epilogue warps, the producer warp, three MMA-issuer warps.
+// NCW = 4: compute warp w owns the 32 tensor-memory lanes of quarter w, two 16-row blocks one after the other or together.
+// NCW = 8 (rows of at most 64 bytes, where registers allow 512 threads): warps w and w + 4 share quarter w & 3 and take one
+// 16-row block each, so every scheduler has two compute warps to hide the latencies of the dependent chain
+// TMEM load -> exp -> shuffle -> pack -> stmatrix behind one another.
+__host__ __device__ constexpr int compute_warps(int C, int mode) { return (C <= 32 && mode == 0) ? 8 : 4; }
+__host__ __device__ constexpr int bwd_threads(int ncw) { return (ncw + 8) * 32; }
 constexpr int kQ = 0, kDO = 1, kK = 2, kV = 3;  // buffers of a stage
 constexpr int kTmemCols = 512;
 constexpr int kColDP = 160, kColDQ = 320, kColDK = 384, kColDV = 448;
@@ -151,8 +156,10 @@ __device__ __noinline__ void bias_grad_tile(const uint8_t* row, int r, int lane,
 
 // The layout as both the launcher and the kernel compute it (one function, so they cannot disagree): bias table for every
 // head when there is a bias, four per-warp (H, win) accumulators when its gradient is wanted.
-__host__ __device__ inline BwdSmemLayout bwd_layout_for(int C, int KT, const Geometry& gm, bool has_bias, bool wants_bias_grad) {
-    return bwd_layout(C, KT, has_bias ? gm.H : 0, wants_bias_grad ? 4 * gm.H * gm.win : 0);
+__host__ __device__ inline BwdSmemLayout bwd_layout_for(int C, int KT, const Geometry& gm, bool has_bias, bool wants_bias_grad,
+                                                        int ncw = 0) {
+    if (ncw == 0) ncw = compute_warps(C, 0);   // one (H, win) bias-gradient accumulator per compute warp
+    return bwd_layout(C, KT, has_bias ? gm.H : 0, wants_bias_grad ? ncw * gm.H * gm.win : 0);
 }
 
 struct alignas(8) BwdMisc {
@@ -180,7 +187,7 @@ template <int NSETS> struct BwdMaps {
 constexpr int kBwdFused = 0, kBandT = 1;
 
 template <typename E, int C, int WB, bool OWN_OUT, bool SEG, int MODE = kBwdFused, bool DROP = false>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(bwd_threads(compute_warps(C, MODE)), 1)
 tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict__ d_rpb, int drpb_direct,
               const float* __restrict__ lse,
               const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, SegGeom sg, int stride, int KT,
@@ -190,11 +197,13 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
     // re-derived from (seed, dense row index, neighbour index), nothing was stored.
     constexpr int NG = tc::band_groups(WB);  // 8-column groups holding the band of a 16-row block
     constexpr int NS = bwd_stages(C);         // ring depth: tile `it` uses stage it % NS in ring round it / NS
+    constexpr int NCW = compute_warps(C, MODE);
+    constexpr int kThreads = bwd_threads(NCW), kProducerWarp = NCW + 4, kMmaWarp = NCW + 5, kEpiTid = NCW * 32;
     constexpr int kRowBytes = C * 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int n_bias = gm.H * gm.win;  // entries of the bias gradient
-    const BwdSmemLayout L = bwd_layout_for(C, KT, gm, rpb != nullptr, d_rpb != nullptr);
+    const BwdSmemLayout L = bwd_layout_for(C, KT, gm, rpb != nullptr, d_rpb != nullptr, NCW);
     uint8_t* sDS = smem + L.ds;
     uint8_t* sP = smem + L.p;
     BwdMisc* misc = reinterpret_cast<BwdMisc*>(smem + L.misc);
@@ -245,11 +254,11 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
         for (int s = 0; s < NS; ++s)
             for (int b = 0; b < 4; ++b) { ptx::mbar_init(&misc->full[s][b], 1); ptx::mbar_init(&misc->empty[s][b], 1); }
         ptx::mbar_init(&misc->s_ready, 2);   // S chain and dP chain
-        ptx::mbar_init(&misc->s_free, 128);
-        ptx::mbar_init(&misc->p_ready, 128);
+        ptx::mbar_init(&misc->s_free, NCW * 32);
+        ptx::mbar_init(&misc->p_ready, NCW * 32);
         ptx::mbar_init(&misc->o_ready, MODE == kBwdFused ? 3 : 1);   // dQ, dV, dK chains (only dV in the band-transpose mode)
         for (int i = 0; i < 3; ++i) ptx::mbar_init(&misc->o_free[i], 128);
-        ptx::mbar_init(&misc->acc_done, 128);
+        ptx::mbar_init(&misc->acc_done, NCW * 32);
         misc->abort = 0;
         ptx::fence_mbar_init();
         for (int i = 0; i < (SEG ? 2 : 1); ++i) {
@@ -377,12 +386,17 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
             }
             if (!ok) { atomicExch(&g_tc_bwd_status, 12); *abort_flag = 1; }
         }
-    } else if (warp < 4) {
+    } else if (warp < NCW) {
         // ------------------------------------------------------------ compute warps
-        const int r = warp * 32 + lane;                 // row of the 32x32b epilogue loads
+        const int cw = warp & 3;                        // quarter of the tensor-memory lanes (and tile rows) this warp works on
+        const int bsel = warp >> 2;                     // NCW = 8: the 16-row block of that quarter this warp takes
+        const int ct = warp * 32 + lane;                // index among the compute threads
+        // row of the tile whose dS this lane reads back for the bias gradient: a warp reads back exactly the rows it is about
+        // to overwrite (NCW = 8: its own 16-row block, on lanes 0-15)
+        const int r = NCW == 8 ? cw * 32 + bsel * 16 + (lane & 15) : cw * 32 + lane;
         const int fr = lane >> 2, fc = 2 * (lane & 3);  // fragment row / first column inside an 8x8 block
         const int fa = fc - fr;                         // neighbour index = 8(n-h) + e + fa
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        const uint32_t lane_base = tmem + ((uint32_t)(cw * 32) << 16);
         const float sc = gm.scale * kLog2e;
         const float mask2 = kMaskValue * kLog2e;
         // which of the thread's fragment slots are neighbours: slot (g, hh, e) is window offset 8 (g - hh) + e + fa, the same
@@ -396,15 +410,15 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
         const float inv_T = 1.f / (float)T, inv_H = 1.f / (float)gm.H;
         const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
         if (d_rpb)
-            for (int i = r; i < 4 * n_bias; i += 128) bias_acc[i] = 0.f;
+            for (int i = ct; i < NCW * n_bias; i += NCW * 32) bias_acc[i] = 0.f;
         if (rpb) {
             // bias table of every head, once per CTA (barrier among the 4 compute warps only)
-            for (int i = r; i < gm.H * kBiasRowB; i += 128) {
+            for (int i = ct; i < gm.H * kBiasRowB; i += NCW * 32) {
                 const int hh_ = i / kBiasRowB, kk = i - hh_ * kBiasRowB - kBiasPad;
                 bias_tab[i] = (kk >= 0 && kk < win && (kk & dmask) == 0) ? __ldg(rpb + hh_ * gm.win + (kk >> dshift)) * kLog2e : 0.f;
             }
         }
-        if (rpb || d_rpb) asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (rpb || d_rpb) asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
         int it = 0;
         // log-sum-exp of the four fragment rows of a tile; loaded one tile ahead so the DRAM latency is hidden
         tc::RowCursor cur = {};  // flat tiling: row tile * stride = g0 + right
@@ -421,7 +435,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
             for (int b = 0; b < 2; ++b)
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
-                    const int gq = g0_ + warp * 32 + 16 * b + 8 * hh + fr;
+                    const int gq = g0_ + cw * 32 + 16 * b + 8 * hh + fr;
                     dst[b][hh] = (tile_ < total_tiles && gq >= 0 && gq < rows_) ? __ldg(base_ + (size_t)gq * mul_) : 0.f;
                 }
         };
@@ -447,10 +461,10 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 bool live4[2][2];
                 {
                     int tq, hq, bq;
-                    cur.row_at(warp * 32 + fr - right, inv_T, inv_H, tq, hq, bq);
+                    cur.row_at(cw * 32 + fr - right, inv_T, inv_H, tq, hq, bq);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        const int gq = g0 + warp * 32 + fr + 8 * k;
+                        const int gq = g0 + cw * 32 + fr + 8 * k;
                         live4[k >> 1][k & 1] = gq >= 0 && gq < rows_total;
                         jb[k >> 1][k & 1] = tq - left + fa;
                         tc::row_step8(T, gm.H, tq, hq, bq);
@@ -463,7 +477,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     for (int g = 0; g < NG; ++g)
 #pragma unroll
                         for (int hh = 0; hh < 2; ++hh) {
-                            const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
+                            const int gq = g0 + cw * 32 + 16 * b + 8 * hh + fr;
                             const float* src = lse + (size_t)min(max(gq, 0), rows_total - 1) * gm.win;
                             float p[2];
 #pragma unroll
@@ -479,7 +493,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
 #pragma unroll
                 for (int b = 0; b < 2; ++b) {
-                    const uint32_t blk = (uint32_t)(4 * warp + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * warp + 2 * b) * 128u;
+                    const uint32_t blk = (uint32_t)(4 * cw + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * cw + 2 * b) * 128u;
                     tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p[b], lane);
                 }
                 ptx::fence_proxy_async_smem();
@@ -487,7 +501,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 ptx::mbar_arrive(&misc->p_ready);
                 cur.advance();
                 continue;
-            } else if constexpr (WB == 33) {
+            } else if constexpr (WB == 33 || NCW == 8) {
                 // Widest window bucket: the two 16-row blocks of the warp are processed one after the other in a ROLLED loop.
                 // 48 fragment values of S and of dP per block and thread: holding both blocks at once spilled registers, and
                 // the unrolled code of both did not fit the instruction cache (measured: 2-3x more cycles per tile).
@@ -495,7 +509,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 ptx::tc_fence_after_sync();
                 bool failed = false;
 #pragma unroll 1
-                for (int b = 0; b < 2; ++b) {
+                for (int b = (NCW == 8 ? bsel : 0); b < (NCW == 8 ? bsel + 1 : 2); ++b) {
                     // the two rows of this block this thread sees (row half hh): see the comments of the unrolled path below
                     float lse2[2];
                     int jb[2], vle[2], hrow[2];
@@ -503,11 +517,11 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     bool need_mask = false;
                     {
                         int tq = 0, hq = 0, bq = 0;
-                        if constexpr (SEG) { tq = g0 + warp * 32 + 16 * b + fr; hq = scur.h; }
-                        else cur.row_at(warp * 32 + 16 * b + fr - right, inv_T, inv_H, tq, hq, bq);
+                        if constexpr (SEG) { tq = g0 + cw * 32 + 16 * b + fr; hq = scur.h; }
+                        else cur.row_at(cw * 32 + 16 * b + fr - right, inv_T, inv_H, tq, hq, bq);
 #pragma unroll
                         for (int hh = 0; hh < 2; ++hh) {
-                            const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
+                            const int gq = g0 + cw * 32 + 16 * b + 8 * hh + fr;
                             const bool live = gq >= 0 && gq < (SEG ? Trow : rows_total);
                             const int vlr = !live ? 0 : SEG ? vl_seq : valid_len ? min(T, __ldg(valid_len + min(max(bq, 0), batch - 1))) : T;
                             hrow[hh] = hq;
@@ -521,11 +535,11 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     }
                     need_mask = __any_sync(0xffffffffu, need_mask);
                     float s1[4 * NG], d1[4 * NG];
-                    const uint32_t a = lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b);
+                    const uint32_t a = lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(cw * 32 + 16 * b);
                     tc::ld_frag<NG>(a, s1);
                     tc::ld_frag<NG>(a + kColDP, d1);
                     ptx::tmem_ld_wait();
-                    if (b == 1) {  // S and dP of this tile are out of tensor memory
+                    if (b == 1 || NCW == 8) {  // S and dP of this tile (this warp's share of them) are out of tensor memory
                         ptx::tc_fence_before_sync();
                         ptx::mbar_arrive(&misc->s_free);
                     }
@@ -563,7 +577,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     if (need_mask) elements(std::true_type{}); else elements(std::false_type{});
                     delta[0] = tc::quad_sum(delta[0]);
                     delta[1] = tc::quad_sum(delta[1]);
-                    if (b == 0) {
+                    if (b == 0 || NCW == 8) {
                         // batch 2 of the previous tile must have finished reading the operand matrices before they are rewritten
                         if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { failed = true; break; }
                         if (d_rpb && it > 0)
@@ -583,7 +597,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             if (need_mask) {
                                 const int kc = 8 * (g - hh), kk0 = kc + fa;
                                 const int j0 = jb[hh] + kc;
-                                const int row = warp * 32 + 16 * b + 8 * hh + fr;
+                                const int row = cw * 32 + 16 * b + 8 * hh + fr;
                                 const bool own = d_rpb && row >= right && row < kTileM - left;
                                 const bool out0 = (unsigned)j0 >= (unsigned)Trow, out1 = (unsigned)(j0 + 1) >= (unsigned)Trow;
                                 if (out0 | out1) {
@@ -600,7 +614,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             }
                             pk_p[2 * g + hh] = Cvt<E>::pack2(p0, p1);
                         }
-                    const uint32_t blk = (uint32_t)(4 * warp + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * warp + 2 * b) * 128u;
+                    const uint32_t blk = (uint32_t)(4 * cw + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * cw + 2 * b) * 128u;
                     tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d, lane);
                     tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
                 }
@@ -617,11 +631,11 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 bool need_mask = false;
                 {
                     int tq = 0, hq = 0, bq = 0;
-                    if constexpr (SEG) { tq = g0 + warp * 32 + fr; hq = scur.h; }
-                    else cur.row_at(warp * 32 + fr - right, inv_T, inv_H, tq, hq, bq);
+                    if constexpr (SEG) { tq = g0 + cw * 32 + fr; hq = scur.h; }
+                    else cur.row_at(cw * 32 + fr - right, inv_T, inv_H, tq, hq, bq);
     #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        const int gq = g0 + warp * 32 + fr + 8 * k;
+                        const int gq = g0 + cw * 32 + fr + 8 * k;
                         const bool live = gq >= 0 && gq < (SEG ? Trow : rows_total);
                         const int vlr = !live ? 0 : SEG ? vl_seq : valid_len ? min(T, __ldg(valid_len + min(max(bq, 0), batch - 1))) : T;
                         hrow[k >> 1][k & 1] = hq;
@@ -641,7 +655,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 float s[2][4 * NG], d[2][4 * NG];
     #pragma unroll
                 for (int b = 0; b < 2; ++b) {
-                    const uint32_t a = lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b);
+                    const uint32_t a = lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(cw * 32 + 16 * b);
                     tc::ld_frag<NG>(a, s[b]);
                     tc::ld_frag<NG>(a + kColDP, d[b]);
                 }
@@ -711,7 +725,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                 // bias gradient, but it must not reach the other sequence's dK/dV nor this query's dQ
                                 const int kc = 8 * (g - hh), kk0 = kc + fa;
                                 const int j0 = jb[b][hh] + kc;
-                                const int row = warp * 32 + 16 * b + 8 * hh + fr;
+                                const int row = cw * 32 + 16 * b + 8 * hh + fr;
                                 const bool own = d_rpb && row >= right && row < kTileM - left;
                                 const bool out0 = (unsigned)j0 >= (unsigned)Trow, out1 = (unsigned)(j0 + 1) >= (unsigned)Trow;
                                 if (out0 | out1) {
@@ -729,7 +743,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             pk_p[2 * g + hh] = Cvt<E>::pack2(p0, p1);
                         }
                     // core matrix of the block's first row / first column: row group 4w+2b, column group 4w+2b
-                    const uint32_t blk = (uint32_t)(4 * warp + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * warp + 2 * b) * 128u;
+                    const uint32_t blk = (uint32_t)(4 * cw + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * cw + 2 * b) * 128u;
                     tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d, lane);
                     tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
                 }
@@ -741,7 +755,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 // head of the row this lane will read back (-1: a row this tile does not own)
                 const int gr = g0 + r;
                 prev_hr = -1;
-                if (r >= right && r < kTileM - left && gr >= 0 && gr < (SEG ? Trow : rows_total)) {
+                if ((NCW == 4 || lane < 16) && r >= right && r < kTileM - left && gr >= 0 && gr < (SEG ? Trow : rows_total)) {
                     if constexpr (SEG) prev_hr = scur.h;
                     else {
                         int tr, br;
@@ -762,15 +776,17 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
             ptx::mbar_arrive(&misc->acc_done);
             if (warp == 0 && ptx::mbar_wait(&misc->acc_done, 0)) {
                 for (int i = lane; i < n_bias; i += 32) {
-                    const float x = (bias_acc[i] + bias_acc[n_bias + i]) + (bias_acc[2 * n_bias + i] + bias_acc[3 * n_bias + i]);
+                    float x = (bias_acc[i] + bias_acc[n_bias + i]) + (bias_acc[2 * n_bias + i] + bias_acc[3 * n_bias + i]);
+                    if constexpr (NCW == 8)
+                        x += (bias_acc[4 * n_bias + i] + bias_acc[5 * n_bias + i]) + (bias_acc[6 * n_bias + i] + bias_acc[7 * n_bias + i]);
                     if (drpb_direct) { if (x != 0.f) atomicAdd(d_rpb + i, x); }
                     else d_rpb[(size_t)blockIdx.x * n_bias + i] = x;
                 }
             }
         }
-    } else if (warp < 8) {
-        // ------------------------------------------------------------ epilogue warps (TMEM lanes 32(warp-4)..)
-        const int ew = warp - 4;
+    } else if (warp < NCW + 4) {
+        // ------------------------------------------------------------ epilogue warps (TMEM lanes 32 (warp - NCW) ..)
+        const int ew = warp - NCW;
         const int r = ew * 32 + lane;  // accumulator row m
         const uint32_t lane_base = tmem + ((uint32_t)(ew * 32) << 16);
         constexpr int CH = C / 8;
@@ -824,7 +840,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 if (L.out_bufs == 3) {
                     // one buffer per output: wait (only now) until the previous tile's stores have read them, stage all three,
                     // issue the three stores together
-                    if (tid == 128) ptx::tma_store_wait_read();
+                    if (tid == kEpiTid) ptx::tma_store_wait_read();
                     asm volatile("bar.sync 2, 128;" ::: "memory");
                     constexpr int kOutBuf = round_up(kTileM * C * 2, 1024);
 #pragma unroll
@@ -840,7 +856,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     }
                     ptx::fence_proxy_async_smem();
                     asm volatile("bar.sync 2, 128;" ::: "memory");
-                    if (tid == 128) {
+                    if (tid == kEpiTid) {
 #pragma unroll
                         for (int which = 0; which < 3; ++which) {
                             if (MODE == kBandT && which != 1) continue;
@@ -863,7 +879,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     }
                     ptx::fence_proxy_async_smem();
                     asm volatile("bar.sync 2, 128;" ::: "memory");
-                    if (tid == 128) {
+                    if (tid == kEpiTid) {
                         store_rows(which == 0 ? tm.dq : which == 1 ? tm.dv : tm.dk, buf, out_row);
                         ptx::tma_store_commit();
                         ptx::tma_store_wait_read();
@@ -889,7 +905,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 stage_rows(st + L.stage_k, acc, win - 1);
                 ptx::fence_proxy_async_smem();
                 asm volatile("bar.sync 2, 128;" ::: "memory");
-                if (tid == 128) {
+                if (tid == kEpiTid) {
                     store_rows(tm.dq, st + L.stage_q, out_row);
                     store_rows(tm.dk, st + L.stage_do, out_row);
                     store_rows(tm.dv, st + L.stage_k, out_row);
@@ -903,7 +919,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
             }
             if constexpr (SEG) ocur.advance();
         }
-        if (tid == 128) ptx::tma_store_wait_all();
+        if (tid == kEpiTid) ptx::tma_store_wait_all();
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
@@ -946,7 +962,7 @@ cudaError_t launch_bwd(const BwdMaps<SEG ? 2 : 1>& maps, float* d_rpb, float* sc
     const int grid = total < sm_count ? total : sm_count;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(bwd_threads(compute_warps(C, MODE)));
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
