@@ -68,6 +68,15 @@ __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fe
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ------------------------------------------------------------------ register budget per warp group
+// Four consecutive warps (a warp group) hand registers back to the CTA's pool or take more from it; every warp of the group
+// executes the same instruction, converged. R: registers per thread afterwards, a multiple of 8. The increase blocks until the
+// pool holds enough, so the groups that shrink must do so unconditionally.
+template <int R>
+__device__ __forceinline__ void warpgroup_regs_grow() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R)); }
+template <int R>
+__device__ __forceinline__ void warpgroup_regs_shrink() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(R)); }
+
 // ------------------------------------------------------------------ TMA (tiled, 3-D tensors (C, T, N))
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
     asm volatile(

@@ -199,6 +199,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
     constexpr int NS = bwd_stages(C);         // ring depth: tile `it` uses stage it % NS in ring round it / NS
     constexpr int NCW = compute_warps(C, MODE);
     constexpr int kThreads = bwd_threads(NCW), kProducerWarp = NCW + 4, kMmaWarp = NCW + 5, kEpiTid = NCW * 32;
+    constexpr int kRegsCompute = 176, kRegsEpilogue = 104, kRegsIssue = 56;   // per thread, after the warp groups rebalance
     constexpr int kRowBytes = C * 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -295,6 +296,12 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
 
+    // 512 threads (NCW = 8) leave 128 registers each, which the compute warps' 16-row block does not fit in (spills in the
+    // tile loop); the epilogue, producer and issuer warps need far fewer. Warp groups 0-1 (compute) take what groups 2
+    // (epilogue) and 3 (producer, issuers) give back, each at the head of its own branch
+    // (the register allocator then treats every branch with its own budget): 2 x 176 + 104 + 56 = 4 x 128.
+    if (warp >= NCW + 4) {
+    if constexpr (NCW == 8) ptx::warpgroup_regs_shrink<kRegsIssue>();
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -386,7 +393,9 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
             }
             if (!ok) { atomicExch(&g_tc_bwd_status, 12); *abort_flag = 1; }
         }
+    }
     } else if (warp < NCW) {
+        if constexpr (NCW == 8) ptx::warpgroup_regs_grow<kRegsCompute>();
         // ------------------------------------------------------------ compute warps
         const int cw = warp & 3;                        // quarter of the tensor-memory lanes (and tile rows) this warp works on
         const int bsel = warp >> 2;                     // NCW = 8: the 16-row block of that quarter this warp takes
@@ -784,8 +793,9 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 }
             }
         }
-    } else if (warp < NCW + 4) {
+    } else {
         // ------------------------------------------------------------ epilogue warps (TMEM lanes 32 (warp - NCW) ..)
+        if constexpr (NCW == 8) ptx::warpgroup_regs_shrink<kRegsEpilogue>();
         const int ew = warp - NCW;
         const int r = ew * 32 + lane;  // accumulator row m
         const uint32_t lane_base = tmem + ((uint32_t)(ew * 32) << 16);
