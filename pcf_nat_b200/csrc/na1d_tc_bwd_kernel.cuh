@@ -586,13 +586,6 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     if (need_mask) elements(std::true_type{}); else elements(std::false_type{});
                     delta[0] = tc::quad_sum(delta[0]);
                     delta[1] = tc::quad_sum(delta[1]);
-                    if (b == 0 || NCW == 8) {
-                        // batch 2 of the previous tile must have finished reading the operand matrices before they are rewritten
-                        if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { failed = true; break; }
-                        if (d_rpb && it > 0)
-                            bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask,
-                                                      dshift, 1.f / gm.scale, bias_acc + warp * n_bias);
-                    }
                     uint32_t pk_p[2 * NG], pk_d[2 * NG];
 #pragma unroll
                     for (int g = 0; g < NG; ++g)
@@ -623,6 +616,15 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             }
                             pk_p[2 * g + hh] = Cvt<E>::pack2(p0, p1);
                         }
+                    if (b == 0 || NCW == 8) {
+                        // Only the stores need the operand matrices: batch 2 of the previous tile must have finished reading
+                        // them (everything above overlaps with it). The previous tile's bias gradient is read back from its
+                        // dS operand first.
+                        if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { failed = true; break; }
+                        if (d_rpb && it > 0)
+                            bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask,
+                                                      dshift, 1.f / gm.scale, bias_acc + warp * n_bias);
+                    }
                     const uint32_t blk = (uint32_t)(4 * cw + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * cw + 2 * b) * 128u;
                     tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d, lane);
                     tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
@@ -710,22 +712,15 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 for (int b = 0; b < 2; ++b)
     #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) delta[b][hh] = tc::quad_sum(delta[b][hh]);
-                // batch 2 of the previous tile must have finished reading the operand matrices before they are rewritten
-                if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
-                // Bias gradient of the PREVIOUS tile, read back from its dS operand now: while batch 2 runs its operand fetches own
-                // the shared-memory bandwidth and the same read-back took thousands of cycles; here the tensor pipe is done with it.
-                if (d_rpb && it > 0)
-                    bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask, dshift,
-                                              1.f / gm.scale, bias_acc + warp * n_bias);
+                uint32_t pk_p[2][2 * NG], pk_d[2][2 * NG];
     #pragma unroll
                 for (int b = 0; b < 2; ++b) {
-                    uint32_t pk_p[2 * NG], pk_d[2 * NG];
     #pragma unroll
                     for (int g = 0; g < NG; ++g)
     #pragma unroll
                         for (int hh = 0; hh < 2; ++hh) {
                             const int idx = 4 * g + 2 * hh;
-                            if (tc::dead_slot(g, hh, NG)) { pk_d[2 * g + hh] = 0u; pk_p[2 * g + hh] = 0u; continue; }
+                            if (tc::dead_slot(g, hh, NG)) { pk_d[b][2 * g + hh] = 0u; pk_p[b][2 * g + hh] = 0u; continue; }
                             float ds0 = s[b][idx] * (d[b][idx] - delta[b][hh]);
                             float ds1 = s[b][idx + 1] * (d[b][idx + 1] - delta[b][hh]);
                             float p0 = s[b][idx], p1 = s[b][idx + 1];
@@ -743,18 +738,29 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                     if (out1) { ds1 = 0.f; p1 = 0.f; }
                                 }
                             }
-                            pk_d[2 * g + hh] = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
+                            pk_d[b][2 * g + hh] = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
                             if constexpr (DROP) {
                                 const int off = 8 * (g - hh) + fa;
                                 p0 = drop_hash(drow[b][hh], (uint32_t)(off >> dshift), drop.seed) >= drop.threshold ? p0 * drop.scale : 0.f;
                                 p1 = drop_hash(drow[b][hh], (uint32_t)((off + 1) >> dshift), drop.seed) >= drop.threshold ? p1 * drop.scale : 0.f;
                             }
-                            pk_p[2 * g + hh] = Cvt<E>::pack2(p0, p1);
+                            pk_p[b][2 * g + hh] = Cvt<E>::pack2(p0, p1);
                         }
+                }
+                // Only the stores need the operand matrices: batch 2 of the previous tile must have finished reading them
+                // (everything above overlaps with it).
+                if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
+                // Bias gradient of the PREVIOUS tile, read back from its dS operand now: while batch 2 runs its operand fetches own
+                // the shared-memory bandwidth and the same read-back took thousands of cycles; here the tensor pipe is done with it.
+                if (d_rpb && it > 0)
+                    bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask, dshift,
+                                              1.f / gm.scale, bias_acc + warp * n_bias);
+    #pragma unroll
+                for (int b = 0; b < 2; ++b) {
                     // core matrix of the block's first row / first column: row group 4w+2b, column group 4w+2b
                     const uint32_t blk = (uint32_t)(4 * cw + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * cw + 2 * b) * 128u;
-                    tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d, lane);
-                    tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
+                    tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d[b], lane);
+                    tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p[b], lane);
                 }
             }
             ptx::fence_proxy_async_smem();
