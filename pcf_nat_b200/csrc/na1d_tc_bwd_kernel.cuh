@@ -314,41 +314,43 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
         // ------------------------------------------------------------ MMA issuers
         // One tcgen05.mma costs its issuing thread about 120 cycles whatever its size (measured), far more than the
         // tensor pipe needs for these small shapes, but issuers in different warps overlap. Three warps therefore issue
-        // the MMAs of the three independent accumulator chains:  role 0: S and dQ,  role 1: dP and dV,  role 2: dK.
+        // the MMAs of the three independent accumulator chains:  role 0: dQ (the longest chain),  role 1: dP and dV,
+        // role 2: S and dK.
         const int role = warp - kMmaWarp;
         if (lane == 0) {
             const uint32_t idesc_s = ptx::instr_desc(Fmt<E>::v, 0, 0, kTileM, (uint32_t)KT);
             const uint32_t idesc_dq = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);   // A K-major, B MN-major
             const uint32_t idesc_dkv = ptx::instr_desc(Fmt<E>::v, 1, 1, kTileM, (uint32_t)C);  // A MN-major, B MN-major
             const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
-            const int nks = KT / 16;
-            // this role's part of batch 1 of tile `jt`: S = Q.K^T -> cols [0,KT) (role 0), dP = dO.V^T -> cols [160,160+KT) (role 1)
+            // key chunks of dQ = dS.K: the rows this tile owns end at 128 - left, their neighbours at column 127 + right
+            const int nks = min(KT / 16, (kTileM + right + 15) / 16);
+            // this role's part of batch 1 of tile `jt`: S = Q.K^T -> cols [0,KT) (role 2), dP = dO.V^T -> cols [160,160+KT) (role 1)
             auto batch1_ready = [&](int jt) -> bool {  // non-blocking: have this role's two operands of tile jt landed?
                 const int s = jt % NS, k = jt / NS;
-                return ptx::mbar_try_wait(&misc->full[s][role == 0 ? kK : kV], k & 1) &&
-                       ptx::mbar_try_wait(&misc->full[s][role == 0 ? kQ : kDO], k & 1);
+                return ptx::mbar_try_wait(&misc->full[s][role == 2 ? kK : kV], k & 1) &&
+                       ptx::mbar_try_wait(&misc->full[s][role == 2 ? kQ : kDO], k & 1);
             };
             auto batch1 = [&](int jt) {
                 const int s = jt % NS;
                 const uint32_t st = ptx::smem_u32(smem + s * L.stage_bytes);
                 ptx::tc_fence_after_sync();
-                const uint64_t da0 = ptx::smem_desc(st + (role == 0 ? L.stage_q : L.stage_do), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                const uint64_t db0 = ptx::smem_desc(st + (role == 0 ? L.stage_k : L.stage_v), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
-                const uint32_t dcol = tmem + (role == 0 ? 0u : (uint32_t)kColDP);
+                const uint64_t da0 = ptx::smem_desc(st + (role == 2 ? L.stage_q : L.stage_do), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                const uint64_t db0 = ptx::smem_desc(st + (role == 2 ? L.stage_k : L.stage_v), 16, 8 * kRowBytes, RowSwizzle<C>::umma);
+                const uint32_t dcol = tmem + (role == 2 ? 0u : (uint32_t)kColDP);
 #pragma unroll
                 for (int ks = 0; ks < C / 16; ++ks)
                     ptx::mma_ss(dcol, tc::desc_advance(da0, ks * 32), tc::desc_advance(db0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
                 if (role == 1) ptx::mma_commit(&misc->empty[s][kV]);  // nothing else reads V
                 ptx::mma_commit(&misc->s_ready);
             };
-            // Two job streams per issuer: batch 1 of iteration j (roles 0 and 1; needs the compute warps to have read S/dP of
+            // Two job streams per issuer: batch 1 of iteration j (roles 1 and 2; needs the compute warps to have read S/dP of
             // iteration j-1 and the operands of tile j in shared memory) and batch 2 of iteration i (needs the compute warps'
             // operand matrices and the drained accumulator). Whichever is ready first is issued first, so a late TMA load never
             // holds back MMAs whose inputs are already there. Batch 1 runs at most one iteration ahead of batch 2.
             // band-transpose mode: no batch 1 at all, and only role 1 (the dV chain) has a batch 2
             const int n_it = (blockIdx.x < total_tiles && (MODE == kBwdFused || role == 1))
                                  ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-            int next_b1 = (role < 2 && MODE == kBwdFused) ? 0 : n_it, it = 0;
+            int next_b1 = (role > 0 && MODE == kBwdFused) ? 0 : n_it, it = 0;
             uint32_t polls = 0;
             bool ok = true;
             while (it < n_it) {
@@ -440,11 +442,12 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
             const int rows_ = SEG ? scur.rows(sg) : rows_total;
             const float* base_ = SEG ? lse + (size_t)(scur.b * gm.H + scur.h) * T + scur.r : lse;
             const int mul_ = SEG ? sg.d : 1;
+            // one block per warp (NCW = 8): only that block's two rows, kept in dst[0]
 #pragma unroll
-            for (int b = 0; b < 2; ++b)
+            for (int b = 0; b < (NCW == 8 ? 1 : 2); ++b)
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
-                    const int gq = g0_ + cw * 32 + 16 * b + 8 * hh + fr;
+                    const int gq = g0_ + cw * 32 + 16 * (NCW == 8 ? bsel : b) + 8 * hh + fr;
                     dst[b][hh] = (tile_ < total_tiles && gq >= 0 && gq < rows_) ? __ldg(base_ + (size_t)gq * mul_) : 0.f;
                 }
         };
@@ -514,17 +517,13 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 // Widest window bucket: the two 16-row blocks of the warp are processed one after the other in a ROLLED loop.
                 // 48 fragment values of S and of dP per block and thread: holding both blocks at once spilled registers, and
                 // the unrolled code of both did not fit the instruction cache (measured: 2-3x more cycles per tile).
-                if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 14); *abort_flag = 1; break; }
-                ptx::tc_fence_after_sync();
-                bool failed = false;
-#pragma unroll 1
-                for (int b = (NCW == 8 ? bsel : 0); b < (NCW == 8 ? bsel + 1 : 2); ++b) {
-                    // the two rows of this block this thread sees (row half hh): see the comments of the unrolled path below
-                    float lse2[2];
-                    int jb[2], vle[2], hrow[2];
-                    uint32_t drow[2] = {0u, 0u};   // dense row index n*T + t of the two rows (dropout mask key)
-                    bool need_mask = false;
-                    {
+                // the two rows of block b this thread sees (row half hh): see the comments of the unrolled path below
+                float lse2[2];
+                int jb[2], vle[2], hrow[2];
+                uint32_t drow[2] = {0u, 0u};   // dense row index n*T + t of the two rows (dropout mask key)
+                bool need_mask = false;
+                auto row_facts = [&](int b) {
+                        need_mask = false;
                         int tq = 0, hq = 0, bq = 0;
                         if constexpr (SEG) { tq = g0 + cw * 32 + 16 * b + fr; hq = scur.h; }
                         else cur.row_at(cw * 32 + 16 * b + fr - right, inv_T, inv_H, tq, hq, bq);
@@ -537,12 +536,20 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             jb[hh] = tq - left + fa;
                             vle[hh] = !live ? -1 : tq >= vlr ? 0 : vlr;
                             need_mask |= tq < left || tq + right >= vlr;
-                            lse2[hh] = (b ? lse_next[1][hh] : lse_next[0][hh]) * kLog2e;
+                            lse2[hh] = (NCW != 8 && b ? lse_next[1][hh] : lse_next[0][hh]) * kLog2e;
                             if constexpr (DROP) drow[hh] = SEG ? (uint32_t)((scur.b * gm.H + scur.h) * T + tq * sg.d + scur.r) : (uint32_t)gq;
                             if constexpr (SEG) tq += 8; else tc::row_step8(T, gm.H, tq, hq, bq);
                         }
-                    }
                     need_mask = __any_sync(0xffffffffu, need_mask);
+                };
+                // one block per warp: its row facts do not depend on S, so they are worked out while the S chain still runs
+                if constexpr (NCW == 8) row_facts(bsel);
+                if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_bwd_status, 14); *abort_flag = 1; break; }
+                ptx::tc_fence_after_sync();
+                bool failed = false;
+#pragma unroll 1
+                for (int b = (NCW == 8 ? bsel : 0); b < (NCW == 8 ? bsel + 1 : 2); ++b) {
+                    if constexpr (NCW != 8) row_facts(b);
                     float s1[4 * NG], d1[4 * NG];
                     const uint32_t a = lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(cw * 32 + 16 * b);
                     tc::ld_frag<NG>(a, s1);
