@@ -50,9 +50,19 @@ using tc::RowSwizzle;
 using tc::Fmt;
 constexpr int kThreads = 224;  // 4 softmax warps, producer/store warp, two MMA issuer warps
 constexpr int kTmemCols = 256;
-constexpr int kOCol = 192;   // O accumulator of the even key steps; S (fp32) and then P (16-bit pairs) use [0, KT), KT <= 160
-constexpr int kOColB = 96;   // O accumulator of the odd key steps: inside the S columns, which are dead once softmax has read
-                             // them (P only needs the packed columns [0, KT/2 <= 80))
+// Tensor-memory columns. P (16-bit pairs, KT/2 <= 80 columns) always starts at column 0. Two layouts:
+//   shared  : S (fp32, KT <= 160 columns) at [0, KT) under P; O of the even key steps at [192, 192+C), O of the odd key
+//             steps at [96, 96+C) inside the S columns (dead once softmax has read them). S overwrites the P area every
+//             tile, so every tile re-zeroes the part of P outside the band.
+//   separate: P at [0, KTmax/2), O (even) behind it, S at [256-KTmax, 256), O (odd) on the first S columns. Nothing but
+//             the band stores ever writes the P columns: they are zeroed once, and the band chunks of a row block are the
+//             same in every tile. Fits when KTmax/2 + C + KTmax <= 256 (16-channel rows; 32-channel rows below the
+//             widest window bucket).
+__host__ __device__ constexpr int kt_max(int WB) { return WB > 17 ? 160 : 144; }   // KT = round16(128 + win - 1)
+__host__ __device__ constexpr bool separate_p(int C, int WB) { return kt_max(WB) / 2 + C + kt_max(WB) <= kTmemCols; }
+__host__ __device__ constexpr int col_s(int C, int WB) { return separate_p(C, WB) ? kTmemCols - kt_max(WB) : 0; }
+__host__ __device__ constexpr int col_o(int C, int WB) { return separate_p(C, WB) ? kt_max(WB) / 2 : 192; }
+__host__ __device__ constexpr int col_ob(int C, int WB) { return separate_p(C, WB) ? col_s(C, WB) : 96; }
 constexpr int kBiasPad = 16;
 
 struct FwdSmemLayout {
@@ -105,6 +115,8 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
     static_assert(MODE == kFused || !SEG, "the unfused modes run on the flat tiling");
     constexpr int NG = tc::band_groups(WB);
     constexpr int kRowBytes = C * 2;
+    constexpr bool kSepP = separate_p(C, WB);
+    constexpr int kSCol = col_s(C, WB), kOCol = col_o(C, WB), kOColB = col_ob(C, WB);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const FwdSmemLayout L = fwd_layout(C, KT, rpb ? gm.H : 0);
@@ -238,7 +250,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     const uint64_t b0 = ptx::smem_desc(st + L.stage_k, 16, 8 * kRowBytes, RowSwizzle<C>::umma);
 #pragma unroll
                     for (int ks = 0; ks < C / 16; ++ks)
-                        ptx::mma_ss(tmem, tc::desc_advance(a0, ks * 32), tc::desc_advance(b0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
+                        ptx::mma_ss(tmem + kSCol, tc::desc_advance(a0, ks * 32), tc::desc_advance(b0, ks * 32), idesc_s, ks > 0 ? 1u : 0u);
                 }
                 if constexpr (MODE != kBandIn) {
                     ptx::mma_commit(&misc->empty_q);  // Q is read by nothing else
@@ -307,6 +319,14 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
+        if constexpr (kSepP && MODE != kBandOut) {
+            // P columns of this warp's lanes: zero once, only the band chunks are ever written again
+            const uint32_t zeros[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+                for (int ci = 0; ci < KT / 16; ++ci) tc::st_pack2(lane_base + ((uint32_t)(16 * b) << 16) + ci * 8, zeros);
+            ptx::tmem_st_wait();
+        }
         int it = 0;
         tc::RowCursor cur = {};
         tc::SegCursor scur = {};
@@ -360,7 +380,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 ptx::tc_fence_after_sync();
 #pragma unroll
                 for (int b = 0; b < 2; ++b)
-                    tc::ld_frag<NG>(lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(warp * 32 + 16 * b), s[b]);
+                    tc::ld_frag<NG>(lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(kSCol + warp * 32 + 16 * b), s[b]);
                 ptx::tmem_ld_wait();
             }
             if constexpr (MODE == kBandOut) {
@@ -479,8 +499,9 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                         sum[b][hh] = tc::fast_rcp(sum[b][hh]);
                     }
             }
-            // P over the S columns. Per 16-lane block the band occupies NGP 8-key groups starting at the block's own
-            // first row; every other 16-key chunk of the row range is zeroed. The two sets are disjoint, so one wait.
+            // P. Per 16-lane block the band occupies NGP 8-key groups starting at the block's own first row; every other
+            // 16-key chunk of the row range is zero: zeroed here when S shares the columns (the two sets are disjoint, so
+            // one wait), once at the start otherwise.
             {
                 constexpr int NGP = NG + (NG & 1);  // band groups padded to whole 16-key chunks
                 const uint32_t zeros[4] = {0, 0, 0, 0};
@@ -488,8 +509,9 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 for (int b = 0; b < 2; ++b) {
                     const uint32_t blk = lane_base + ((uint32_t)(16 * b) << 16);
                     const int c0 = 2 * warp + b;  // first band chunk (16 keys = 8 packed columns) of this block
-                    for (int ci = 0; ci < KT / 16; ++ci)
-                        if (ci < c0 || ci >= c0 + NGP / 2) tc::st_pack2(blk + ci * 8, zeros);
+                    if constexpr (!kSepP)
+                        for (int ci = 0; ci < KT / 16; ++ci)
+                            if (ci < c0 || ci >= c0 + NGP / 2) tc::st_pack2(blk + ci * 8, zeros);
                     uint32_t pk[2 * NGP];
 #pragma unroll
                     for (int g = 0; g < NGP; ++g)
