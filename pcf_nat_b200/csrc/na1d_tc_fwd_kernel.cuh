@@ -48,7 +48,12 @@ using tc::kTileM;
 using tc::round_up;
 using tc::RowSwizzle;
 using tc::Fmt;
-constexpr int kThreads = 224;  // 4 softmax warps, producer/store warp, two MMA issuer warps
+// Softmax warps per CTA: 4 (each takes the two 16-row blocks of its quarter of the tile) or, for rows of 16 and 32 channels
+// in the fused mode, 8 (warps w and w + 4 share tensor-memory lane quarter w & 3 and take one block each: these shapes are
+// bound by the softmax warps' per-row work, not by bytes). Behind them: producer/store warp, two MMA issuer warps, and with
+// 8 softmax warps one idle warp that completes the last warp group.
+__host__ __device__ constexpr int softmax_warps(int C, int mode) { return (C <= 32 && mode == 0) ? 8 : 4; }
+__host__ __device__ constexpr int fwd_threads(int nsw) { return nsw == 8 ? 384 : 224; }
 constexpr int kTmemCols = 256;
 // Tensor-memory columns. P (16-bit pairs, KT/2 <= 80 columns) always starts at column 0. Two layouts:
 //   shared  : S (fp32, KT <= 160 columns) at [0, KT) under P; O of the even key steps at [192, 192+C), O of the odd key
@@ -108,7 +113,7 @@ template <int NSETS> struct FwdMaps {
 constexpr int kFused = 0, kBandOut = 1, kBandIn = 2;
 
 template <typename E, int C, int WB, bool SEG, int MODE = kFused, bool DROP = false>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(fwd_threads(softmax_warps(C, MODE)), 2)
 tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict__ lse, float* __restrict__ band,
               const float* __restrict__ rpb, const int* __restrict__ valid_len, Geometry gm, SegGeom sg, int KT, int total_tiles,
               DropoutCfg drop) {
@@ -116,6 +121,10 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
     constexpr int NG = tc::band_groups(WB);
     constexpr int kRowBytes = C * 2;
     constexpr bool kSepP = separate_p(C, WB);
+    constexpr int NSW = softmax_warps(C, MODE), NB = NSW == 8 ? 1 : 2;   // softmax warps; 16-row blocks per warp
+    constexpr int kProducerWarp = NSW, kIssuerA = NSW + 1, kIssuerB = NSW + 2;
+    // registers per thread after the warp groups rebalance (NSW = 8: 384 threads, two CTAs per SM, 80 each at launch)
+    constexpr int kRegsSoftmax = 104, kRegsOther = 32;
     constexpr int kSCol = col_s(C, WB), kOCol = col_o(C, WB), kOColB = col_ob(C, WB);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -162,17 +171,17 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
         return true;
     };
     bool first_ok = true;
-    if (tid == 4 * 32) {
+    if (tid == kProducerWarp * 32) {
         // The producer thread sets up the barriers and requests the CTA's first tile at once: the loads are in flight
         // while the other warps allocate tensor memory and meet at the barrier below.
         for (int s = 0; s < 2; ++s) { ptx::mbar_init(&misc->full[s], 1); ptx::mbar_init(&misc->empty[s], 1); }
         ptx::mbar_init(&misc->full_q, 1);
         ptx::mbar_init(&misc->empty_q, 1);
         ptx::mbar_init(&misc->s_ready, 1);
-        ptx::mbar_init(&misc->p_ready, 128);
+        ptx::mbar_init(&misc->p_ready, NSW * 32);
         ptx::mbar_init(&misc->o_ready, 2);  // one commit per MMA issuer
-        ptx::mbar_init(&misc->o_free, 128);
-        ptx::mbar_init(&misc->o_staged, 128);
+        ptx::mbar_init(&misc->o_free, NSW * 32);
+        ptx::mbar_init(&misc->o_staged, NSW * 32);
         misc->abort = 0;
         ptx::fence_mbar_init();
         for (int i = 0; i < (SEG ? 2 : 1); ++i) {
@@ -200,7 +209,9 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
 
-    if (warp == 4) {
+    if (warp >= NSW) {
+    if constexpr (NSW == 8) ptx::warpgroup_regs_shrink<kRegsOther>();
+    if (warp == kProducerWarp) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             int it = 1;
@@ -229,7 +240,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
             }
             ptx::tma_store_wait_all();
         }
-    } else if (warp == 5) {
+    } else if (warp == kIssuerA) {
         // ------------------------------------------------------------ MMA issuer A: S, and the even key steps of P.V
         if (lane == 0) {
             const uint32_t idesc_s = ptx::instr_desc(Fmt<E>::v, 0, 0, kTileM, (uint32_t)KT);
@@ -271,7 +282,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 ptx::mma_commit(&misc->o_ready);
             }
         }
-    } else if (warp == 6) {
+    } else if (warp == kIssuerB) {
         // ------------------------------------------------------------ MMA issuer B: the odd key steps of P.V
         if (lane == 0 && MODE != kBandOut) {
             const uint32_t idesc_o = ptx::instr_desc(Fmt<E>::v, 0, 1, kTileM, (uint32_t)C);
@@ -291,12 +302,17 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 ptx::mma_commit(&misc->o_ready);
             }
         }
+    }
     } else {
         // ------------------------------------------------------------ softmax / epilogue warps
-        const int r = warp * 32 + lane;
+        if constexpr (NSW == 8) ptx::warpgroup_regs_grow<kRegsSoftmax>();
+        const int cw = warp & 3;                          // quarter of the tensor-memory lanes (and tile rows)
+        const int bo = NSW == 8 ? warp >> 2 : 0;          // first 16-row block of that quarter this warp takes
+        const int rb = cw * 32 + 16 * bo;                 // tile row of that block
+        const int r = cw * 32 + lane;                     // accumulator row this lane drains in the epilogue
         const int fr = lane >> 2, fc = 2 * (lane & 3);
         const int fa = fc - fr;
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        const uint32_t lane_base = tmem + ((uint32_t)(cw * 32) << 16);
         const float sc = gm.scale * kLog2e;
         const float mask2 = kMaskValue * kLog2e;
         // which of the thread's fragment slots are neighbours: slot (g, hh, e) is window offset 8 (g - hh) + e + fa, the same
@@ -312,19 +328,19 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
             // bias table of every head, once per CTA (barrier among the 4 softmax warps only)
             // two copies, the second shifted by one entry: a thread reads the biases of its two adjacent columns with one
             // 8-byte load whatever the parity of its first offset
-            for (int i = r; i < 2 * gm.H * kBiasRow; i += 128) {
+            for (int i = tid; i < 2 * gm.H * kBiasRow; i += NSW * 32) {
                 const int copy = i / (gm.H * kBiasRow), j = i - copy * gm.H * kBiasRow;
                 const int hh_ = j / kBiasRow, kk = j - hh_ * kBiasRow - kBiasPad + copy;
                 bias_tab[i] = (kk >= 0 && kk < win && (kk & dmask) == 0) ? __ldg(rpb + hh_ * gm.win + (kk >> dshift)) * kLog2e : 0.f;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(NSW * 32) : "memory");
         }
         if constexpr (kSepP && MODE != kBandOut) {
             // P columns of this warp's lanes: zero once, only the band chunks are ever written again
             const uint32_t zeros[4] = {0, 0, 0, 0};
 #pragma unroll
-            for (int b = 0; b < 2; ++b)
-                for (int ci = 0; ci < KT / 16; ++ci) tc::st_pack2(lane_base + ((uint32_t)(16 * b) << 16) + ci * 8, zeros);
+            for (int b = 0; b < NB; ++b)
+                for (int ci = 0; ci < KT / 16; ++ci) tc::st_pack2(lane_base + ((uint32_t)(16 * (bo + b)) << 16) + ci * 8, zeros);
             ptx::tmem_st_wait();
         }
         int it = 0;
@@ -350,8 +366,8 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 const int vl = valid_len ? min(T, __ldg(valid_len + scur.b)) : T;
                 const int vl_seq = vl > scur.r ? (vl - scur.r + sg.d - 1) / sg.d : 0;
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int tq = scur.i * kTileM + warp * 32 + fr + 8 * k;
+                for (int k = 0; k < 2 * NB; ++k) {
+                    const int tq = scur.i * kTileM + rb + fr + 8 * k;
                     const int vlr = tq < Trow ? vl_seq : 0;
                     brow[k >> 1][k & 1] = bias_tab + ((fa & 1) ? gm.H * kBiasRow - 1 : 0) + scur.h * kBiasRow + kBiasPad + fa;
                     jb[k >> 1][k & 1] = tq - left + fa;
@@ -360,10 +376,10 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 }
             } else {
                 int tq, hq, bq;
-                cur.row_at(warp * 32 + fr, inv_T, inv_H, tq, hq, bq);
+                cur.row_at(rb + fr, inv_T, inv_H, tq, hq, bq);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const bool live = g0 + warp * 32 + fr + 8 * k < rows_total;
+                for (int k = 0; k < 2 * NB; ++k) {
+                    const bool live = g0 + rb + fr + 8 * k < rows_total;
                     const int vlr = !live ? 0 : valid_len ? min(T, __ldg(valid_len + min(bq, batch - 1))) : T;
                     brow[k >> 1][k & 1] = bias_tab + ((fa & 1) ? gm.H * kBiasRow - 1 : 0) + hq * kBiasRow + kBiasPad + fa;
                     jb[k >> 1][k & 1] = tq - left + fa;
@@ -379,8 +395,8 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 if (!ptx::mbar_wait(&misc->s_ready, it & 1) || *abort_flag) { atomicExch(&g_tc_status, 4); *abort_flag = 1; break; }
                 ptx::tc_fence_after_sync();
 #pragma unroll
-                for (int b = 0; b < 2; ++b)
-                    tc::ld_frag<NG>(lane_base + ((uint32_t)(16 * b) << 16) + (uint32_t)(kSCol + warp * 32 + 16 * b), s[b]);
+                for (int b = 0; b < NB; ++b)
+                    tc::ld_frag<NG>(lane_base + ((uint32_t)(16 * (bo + b)) << 16) + (uint32_t)(kSCol + rb + 16 * b), s[b]);
                 ptx::tmem_ld_wait();
             }
             if constexpr (MODE == kBandOut) {
@@ -389,10 +405,10 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 ptx::tc_fence_before_sync();
                 ptx::mbar_arrive(&misc->o_free);
 #pragma unroll
-                for (int b = 0; b < 2; ++b)
+                for (int b = 0; b < NB; ++b)
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) {
-                        const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
+                        const int gq = g0 + rb + 16 * b + 8 * hh + fr;
                         if (gq >= rows_total) continue;
                         float* dst = band + (size_t)gq * gm.win;
 #pragma unroll
@@ -412,10 +428,10 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 // the probabilities come from the fp32 band tensor instead of a softmax: slot (g, hh, e) of row (b, hh) is
                 // band[row, kk]; 0 outside the band, for rows past the tensor and for keys outside the row's own sequence
 #pragma unroll
-                for (int b = 0; b < 2; ++b)
+                for (int b = 0; b < NB; ++b)
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) {
-                        const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
+                        const int gq = g0 + rb + 16 * b + 8 * hh + fr;
                         const float* src = band + (size_t)min(gq, rows_total - 1) * gm.win;
 #pragma unroll
                         for (int g = 0; g < NG; ++g)
@@ -436,7 +452,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 auto logits = [&](auto masked_tag) {
                     constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
-                    for (int b = 0; b < 2; ++b)
+                    for (int b = 0; b < NB; ++b)
 #pragma unroll
                         for (int g = 0; g < NG; ++g)
 #pragma unroll
@@ -464,11 +480,11 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 };
                 if (need_mask) logits(std::true_type{}); else logits(std::false_type{});
 #pragma unroll
-                for (int b = 0; b < 2; ++b)
+                for (int b = 0; b < NB; ++b)
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) mx[b][hh] = tc::quad_max(mx[b][hh]);
 #pragma unroll
-                for (int b = 0; b < 2; ++b)
+                for (int b = 0; b < NB; ++b)
 #pragma unroll
                     for (int g = 0; g < NG; ++g)
 #pragma unroll
@@ -482,17 +498,17 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                 sum[b][hh] += p;
                             }
 #pragma unroll
-                for (int b = 0; b < 2; ++b)
+                for (int b = 0; b < NB; ++b)
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) {
                         sum[b][hh] = tc::quad_sum(sum[b][hh]);
                         if (lse && (lane & 3) == 0) {
                             const float val = (mx[b][hh] + tc::fast_log2(sum[b][hh])) * kLn2;
                             if constexpr (SEG) {
-                                const int tq = scur.i * kTileM + warp * 32 + 16 * b + 8 * hh + fr;
+                                const int tq = scur.i * kTileM + rb + 16 * b + 8 * hh + fr;
                                 if (tq < Trow) lse[(size_t)(scur.b * gm.H + scur.h) * T + (size_t)tq * sg.d + scur.r] = val;
                             } else {
-                                const int gq = g0 + warp * 32 + 16 * b + 8 * hh + fr;
+                                const int gq = g0 + rb + 16 * b + 8 * hh + fr;
                                 if (gq < rows_total) lse[gq] = val;
                             }
                         }
@@ -506,9 +522,9 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 constexpr int NGP = NG + (NG & 1);  // band groups padded to whole 16-key chunks
                 const uint32_t zeros[4] = {0, 0, 0, 0};
 #pragma unroll
-                for (int b = 0; b < 2; ++b) {
-                    const uint32_t blk = lane_base + ((uint32_t)(16 * b) << 16);
-                    const int c0 = 2 * warp + b;  // first band chunk (16 keys = 8 packed columns) of this block
+                for (int b = 0; b < NB; ++b) {
+                    const uint32_t blk = lane_base + ((uint32_t)(16 * (bo + b)) << 16);
+                    const int c0 = 2 * cw + bo + b;  // first band chunk (16 keys = 8 packed columns) of this block
                     if constexpr (!kSepP)
                         for (int ci = 0; ci < KT / 16; ++ci)
                             if (ci < c0 || ci >= c0 + NGP / 2) tc::st_pack2(blk + ci * 8, zeros);
@@ -529,8 +545,8 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             if constexpr (DROP) {
                                 // attention dropout on the normalised probabilities; the row's log-sum-exp is not affected
                                 const int off = 8 * (g - hh) + fa;
-                                const uint32_t row = SEG ? (uint32_t)((scur.b * gm.H + scur.h) * T + (scur.i * kTileM + warp * 32 + 16 * b + 8 * hh + fr) * sg.d + scur.r)
-                                                         : (uint32_t)(g0 + warp * 32 + 16 * b + 8 * hh + fr);
+                                const uint32_t row = SEG ? (uint32_t)((scur.b * gm.H + scur.h) * T + (scur.i * kTileM + rb + 16 * b + 8 * hh + fr) * sg.d + scur.r)
+                                                         : (uint32_t)(g0 + rb + 16 * b + 8 * hh + fr);
                                 p0 = drop_hash(row, (uint32_t)(off >> dshift), drop.seed) >= drop.threshold ? p0 * drop.scale : 0.f;
                                 p1 = drop_hash(row, (uint32_t)((off + 1) >> dshift), drop.seed) >= drop.threshold ? p1 * drop.scale : 0.f;
                             }
@@ -550,9 +566,11 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 uint8_t* sO = smem + L.ring + (it & 1) * L.stage_bytes + L.stage_v;  // this tile's V buffer: P.V has retired
                 // row r, 16-byte chunk c at r*rowbytes + ((c ^ swz(r)) * 16): the TMA swizzle of this row size
                 const int swz = (C == 64) ? (r & 7) : (C == 32) ? ((r >> 1) & 3) : ((r >> 2) & 1);
-                constexpr int HALF = C >= 32 ? C / 2 : C;  // columns per round (two rounds keep the register count down)
+                // columns per round: two rounds keep the register count down; with 8 softmax warps the two warps of a lane
+                // quarter take one half of the columns each
+                constexpr int HALF = (NSW == 8 || C >= 32) ? C / 2 : C;
 #pragma unroll
-                for (int c0 = 0; c0 < C; c0 += HALF) {
+                for (int c0 = (NSW == 8 ? bo * HALF : 0); c0 < (NSW == 8 ? (bo + 1) * HALF : C); c0 += HALF) {
                     float acc[HALF], accb[HALF];
 #pragma unroll
                     for (int c = 0; c < HALF; c += 8) {
@@ -560,7 +578,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                         ptx::tmem_ld8(lane_base + kOColB + c0 + c, &accb[c]);
                     }
                     ptx::tmem_ld_wait();
-                    if (c0 + HALF >= C) {
+                    if (NSW == 8 || c0 + HALF >= C) {
                         ptx::tc_fence_before_sync();
                         ptx::mbar_arrive(&misc->o_free);
                     }
@@ -597,7 +615,7 @@ cudaError_t launch_fwd(const FwdMaps<SEG ? 2 : 1>& maps, float* lse, float* band
     const int grid = total < slots ? total : slots;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3((unsigned)fwd_threads(softmax_warps(C, MODE)));
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
