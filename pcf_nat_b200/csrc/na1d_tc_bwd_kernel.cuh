@@ -436,11 +436,11 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
         tc::SegCursor scur = {};  // segmented tiling: the tile's residue sequence and its index in it
         if constexpr (SEG) scur.init((int)blockIdx.x, (int)gridDim.x, sg, gm.H);
         else cur.init(blockIdx.x * stride, T, gm.H, gridDim.x * stride);
-        // fetches the log-sum-exp of tile `tile_`; in the segmented tiling `scur` must stand on that tile
-        auto load_lse = [&](int tile_, float (&dst)[2][2]) {
-            const int g0_ = (SEG ? scur.i : tile_) * stride - right;
-            const int rows_ = SEG ? scur.rows(sg) : rows_total;
-            const float* base_ = SEG ? lse + (size_t)(scur.b * gm.H + scur.h) * T + scur.r : lse;
+        // fetches the log-sum-exp of tile `tile_`; in the segmented tiling `at` must stand on that tile
+        auto load_lse = [&](int tile_, const tc::SegCursor& at, float (&dst)[2][2]) {
+            const int g0_ = (SEG ? at.i : tile_) * stride - right;
+            const int rows_ = SEG ? at.rows(sg) : rows_total;
+            const float* base_ = SEG ? lse + (size_t)(at.b * gm.H + at.h) * T + at.r : lse;
             const int mul_ = SEG ? sg.d : 1;
             // one block per warp (NCW = 8): only that block's two rows, kept in dst[0]
 #pragma unroll
@@ -452,10 +452,21 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 }
         };
         float lse_next[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-        if constexpr (MODE == kBwdFused) load_lse(blockIdx.x, lse_next);
+        if constexpr (MODE == kBwdFused) load_lse(blockIdx.x, scur, lse_next);
         int prev_hr = -1;
         const int batch = gm.N / gm.H;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+            // This tile's log-sum-exp was requested one tile ago; the next tile's is requested now, at the top, so that its
+            // DRAM latency is over long before the values are used (requested at the end of the tile they stalled the
+            // row facts of the next one for most of that latency).
+            float lse_cur[2][2];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) lse_cur[i >> 1][i & 1] = lse_next[i >> 1][i & 1];
+            if constexpr (MODE == kBwdFused) {
+                tc::SegCursor nxt = scur;
+                if constexpr (SEG) nxt.advance();
+                load_lse(tile + gridDim.x, nxt, lse_next);
+            }
             // first row of the window: on the flattened axis, or inside the tile's residue sequence
             const int g0 = (SEG ? scur.i : tile) * stride - right;
             // tokens of the sequence the keys must lie in, and (segmented) the valid tokens of the residue sequence
@@ -536,7 +547,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             jb[hh] = tq - left + fa;
                             vle[hh] = !live ? -1 : tq >= vlr ? 0 : vlr;
                             need_mask |= tq < left || tq + right >= vlr;
-                            lse2[hh] = (NCW != 8 && b ? lse_next[1][hh] : lse_next[0][hh]) * kLog2e;
+                            lse2[hh] = (NCW != 8 && b ? lse_cur[1][hh] : lse_cur[0][hh]) * kLog2e;
                             if constexpr (DROP) drow[hh] = SEG ? (uint32_t)((scur.b * gm.H + scur.h) * T + tq * sg.d + scur.r) : (uint32_t)gq;
                             if constexpr (SEG) tq += 8; else tc::row_step8(T, gm.H, tq, hq, bq);
                         }
@@ -660,7 +671,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                         jb[k >> 1][k & 1] = tq - left + fa;
                         vle[k >> 1][k & 1] = !live ? -1 : tq >= vlr ? 0 : vlr;
                         need_mask |= tq < left || tq + right >= vlr;
-                        lse2[k >> 1][k & 1] = lse_next[k >> 1][k & 1] * kLog2e;
+                        lse2[k >> 1][k & 1] = lse_cur[k >> 1][k & 1] * kLog2e;
                         if constexpr (DROP) drow[k >> 1][k & 1] = SEG ? (uint32_t)((scur.b * gm.H + scur.h) * T + tq * sg.d + scur.r) : (uint32_t)gq;
                         if constexpr (SEG) tq += 8; else tc::row_step8(T, gm.H, tq, hq, bq);
                     }
@@ -786,7 +797,6 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 }
             }
             if constexpr (SEG) scur.advance(); else cur.advance();
-            if constexpr (MODE == kBwdFused) load_lse(tile + gridDim.x, lse_next);
         }
         if (d_rpb && it > 0 && ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) && !*abort_flag)  // the last tile's share
             bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask, dshift,
