@@ -436,6 +436,11 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
         tc::SegCursor scur = {};  // segmented tiling: the tile's residue sequence and its index in it
         if constexpr (SEG) scur.init((int)blockIdx.x, (int)gridDim.x, sg, gm.H);
         else cur.init(blockIdx.x * stride, T, gm.H, gridDim.x * stride);
+        // one block per warp, flat tiling: a cursor of the thread's own first fragment row, so that the row facts of a tile
+        // need no division
+        constexpr bool kOwnCursor = !SEG && NCW == 8;
+        tc::RowCursor mine = {};
+        if constexpr (kOwnCursor) mine.init_signed((int)blockIdx.x * stride + cw * 32 + 16 * bsel + fr - right, T, gm.H, gridDim.x * stride);
         // fetches the log-sum-exp of tile `tile_`; in the segmented tiling `at` must stand on that tile
         auto load_lse = [&](int tile_, const tc::SegCursor& at, float (&dst)[2][2]) {
             const int g0_ = (SEG ? at.i : tile_) * stride - right;
@@ -537,6 +542,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                         need_mask = false;
                         int tq = 0, hq = 0, bq = 0;
                         if constexpr (SEG) { tq = g0 + cw * 32 + 16 * b + fr; hq = scur.h; }
+                        else if constexpr (kOwnCursor) { tq = mine.t; hq = mine.h; bq = mine.b; }
                         else cur.row_at(cw * 32 + 16 * b + fr - right, inv_T, inv_H, tq, hq, bq);
 #pragma unroll
                         for (int hh = 0; hh < 2; ++hh) {
@@ -797,6 +803,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 }
             }
             if constexpr (SEG) scur.advance(); else cur.advance();
+            if constexpr (kOwnCursor) mine.advance();
         }
         if (d_rpb && it > 0 && ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) && !*abort_flag)  // the last tile's share
             bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask, dshift,

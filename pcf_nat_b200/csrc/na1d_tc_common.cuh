@@ -175,6 +175,12 @@ struct RowCursor {
         step_b = sn / H;
         step_h = sn - step_b * H;
     }
+    // the same for a row that may lie up to T - 1 rows before the tensor (a halo row of the first tile): it counts as a row
+    // of sequence -1, which the caller treats as not live
+    __device__ __forceinline__ void init_signed(int row, int T_, int H_, int step_rows) {  // row > -T
+        init(row < 0 ? row + T_ : row, T_, H_, step_rows);
+        if (row < 0) { h = H_ - 1; b = -1; }
+    }
     __device__ __forceinline__ void advance() {
         t += step_t;
         const int carry = t >= T ? 1 : 0;
