@@ -105,61 +105,85 @@ __device__ __noinline__ void bias_grad_outside(float* row, int off, int dshift, 
     if (g1 != 0.f) atomicAdd(row + ((off + 1) >> dshift), g1);
 }
 
-// Bias gradient of one tile, one warp: column sums of dS over the warp's owned query rows (hr = the row's head, -1 for a row
-// this tile does not own). Lane r has the address of row r of the dS operand (16-bit, scaled); a shuffle butterfly leaves the
-// sum of window offset i on lane i * (32 / NV), which adds it to the warp's own accumulator (no atomics: lanes hold distinct
-// offsets). Rows of different heads (a warp spans at most two sequences) take one pass per head. NV = 8, 16 or 32 offsets go
-// through the butterfly; offset NV exists only when the window fills its bucket. Not inlined: it keeps the tile loop short.
-template <typename E, int NV>
-__device__ __noinline__ void bias_grad_tile(const uint8_t* row, int r, int lane, int hr, int win, int ref_win, int dmask,
-                                            int dshift, float inv_scale, float* acc) {
-    // Every step below is a dependent chain in one warp (measured 1150 cycles for 8 offsets when written with conditional
-    // generic loads, integer reductions for the head range and a synchronised second accumulator update), so: unconditional
-    // shared-space loads, votes instead of reductions in the common one-head case, one accumulator update.
+// Bias gradient of one tile, one warp: sums of dS along the band's diagonals over the warp's owned query rows, read back
+// from a 16-bit, scaled dS matrix in 8x8 core-matrix order (element (q, c) at (q/8) lboq + (c/8) 128 + (q%8) 16 + (c%8) 2): the
+// dS operand of the tile, or the warp's private copy of its block (see the kernel). The warp's ROWS
+// consecutive tile rows start at r0; lane l holds hr = the head of row r0 + l (-1: a row this tile does not own, and lanes
+// past ROWS). A lane owns a WINDOW OFFSET, not a row: lane group rg = lane / NV walks the rows rg, rg + G, ... and adds up
+// dS[row, row + i] for its offset i = lane % NV, so whether a row counts and for which head is the same for all lanes of
+// a group at every step, nothing is exchanged until the G groups are added up (log2 G shuffles), and distinct lanes add
+// to distinct accumulator entries (no atomics). ROWS rows span at most two sequences (T >= 32), hence two heads: two sums.
+// (One lane per ROW with a shuffle butterfly over the 32 rows cost 3x the whole kernel's time at 33 offsets.) Offset NV
+// exists only when the window fills its bucket. Not inlined: it keeps the tile loop short.
+template <typename E, int NV, int ROWS, bool ATOMIC>
+__device__ __noinline__ void bias_grad_tile(const uint8_t* ds, int lboq, int r0, int lane, int hr, int win, int ref_win,
+                                            int dmask, int dshift, float inv_scale, float* acc) {
     const unsigned owned = __ballot_sync(0xffffffffu, hr >= 0);
     if (owned == 0) return;
-    const uint32_t row_s = ptx::smem_u32(row);
-    int hsel = __shfl_sync(0xffffffffu, hr, __ffs(owned) - 1);           // head of the first owned row
-    unsigned todo = owned;
-    for (;;) {
-        const bool mine = hr == hsel;
-        todo &= ~__ballot_sync(0xffffffffu, mine);
-        float x[NV];
+    const int head_a = __shfl_sync(0xffffffffu, hr, __ffs(owned) - 1);
+    const unsigned in_a = __ballot_sync(0xffffffffu, hr == head_a);
+    const unsigned in_b = owned & ~in_a;
+    const int head_b = __shfl_sync(0xffffffffu, hr, in_b ? __ffs(in_b) - 1 : 0);
+    constexpr int G = 32 / NV, NR = ROWS / G;
+    const int i = lane % NV, rg = lane / NV;
+    const uint32_t base = ptx::smem_u32(ds);
+    auto entry = [&](int row, int col) -> float {
+        unsigned short raw;
+        asm volatile("ld.shared.u16 %0, [%1];"
+                     : "=h"(raw) : "r"(base + (uint32_t)((row >> 3) * lboq + (row & 7) * 16 + (col >> 3) * 128 + (col & 7) * 2)));
+        return Cvt<E>::from_bits(raw);
+    };
+    auto add = [&](int head, int off, float x) {
+        float* dst = acc + head * ref_win + (off >> dshift);
+        if constexpr (ATOMIC) atomicAdd(dst, x * inv_scale); else *dst += x * inv_scale;
+    };
+    // all loads first (they are independent), then the sums; the second head only when the rows do cross a sequence end
+    float v[NR];
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int col = r + i;
-            unsigned short raw;
-            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(raw) : "r"(row_s + (uint32_t)((col >> 3) * 128 + (col & 7) * 2)));
-            const float v = Cvt<E>::from_bits(raw);
-            x[i] = (mine && i < win) ? v : 0.f;
-        }
-        float last = 0.f;
-        if (win > NV) {  // offset NV: only when the window fills its bucket
-            const int col = r + NV;
-            unsigned short raw;
-            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(raw) : "r"(row_s + (uint32_t)((col >> 3) * 128 + (col & 7) * 2)));
-            last = mine ? Cvt<E>::from_bits(raw) : 0.f;
+    for (int k = 0; k < NR; ++k) v[k] = entry(r0 + k * G + rg, r0 + k * G + rg + i);
+    float a = 0.f, b = 0.f;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) last += __shfl_xor_sync(0xffffffffu, last, o);
+    for (int k = 0; k < NR; ++k) a += ((in_a >> (k * G + rg)) & 1u) ? v[k] : 0.f;
+    if (in_b) {
+#pragma unroll
+        for (int k = 0; k < NR; ++k) b += ((in_b >> (k * G + rg)) & 1u) ? v[k] : 0.f;
+    }
+#pragma unroll
+    for (int o = NV; o < 32; o <<= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        b += __shfl_xor_sync(0xffffffffu, b, o);
+    }
+    if (rg == 0 && i < win && (i & dmask) == 0) {
+        add(head_a, i, a);
+        if (in_b) add(head_b, i, b);
+    }
+    if (win > NV) {  // offset NV: one row per lane, then a sum over the lanes
+        const int rl = lane < ROWS ? lane : 0;
+        const float x = lane < ROWS ? entry(r0 + rl, r0 + rl + NV) : 0.f;
+        float a2 = ((in_a >> rl) & 1u) ? x : 0.f, b2 = ((in_b >> rl) & 1u) ? x : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            a2 += __shfl_xor_sync(0xffffffffu, a2, o);
+            b2 += __shfl_xor_sync(0xffffffffu, b2, o);
         }
-        const float v = tc::column_sums<NV>(x, lane);
-        const int off = lane / (32 / NV);
-        float* acc_row = acc + hsel * ref_win;
-        // distinct lanes hold distinct offsets, and offset NV maps to an entry of its own: no two writes meet
-        if (lane % (32 / NV) == 0 && off < win && (off & dmask) == 0) acc_row[off >> dshift] += v * inv_scale;
-        if (win > NV && lane == 0) acc_row[NV >> dshift] += last * inv_scale;
-        if (todo == 0) break;
-        __syncwarp();
-        hsel = __shfl_sync(0xffffffffu, hr, __ffs(todo) - 1);
+        if (lane == 0) {
+            add(head_a, NV, a2);
+            if (in_b) add(head_b, NV, b2);
+        }
     }
 }
 
 // The layout as both the launcher and the kernel compute it (one function, so they cannot disagree): bias table for every
 // head when there is a bias, four per-warp (H, win) accumulators when its gradient is wanted.
+__host__ __device__ constexpr int bias_copy_bytes(int KT) { return 2 * (KT > 144 ? 6 : 4) * 128; }
 __host__ __device__ inline BwdSmemLayout bwd_layout_for(int C, int KT, const Geometry& gm, bool has_bias, bool wants_bias_grad,
                                                         int ncw = 0) {
-    if (ncw == 0) ncw = compute_warps(C, 0);   // one (H, win) bias-gradient accumulator per compute warp
-    return bwd_layout(C, KT, has_bias ? gm.H : 0, wants_bias_grad ? ncw * gm.H * gm.win : 0);
+    if (ncw == 0) ncw = compute_warps(C, 0);
+    // bias gradient. 4 compute warps: one (H, win) accumulator per warp. 8 compute warps: one accumulator for the CTA and, per
+    // warp, a private 16-bit copy of its block's dS band (16 rows x 8 NG columns in core-matrix order; NG <= 4 below the
+    // widest bucket, 6 in it)
+    const int acc = ncw == 8 ? round_up(gm.H * gm.win, 32) + 8 * bias_copy_bytes(KT) / 4 : ncw * gm.H * gm.win;
+    return bwd_layout(C, KT, has_bias ? gm.H : 0, wants_bias_grad ? acc : 0);
 }
 
 struct alignas(8) BwdMisc {
@@ -213,6 +237,13 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
     // for the usual sizes -- serialise (5x the whole kernel's time when every tile issued them), so each warp adds up its
     // tiles here without atomics and the CTA hands over one row of partial sums at its end
     float* bias_acc = bias_tab + round_up((rpb ? gm.H : 0) * kBiasRowB, 64);
+    // 8 compute warps: ONE accumulator for the CTA, and behind it every warp's private copy of its block's dS band. The
+    // copy keeps the entries of neighbours outside the query's own sequence (they have a bias gradient but are zeroed in
+    // the operand matrices) and is read back by its own warp right after the tile's stores, while batch 2 runs: the
+    // read-back from the operand had to sit between "batch 2 retired" and "the next tile's stores", on the critical loop.
+    constexpr bool kBiasCopy = NCW == 8;
+    constexpr int kCopyLbo = NG * 128;   // bytes between the two 8-row groups of a copy
+    uint8_t* bias_copy = reinterpret_cast<uint8_t*>(bias_acc + round_up(n_bias, 32));
     const int rows_total = gm.N * gm.T;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -405,6 +436,8 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
         // row of the tile whose dS this lane reads back for the bias gradient: a warp reads back exactly the rows it is about
         // to overwrite (NCW = 8: its own 16-row block, on lanes 0-15)
         const int r = NCW == 8 ? cw * 32 + bsel * 16 + (lane & 15) : cw * 32 + lane;
+        constexpr int kRowsPerWarp = NCW == 8 ? 16 : 32;
+        const int r0w = cw * 32 + (NCW == 8 ? bsel * 16 : 0);   // first tile row of this warp
         const int fr = lane >> 2, fc = 2 * (lane & 3);  // fragment row / first column inside an 8x8 block
         const int fa = fc - fr;                         // neighbour index = 8(n-h) + e + fa
         const uint32_t lane_base = tmem + ((uint32_t)(cw * 32) << 16);
@@ -421,7 +454,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
         const float inv_T = 1.f / (float)T, inv_H = 1.f / (float)gm.H;
         const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
         if (d_rpb)
-            for (int i = ct; i < NCW * n_bias; i += NCW * 32) bias_acc[i] = 0.f;
+            for (int i = ct; i < (kBiasCopy ? 1 : NCW) * n_bias; i += NCW * 32) bias_acc[i] = 0.f;
         if (rpb) {
             // bias table of every head, once per CTA (barrier among the 4 compute warps only)
             for (int i = ct; i < gm.H * kBiasRowB; i += NCW * 32) {
@@ -610,16 +643,22 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     if (need_mask) elements(std::true_type{}); else elements(std::false_type{});
                     delta[0] = tc::quad_sum(delta[0]);
                     delta[1] = tc::quad_sum(delta[1]);
-                    uint32_t pk_p[2 * NG], pk_d[2 * NG];
+                    uint32_t pk_p[2 * NG], pk_d[2 * NG], pk_b[kBiasCopy ? 2 * NG : 1];
 #pragma unroll
                     for (int g = 0; g < NG; ++g)
 #pragma unroll
                         for (int hh = 0; hh < 2; ++hh) {
                             const int idx = 4 * g + 2 * hh;
-                            if (tc::dead_slot(g, hh, NG)) { pk_d[2 * g + hh] = 0u; pk_p[2 * g + hh] = 0u; continue; }
+                            if (tc::dead_slot(g, hh, NG)) {
+                                pk_d[2 * g + hh] = 0u; pk_p[2 * g + hh] = 0u;
+                                if constexpr (kBiasCopy) pk_b[2 * g + hh] = 0u;
+                                continue;
+                            }
                             float ds0 = s1[idx] * (d1[idx] - delta[hh]);
                             float ds1 = s1[idx + 1] * (d1[idx + 1] - delta[hh]);
                             float p0 = s1[idx], p1 = s1[idx + 1];
+                            uint32_t dsp = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
+                            if constexpr (kBiasCopy) pk_b[2 * g + hh] = dsp;   // the bias gradient sees every entry of the band
                             if (need_mask) {
                                 const int kc = 8 * (g - hh), kk0 = kc + fa;
                                 const int j0 = jb[hh] + kc;
@@ -627,12 +666,14 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                 const bool own = d_rpb && row >= right && row < kTileM - left;
                                 const bool out0 = (unsigned)j0 >= (unsigned)Trow, out1 = (unsigned)(j0 + 1) >= (unsigned)Trow;
                                 if (out0 | out1) {
-                                    if (own) bias_grad_outside(bias_acc + warp * n_bias + hrow[hh] * gm.win, kk0, dshift, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
+                                    if constexpr (!kBiasCopy)
+                                        if (own) bias_grad_outside(bias_acc + warp * n_bias + hrow[hh] * gm.win, kk0, dshift, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
                                     if (out0) { ds0 = 0.f; p0 = 0.f; }
                                     if (out1) { ds1 = 0.f; p1 = 0.f; }
+                                    dsp = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
                                 }
                             }
-                            pk_d[2 * g + hh] = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
+                            pk_d[2 * g + hh] = dsp;
                             if constexpr (DROP) {
                                 const int off = 8 * (g - hh) + fa;
                                 p0 = drop_hash(drow[hh], (uint32_t)(off >> dshift), drop.seed) >= drop.threshold ? p0 * drop.scale : 0.f;
@@ -645,13 +686,16 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                         // them (everything above overlaps with it). The previous tile's bias gradient is read back from its
                         // dS operand first.
                         if (it > 0 && (!ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) || *abort_flag)) { failed = true; break; }
-                        if (d_rpb && it > 0)
-                            bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask,
-                                                      dshift, 1.f / gm.scale, bias_acc + warp * n_bias);
+                        if constexpr (!kBiasCopy)
+                            if (d_rpb && it > 0)
+                                bias_grad_tile<E, WB - 1, kRowsPerWarp, false>(sDS, lboq, r0w, lane, prev_hr, win, gm.win, dmask, dshift,
+                                                                               1.f / gm.scale, bias_acc + warp * n_bias);
                     }
                     const uint32_t blk = (uint32_t)(4 * cw + 2 * b) * (uint32_t)lboq + (uint32_t)(4 * cw + 2 * b) * 128u;
                     tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d, lane);
                     tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
+                    if constexpr (kBiasCopy)
+                        if (d_rpb) tc::store_block_operand<NG>(ptx::smem_u32(bias_copy) + (uint32_t)(warp * bias_copy_bytes(KT)), (uint32_t)kCopyLbo, pk_b, lane);
                 }
                 if (failed) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
             } else {
@@ -777,8 +821,8 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 // Bias gradient of the PREVIOUS tile, read back from its dS operand now: while batch 2 runs its operand fetches own
                 // the shared-memory bandwidth and the same read-back took thousands of cycles; here the tensor pipe is done with it.
                 if (d_rpb && it > 0)
-                    bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask, dshift,
-                                              1.f / gm.scale, bias_acc + warp * n_bias);
+                    bias_grad_tile<E, WB - 1, kRowsPerWarp, false>(sDS, lboq, r0w, lane, prev_hr, win, gm.win, dmask, dshift, 1.f / gm.scale,
+                                                                   bias_acc + warp * n_bias);
     #pragma unroll
                 for (int b = 0; b < 2; ++b) {
                     // core matrix of the block's first row / first column: row group 4w+2b, column group 4w+2b
@@ -794,20 +838,32 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 // head of the row this lane will read back (-1: a row this tile does not own)
                 const int gr = g0 + r;
                 prev_hr = -1;
+                // (own cursor: lanes 0-3 stand on the warp's first row, and its 16 rows cross at most one sequence end)
+                int t0 = 0, h0 = 0;
+                if constexpr (kOwnCursor) { t0 = __shfl_sync(0xffffffffu, mine.t, 0); h0 = __shfl_sync(0xffffffffu, mine.h, 0); }
                 if ((NCW == 4 || lane < 16) && r >= right && r < kTileM - left && gr >= 0 && gr < (SEG ? Trow : rows_total)) {
                     if constexpr (SEG) prev_hr = scur.h;
+                    else if constexpr (kOwnCursor) prev_hr = t0 + (lane & 15) < T ? h0 : (h0 + 1 == gm.H ? 0 : h0 + 1);
                     else {
                         int tr, br;
                         cur.row_at(r - right, inv_T, inv_H, tr, prev_hr, br);
                     }
                 }
+                if constexpr (kBiasCopy) {
+                    // this tile's share, from the warp's own copy (written by this warp just above: a warp-level barrier is
+                    // all the ordering it needs), while the tensor pipe works on batch 2
+                    __syncwarp();
+                    bias_grad_tile<E, WB - 1, 16, true>(bias_copy + warp * bias_copy_bytes(KT), kCopyLbo, 0, lane, prev_hr, win, gm.win, dmask,
+                                                        dshift, 1.f / gm.scale, bias_acc);
+                }
             }
             if constexpr (SEG) scur.advance(); else cur.advance();
             if constexpr (kOwnCursor) mine.advance();
         }
-        if (d_rpb && it > 0 && ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) && !*abort_flag)  // the last tile's share
-            bias_grad_tile<E, WB - 1>(sDS + (r >> 3) * lboq + (r & 7) * 16, r, lane, prev_hr, win, gm.win, dmask, dshift,
-                                      1.f / gm.scale, bias_acc + warp * n_bias);
+        if constexpr (!kBiasCopy)
+            if (d_rpb && it > 0 && ptx::mbar_wait(&misc->o_ready, (it - 1) & 1) && !*abort_flag)  // the last tile's share
+                bias_grad_tile<E, WB - 1, kRowsPerWarp, false>(sDS, lboq, r0w, lane, prev_hr, win, gm.win, dmask, dshift, 1.f / gm.scale,
+                                                               bias_acc + warp * n_bias);
         if (d_rpb) {
             // hand over this CTA's partial bias gradient: every compute thread arrives (also after an aborted loop), warp 0
             // waits for all of them and writes row blockIdx.x of the partial-sum matrix (or adds to the result directly when
@@ -815,9 +871,8 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
             ptx::mbar_arrive(&misc->acc_done);
             if (warp == 0 && ptx::mbar_wait(&misc->acc_done, 0)) {
                 for (int i = lane; i < n_bias; i += 32) {
-                    float x = (bias_acc[i] + bias_acc[n_bias + i]) + (bias_acc[2 * n_bias + i] + bias_acc[3 * n_bias + i]);
-                    if constexpr (NCW == 8)
-                        x += (bias_acc[4 * n_bias + i] + bias_acc[5 * n_bias + i]) + (bias_acc[6 * n_bias + i] + bias_acc[7 * n_bias + i]);
+                    float x = bias_acc[i];   // 8 compute warps: the CTA's one accumulator
+                    if constexpr (!kBiasCopy) x = (x + bias_acc[n_bias + i]) + (bias_acc[2 * n_bias + i] + bias_acc[3 * n_bias + i]);
                     if (drpb_direct) { if (x != 0.f) atomicAdd(d_rpb + i, x); }
                     else d_rpb[(size_t)blockIdx.x * n_bias + i] = x;
                 }

@@ -241,27 +241,6 @@ struct SegCursor {
     __device__ __forceinline__ int rows(const SegGeom& g) const { return g.Tp - (r >= g.ra ? 1 : 0); }
 };
 
-// Column sums of a 32 x NV matrix held one row per lane (NV = 8, 16 or 32): a butterfly in which every step halves the
-// number of columns a lane still carries, NV - 1 + log2(32 / NV) shuffles in all instead of 5 NV. Returns the sum of column
-// lane / (32 / NV); each column's sum is replicated on the 32 / NV lanes that share that quotient.
-template <int NV> __device__ __forceinline__ float column_sums(float (&x)[NV], int lane) {
-    int mask = 16;
-#pragma unroll
-    for (int half = NV / 2; half >= 1; half >>= 1, mask >>= 1) {
-        const bool up = (lane & mask) != 0;
-#pragma unroll
-        for (int i = 0; i < half; ++i) {
-            const float send = up ? x[i] : x[i + half];
-            const float keep = up ? x[i + half] : x[i];
-            x[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
-        }
-    }
-    float v = x[0];
-#pragma unroll
-    for (int m = (32 / NV) >> 1; m >= 1; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-    return v;
-}
-
 __device__ __forceinline__ float quad_sum(float x) {
     x += __shfl_xor_sync(0xffffffffu, x, 1);
     x += __shfl_xor_sync(0xffffffffu, x, 2);
