@@ -35,9 +35,9 @@ int check_geometry(int64_t N, int64_t heads, int64_t T, int64_t C, int64_t win, 
     return NA1D_OK;
 }
 
-// 32-byte rows with a window in the widest band bucket: the band-in and band-transposed modes of the tcgen05 kernels are
-// bound by the fp32 band's gather there and lose to the CUDA-core kernels (measured at N=8192, T=150, C=16, win=27:
-// 132 / 240 us against 107 / 121 us); the band-out mode wins everywhere (93 against 179 us) and is not affected.
+// 32-byte rows with a window in the widest band bucket: the band-transposed mode of the tcgen05 backward kernel is bound by
+// the fp32 band's gather there and loses to the CUDA-core kernel (measured at N=8192, T=150, C=16, win=27: 197 us against
+// 121 us); the band-out and band-in modes win everywhere (94 against 174 us, 84 against 107 us) and are not affected.
 bool narrow_rows_wide_window(const na1d::Geometry& g) { return g.C == 16 && (g.win - 1) * g.dil + 1 > 17; }
 
 #define NA1D_REQUIRE_PTR(p) do { if ((p) == nullptr) return NA1D_ERR_NULL_POINTER; } while (0)
@@ -74,7 +74,7 @@ int na1d_qk_forward(float* attn, const void* q, const void* k, int64_t N, int64_
     NA1D_REQUIRE_ALIGNED(q); NA1D_REQUIRE_ALIGNED(k);
     na1d::Geometry g;
     if (int s = check_geometry(N, 1, T, C, win, left, dil, dtype, 1.f, g)) return s;
-    if (g_family_override.load() != 0 && na1d::tc_unfused_supports(g))
+    if (g_family_override.load() != 0 && na1d::tc_unfused_supports(g) && aligned16(attn))   // the band goes out in 16-byte stores
         return cuda_status(na1d::tc_qk(attn, q, k, g, dtype, (cudaStream_t)stream));
     return cuda_status(na1d::simt_qk(attn, q, k, g, dtype, (cudaStream_t)stream));
 }
@@ -88,7 +88,7 @@ int na1d_q_backward(void* q_gd, const float* attn_gd, const void* k, int64_t N, 
     NA1D_REQUIRE_ALIGNED(q_gd); NA1D_REQUIRE_ALIGNED(k);
     na1d::Geometry g;
     if (int s = check_geometry(N, 1, T, C, win, left, dil, dtype, 1.f, g)) return s;
-    if (g_family_override.load() != 0 && na1d::tc_unfused_supports(g) && !narrow_rows_wide_window(g))
+    if (g_family_override.load() != 0 && na1d::tc_unfused_supports(g))
         return cuda_status(na1d::tc_band_x(q_gd, attn_gd, k, g, dtype, (cudaStream_t)stream));
     return cuda_status(na1d::simt_band_x(q_gd, attn_gd, k, g, dtype, (cudaStream_t)stream));
 }
@@ -102,7 +102,7 @@ int na1d_k_backward(void* k_gd, const float* attn_gd, const void* q, int64_t N, 
     NA1D_REQUIRE_ALIGNED(k_gd); NA1D_REQUIRE_ALIGNED(q);
     na1d::Geometry g;
     if (int s = check_geometry(N, 1, T, C, win, left, dil, dtype, 1.f, g)) return s;
-    if (g_family_override.load() != 0 && na1d::tc_unfused_t_supports(g) && !narrow_rows_wide_window(g))
+    if (g_family_override.load() != 0 && na1d::tc_unfused_t_supports(g) && (!narrow_rows_wide_window(g) || g_family_override.load() == 1))
         return cuda_status(na1d::tc_bandT_x(k_gd, attn_gd, q, g, dtype, (cudaStream_t)stream));
     return cuda_status(na1d::simt_bandT_x(k_gd, attn_gd, q, g, dtype, (cudaStream_t)stream));
 }

@@ -52,7 +52,7 @@ using tc::Fmt;
 // in the fused mode, 8 (warps w and w + 4 share tensor-memory lane quarter w & 3 and take one block each: these shapes are
 // bound by the softmax warps' per-row work, not by bytes). Behind them: producer/store warp, two MMA issuer warps, and with
 // 8 softmax warps one idle warp that completes the last warp group.
-__host__ __device__ constexpr int softmax_warps(int C, int mode) { return (C <= 32 && mode == 0) ? 8 : 4; }
+__host__ __device__ constexpr int softmax_warps(int C, int mode) { return C <= 32 ? 8 : 4; }
 __host__ __device__ constexpr int fwd_threads(int nsw) { return nsw == 8 ? 384 : 224; }
 constexpr int kTmemCols = 256;
 // Tensor-memory columns. P (16-bit pairs, KT/2 <= 80 columns) always starts at column 0. Two layouts:
@@ -71,9 +71,11 @@ __host__ __device__ constexpr int col_ob(int C, int WB) { return separate_p(C, W
 constexpr int kBiasPad = 16;
 
 struct FwdSmemLayout {
-    int q, ring, stage_k, stage_v, stage_bytes, misc, total;  // q: the single Q buffer; ring: first K/V stage
+    int q, ring, stage_k, stage_v, stage_bytes, misc, band_stage, total;  // q: the single Q buffer; ring: first K/V stage
 };
-__host__ __device__ inline FwdSmemLayout fwd_layout(int C, int KT, int bias_heads) {
+// band_win > 0 (band-out mode with 8 softmax warps): room to stage a tile's fp32 band, 128 rows of band_win entries, for
+// coalesced 16-byte stores
+__host__ __device__ inline FwdSmemLayout fwd_layout(int C, int KT, int bias_heads, int band_win = 0) {
     FwdSmemLayout L;
     // Q is needed only by the S MMAs at the start of a tile, so one buffer serves both stages: it is refilled as soon as
     // those MMAs retire. K and V live in a 2-stage ring; the finished O is staged in the tile's V buffer (idle once the
@@ -84,7 +86,8 @@ __host__ __device__ inline FwdSmemLayout fwd_layout(int C, int KT, int bias_head
     L.stage_v = round_up(KT * C * 2, 1024);
     L.stage_bytes = 2 * round_up(KT * C * 2, 1024);
     L.misc = L.ring + 2 * L.stage_bytes;
-    L.total = L.misc + 256 + round_up(2 * bias_heads * (kBiasPad + 48) * 4, 256) + 1008;  // misc, two bias tables, alignment slack
+    L.band_stage = L.misc + 256 + round_up(2 * bias_heads * (kBiasPad + 48) * 4, 256);
+    L.total = L.band_stage + round_up(kTileM * band_win * 4, 256) + 1008;  // misc, two bias tables, band staging, alignment slack
     return L;
 }
 
@@ -122,13 +125,14 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
     constexpr int kRowBytes = C * 2;
     constexpr bool kSepP = separate_p(C, WB);
     constexpr int NSW = softmax_warps(C, MODE), NB = NSW == 8 ? 1 : 2;   // softmax warps; 16-row blocks per warp
+    constexpr bool kStageBand = NSW == 8;   // band-out mode: the fp32 band goes out through shared memory (16-byte stores)
     constexpr int kProducerWarp = NSW, kIssuerA = NSW + 1, kIssuerB = NSW + 2;
     // registers per thread after the warp groups rebalance (NSW = 8: 384 threads, two CTAs per SM, 80 each at launch)
     constexpr int kRegsSoftmax = 104, kRegsOther = 32;
     constexpr int kSCol = col_s(C, WB), kOCol = col_o(C, WB), kOColB = col_ob(C, WB);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const FwdSmemLayout L = fwd_layout(C, KT, rpb ? gm.H : 0);
+    const FwdSmemLayout L = fwd_layout(C, KT, rpb ? gm.H : 0, (MODE == kBandOut && kStageBand) ? gm.win : 0);
     FwdMisc* misc = reinterpret_cast<FwdMisc*>(smem + L.misc);
     float* bias_tab = reinterpret_cast<float*>(smem + L.misc + 256);
     const int rows_total = gm.N * gm.T;
@@ -404,13 +408,19 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 // is the reference's zero-padded row: 0); the S columns are free for the next tile at once
                 ptx::tc_fence_before_sync();
                 ptx::mbar_arrive(&misc->o_free);
+                // Staged in shared memory first: the band rows of the warp's 16 NB tile rows are one contiguous piece of the
+                // band tensor (row r at r * win floats), 64-byte aligned because the first row is a multiple of 16, so the
+                // warp writes it with full 16-byte stores instead of 20 scattered 4-byte stores per thread and row pair.
+                float* stg = reinterpret_cast<float*>(smem + L.band_stage) + rb * gm.win;
 #pragma unroll
                 for (int b = 0; b < NB; ++b)
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) {
+                        // (4 softmax warps, 128-byte rows: straight to global memory -- the staging costs registers the two
+                        // blocks per warp do not have, and the band is the smaller part of the traffic there)
                         const int gq = g0 + rb + 16 * b + 8 * hh + fr;
-                        if (gq >= rows_total) continue;
-                        float* dst = band + (size_t)gq * gm.win;
+                        if (!kStageBand && gq >= rows_total) continue;
+                        float* dst = kStageBand ? stg + (16 * b + 8 * hh + fr) * gm.win : band + (size_t)gq * gm.win;
 #pragma unroll
                         for (int g = 0; g < NG; ++g)
 #pragma unroll
@@ -421,6 +431,15 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                 dst[(kc + fa) >> dshift] = j < (unsigned)Trow ? s[b][4 * g + 2 * hh + e] : 0.f;
                             }
                     }
+                if constexpr (kStageBand) {
+                    __syncwarp();
+                    const int row0 = g0 + rb;
+                    const int n = max(0, min(16 * NB, rows_total - row0)) * gm.win;   // floats of this warp's rows inside the tensor
+                    float* out = band + (size_t)row0 * gm.win;
+                    for (int i = lane; i < (n >> 2); i += 32) reinterpret_cast<float4*>(out)[i] = reinterpret_cast<const float4*>(stg)[i];
+                    if (lane < (n & 3)) out[(n & ~3) + lane] = stg[(n & ~3) + lane];
+                    __syncwarp();   // the next tile overwrites the staging rows
+                }
                 if constexpr (SEG) scur.advance(); else cur.advance();
                 continue;
             }
@@ -432,6 +451,8 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) {
                         const int gq = g0 + rb + 16 * b + 8 * hh + fr;
+                        // (read straight from global memory: the four lanes of a row share its cache lines, and staging the
+                        // warp's rows through shared memory as the band-out mode does measured 15 % slower)
                         const float* src = band + (size_t)min(gq, rows_total - 1) * gm.win;
 #pragma unroll
                         for (int g = 0; g < NG; ++g)
@@ -606,7 +627,7 @@ template <typename E, int C, int WB, bool SEG, int MODE, bool DROP>
 cudaError_t launch_fwd(const FwdMaps<SEG ? 2 : 1>& maps, float* lse, float* band, const float* rpb, const int* valid_len,
                        const Geometry& gm, const SegGeom& sg, int KT, int total, int sm_count, bool pdl, const DropoutCfg& drop,
                        cudaStream_t st) {
-    const int smem = fwd_layout(C, KT, rpb ? gm.H : 0).total;
+    const int smem = fwd_layout(C, KT, rpb ? gm.H : 0, (MODE == kBandOut && softmax_warps(C, MODE) == 8) ? gm.win : 0).total;
     auto kern = tc_fwd_kernel<E, C, WB, SEG, MODE, DROP>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
