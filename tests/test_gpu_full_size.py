@@ -160,3 +160,45 @@ def test_first_config_forward_strict_and_against_unrounded_reference():
         print("first config %s: vs oracle on rounded inputs %.3e (bound %.0e); vs reference vector on unrounded fp32 "
               "inputs %.3e, of which input rounding alone %.3e" % (str(dtype).split(".")[-1], e_round, TOL[dtype], e_gold, e_inputs))
         assert e_gold <= e_inputs + TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("N,T,C,win,left,dil", [(2051, 150, 16, 27, 13, 1), (1027, 150, 32, 15, 7, 2), (515, 200, 64, 7, 3, 1)])
+def test_unfused_entry_points_many_tiles_per_cta(N, T, C, win, left, dil, dtype):
+    """The six unfused entry points with several tiles per CTA and a ragged last tile (N*T is no multiple of 128): the
+    tcgen05 band modes against the CUDA-core kernels of the same library (both are held to the oracle at small sizes), and
+    the band output through a pointer that is only 4-byte aligned (the 16-byte-store path must not be taken)."""
+    from pcf_nat_b200 import ops
+    g = torch.Generator().manual_seed(77)
+    q, k, v, d_o = ((torch.randn(N, T, C, generator=g) * C ** -0.25).to(dtype).cuda() for _ in range(4))
+    res = {}
+    for fam in (ops.FAMILY_CUDA_CORE, ops.FAMILY_AUTO):
+        old = ops.set_kernel_family(fam)
+        try:
+            attn = ops.qk_forward(q, k, win, left, dil)
+            p = torch.softmax(attn, -1)
+            res[fam] = (attn, ops.av_forward(p, v, win, left, dil), ops.a_backward(d_o, v, win, left, dil), ops.q_backward(p, k, win, left, dil),
+                        ops.k_backward(p, q, win, left, dil), ops.v_backward(p, d_o, win, left, dil))
+        finally:
+            ops.set_kernel_family(old)
+    ops.device_status()
+    names = ("qk", "av", "a_gd", "q_gd", "k_gd", "v_gd")
+    for nm, a, b in zip(names, res[ops.FAMILY_CUDA_CORE], res[ops.FAMILY_AUTO]):
+        if a.dtype == torch.float32:
+            assert float((a - b).abs().max()) < 1e-4 * max(1.0, float(a.abs().max())), nm
+        else:
+            assert_close(b, a, dtype, nm)
+    # band output through a pointer that is 4-byte but not 16-byte aligned
+    import ctypes
+    from pcf_nat_b200 import _lib
+    L = _lib.lib()
+    buf = torch.full((N * T * win + 8,), float("nan"), dtype=torch.float32, device="cuda")
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = L.na1d_qk_forward(ctypes.c_void_p(buf.data_ptr() + 4), ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()),
+                           N, T, C, win, left, dil, 0 if dtype == torch.bfloat16 else 1, st)
+    assert rc == 0
+    torch.cuda.synchronize()
+    got = buf[1:1 + N * T * win].view(N, T, win)
+    ref = res[ops.FAMILY_CUDA_CORE][0]
+    assert float((got - ref).abs().max()) < 1e-4 * max(1.0, float(ref.abs().max()))
+    assert torch.isnan(buf[0]) and torch.isnan(buf[1 + N * T * win:]).all()
