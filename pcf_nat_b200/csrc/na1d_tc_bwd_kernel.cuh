@@ -183,7 +183,7 @@ __host__ __device__ inline BwdSmemLayout bwd_layout_for(int C, int KT, const Geo
     // warp, a private 16-bit copy of its block's dS band (16 rows x 8 NG columns in core-matrix order; NG <= 4 below the
     // widest bucket, 6 in it)
     const int acc = ncw == 8 ? round_up(gm.H * gm.win, 32) + 8 * bias_copy_bytes(KT) / 4 : ncw * gm.H * gm.win;
-    return bwd_layout(C, KT, has_bias ? gm.H : 0, wants_bias_grad ? acc : 0);
+    return bwd_layout(C, KT, has_bias ? gm.H : 1, wants_bias_grad ? acc : 0);   // without a bias: one table row of 0 / -inf
 }
 
 struct alignas(8) BwdMisc {
@@ -236,7 +236,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
     // accumulators of the bias gradient, one (H, win) array per compute warp: global atomics on the result -- one cache line
     // for the usual sizes -- serialise (5x the whole kernel's time when every tile issued them), so each warp adds up its
     // tiles here without atomics and the CTA hands over one row of partial sums at its end
-    float* bias_acc = bias_tab + round_up((rpb ? gm.H : 0) * kBiasRowB, 64);
+    float* bias_acc = bias_tab + round_up((rpb ? gm.H : 1) * kBiasRowB, 64);
     // 8 compute warps: ONE accumulator for the CTA, and behind it every warp's private copy of its block's dS band. The
     // copy keeps the entries of neighbours outside the query's own sequence (they have a bias gradient but are zeroed in
     // the operand matrices) and is read back by its own warp right after the tile's stores, while batch 2 runs: the
@@ -455,14 +455,19 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
         const uint32_t ds_a = ptx::smem_u32(sDS), p_a = ptx::smem_u32(sP);
         if (d_rpb)
             for (int i = ct; i < (kBiasCopy ? 1 : NCW) * n_bias; i += NCW * 32) bias_acc[i] = 0.f;
-        if (rpb) {
-            // bias table of every head, once per CTA (barrier among the 4 compute warps only)
-            for (int i = ct; i < gm.H * kBiasRowB; i += NCW * 32) {
+        {
+            // Table of every head's bias (one all-zero row without a bias), once per CTA, with -inf at every offset that is
+            // not a neighbour (outside the window, between dilated neighbours): the fragment slots take their additive term
+            // from it, and exp2 of it is the 0 of the slots outside the band -- no band test per slot. (Barrier among the
+            // compute warps only.)
+            const int heads = rpb ? gm.H : 1;
+            for (int i = ct; i < heads * kBiasRowB; i += NCW * 32) {
                 const int hh_ = i / kBiasRowB, kk = i - hh_ * kBiasRowB - kBiasPad;
-                bias_tab[i] = (kk >= 0 && kk < win && (kk & dmask) == 0) ? __ldg(rpb + hh_ * gm.win + (kk >> dshift)) * kLog2e : 0.f;
+                const bool nb = kk >= 0 && kk < win && (kk & dmask) == 0;
+                bias_tab[i] = !nb ? -INFINITY : rpb ? __ldg(rpb + hh_ * gm.win + (kk >> dshift)) * kLog2e : 0.f;
             }
         }
-        if (rpb || d_rpb) asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
         int it = 0;
         // log-sum-exp of the four fragment rows of a tile; loaded one tile ahead so the DRAM latency is hidden
         tc::RowCursor cur = {};  // flat tiling: row tile * stride = g0 + right
@@ -569,6 +574,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 // the two rows of block b this thread sees (row half hh): see the comments of the unrolled path below
                 float lse2[2];
                 int jb[2], vle[2], hrow[2];
+                const float* btab[2];          // the rows' bias table entries of window offset fa
                 uint32_t drow[2] = {0u, 0u};   // dense row index n*T + t of the two rows (dropout mask key)
                 bool need_mask = false;
                 auto row_facts = [&](int b) {
@@ -586,7 +592,8 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             jb[hh] = tq - left + fa;
                             vle[hh] = !live ? -1 : tq >= vlr ? 0 : vlr;
                             need_mask |= tq < left || tq + right >= vlr;
-                            lse2[hh] = (NCW != 8 && b ? lse_cur[1][hh] : lse_cur[0][hh]) * kLog2e;
+                            lse2[hh] = !live ? INFINITY : (NCW != 8 && b ? lse_cur[1][hh] : lse_cur[0][hh]) * kLog2e;
+                            btab[hh] = bias_tab + (rpb ? hq : 0) * kBiasRowB + kBiasPad + fa;
                             if constexpr (DROP) drow[hh] = SEG ? (uint32_t)((scur.b * gm.H + scur.h) * T + tq * sg.d + scur.r) : (uint32_t)gq;
                             if constexpr (SEG) tq += 8; else tc::row_step8(T, gm.H, tq, hq, bq);
                         }
@@ -620,19 +627,17 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                 for (int e = 0; e < 2; ++e) {
                                     const int idx = 4 * g + 2 * hh + e;
                                     if (tc::dead_slot(g, hh, NG)) { s1[idx] = 0.f; d1[idx] = 0.f; continue; }
-                                    const int kc = 8 * (g - hh) + e, kk = kc + fa;
-                                    bool on = (band_bits >> (2 * (g - hh + 1) + e)) & 1u;
-                                    float bias = 0.f;
-                                    if (rpb) bias = bias_tab[hrow[hh] * kBiasRowB + kBiasPad + kk];
+                                    const int kc = 8 * (g - hh) + e;
+                                    [[maybe_unused]] const int kk = kc + fa;
+                                    float bias = btab[hh][kc];   // -inf outside the band
                                     float dot = s1[idx], dpv = d1[idx];
                                     if constexpr (kMasked) {
                                         const unsigned j = (unsigned)(jb[hh] + kc);
                                         if (j >= (unsigned)Trow) { dot = 0.f; dpv = 0.f; }
                                         if ((int)j >= vle[hh] || (int)j < 0) bias += mask2;
-                                        on = on && vle[hh] >= 0;
                                     }
-                                    const float x = fmaf(dot, sc, bias) - lse2[hh];
-                                    const float p = on ? tc::fast_exp2(x) : 0.f;
+                                    const float x = fmaf(dot, sc, bias) - lse2[hh];   // lse2 = +inf for rows outside the tensor
+                                    const float p = tc::fast_exp2(x);
                                     if constexpr (DROP)
                                         dpv = drop_hash(drow[hh], (uint32_t)(kk >> dshift), drop.seed) >= drop.threshold ? dpv * drop.scale : 0.f;
                                     s1[idx] = p;
@@ -705,6 +710,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 //         reference's zero-padded K/V row
                 //   vle : keys >= vle are masked (0 when the query itself is padding);  -1 marks a row outside the tensor
                 float lse2[2][2];
+                const float* btab[2][2];   // the rows' bias table entries of window offset fa
                 int jb[2][2], vle[2][2], hrow[2][2];
                 uint32_t drow[2][2] = {{0u, 0u}, {0u, 0u}};   // dense row index n*T + t of the four rows (dropout mask key)
                 bool need_mask = false;
@@ -721,7 +727,8 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                         jb[k >> 1][k & 1] = tq - left + fa;
                         vle[k >> 1][k & 1] = !live ? -1 : tq >= vlr ? 0 : vlr;
                         need_mask |= tq < left || tq + right >= vlr;
-                        lse2[k >> 1][k & 1] = lse_cur[k >> 1][k & 1] * kLog2e;
+                        lse2[k >> 1][k & 1] = !live ? INFINITY : lse_cur[k >> 1][k & 1] * kLog2e;
+                        btab[k >> 1][k & 1] = bias_tab + (rpb ? hq : 0) * kBiasRowB + kBiasPad + fa;
                         if constexpr (DROP) drow[k >> 1][k & 1] = SEG ? (uint32_t)((scur.b * gm.H + scur.h) * T + tq * sg.d + scur.r) : (uint32_t)gq;
                         if constexpr (SEG) tq += 8; else tc::row_step8(T, gm.H, tq, hq, bq);
                     }
@@ -755,19 +762,17 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                 for (int e = 0; e < 2; ++e) {
                                     const int idx = 4 * g + 2 * hh + e;
                                     if (tc::dead_slot(g, hh, NG)) { s[b][idx] = 0.f; d[b][idx] = 0.f; continue; }
-                                    const int kc = 8 * (g - hh) + e, kk = kc + fa;
-                                    bool on = (band_bits >> (2 * (g - hh + 1) + e)) & 1u;
-                                    float bias = 0.f;
-                                    if (rpb) bias = bias_tab[hrow[b][hh] * kBiasRowB + kBiasPad + kk];
+                                    const int kc = 8 * (g - hh) + e;
+                                    [[maybe_unused]] const int kk = kc + fa;
+                                    float bias = btab[b][hh][kc];   // -inf outside the band
                                     float dot = s[b][idx], dpv = d[b][idx];
                                     if constexpr (kMasked) {
                                         const unsigned j = (unsigned)(jb[b][hh] + kc);
                                         if (j >= (unsigned)Trow) { dot = 0.f; dpv = 0.f; }  // the reference's zero-padded K/V row
                                         if ((int)j >= vle[b][hh] || (int)j < 0) bias += mask2;
-                                        on = on && vle[b][hh] >= 0;
                                     }
-                                    const float x = fmaf(dot, sc, bias) - lse2[b][hh];
-                                    const float p = on ? tc::fast_exp2(x) : 0.f;
+                                    const float x = fmaf(dot, sc, bias) - lse2[b][hh];   // lse2 = +inf for rows outside the tensor
+                                    const float p = tc::fast_exp2(x);
                                     if constexpr (DROP)
                                         dpv = drop_hash(drow[b][hh], (uint32_t)(kk >> dshift), drop.seed) >= drop.threshold ? dpv * drop.scale : 0.f;
                                     s[b][idx] = p;
