@@ -91,6 +91,9 @@ __host__ __device__ inline FwdSmemLayout fwd_layout(int C, int KT, int bias_head
     return L;
 }
 
+// rows of the additive-term table: one per head with a bias, one (0 inside the band, -inf outside) without, none in the band modes
+__host__ __device__ constexpr int table_heads(bool has_bias, int H, int mode) { return mode != 0 ? 0 : has_bias ? H : 1; }
+
 struct alignas(8) FwdMisc {
     uint64_t full[2], empty[2];  // K/V ring
     uint64_t full_q, empty_q;    // the single Q buffer
@@ -132,7 +135,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
     constexpr int kSCol = col_s(C, WB), kOCol = col_o(C, WB), kOColB = col_ob(C, WB);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const FwdSmemLayout L = fwd_layout(C, KT, rpb ? gm.H : 0, (MODE == kBandOut && kStageBand) ? gm.win : 0);
+    const FwdSmemLayout L = fwd_layout(C, KT, table_heads(rpb != nullptr, gm.H, MODE), (MODE == kBandOut && kStageBand) ? gm.win : 0);
     FwdMisc* misc = reinterpret_cast<FwdMisc*>(smem + L.misc);
     float* bias_tab = reinterpret_cast<float*>(smem + L.misc + 256);
     const int rows_total = gm.N * gm.T;
@@ -328,14 +331,18 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
             if ((unsigned)kk < (unsigned)win && (kk & dmask) == 0) band_bits |= 1u << c;
         }
         const float inv_T = 1.f / (float)T, inv_H = 1.f / (float)gm.H;
-        if (rpb) {
-            // bias table of every head, once per CTA (barrier among the 4 softmax warps only)
-            // two copies, the second shifted by one entry: a thread reads the biases of its two adjacent columns with one
-            // 8-byte load whatever the parity of its first offset
-            for (int i = tid; i < 2 * gm.H * kBiasRow; i += NSW * 32) {
-                const int copy = i / (gm.H * kBiasRow), j = i - copy * gm.H * kBiasRow;
+        const int heads = table_heads(rpb != nullptr, gm.H, MODE);
+        if constexpr (MODE == kFused) {
+            // Table of every head's bias (one all-zero row without a bias), once per CTA (barrier among the softmax warps
+            // only), with -inf at every offset that is not a neighbour (outside the window, between dilated neighbours): the
+            // fragment slots take their additive term from it and need no band test of their own.
+            // Two copies, the second shifted by one entry: a thread reads the terms of its two adjacent columns with one
+            // 8-byte load whatever the parity of its first offset.
+            for (int i = tid; i < 2 * heads * kBiasRow; i += NSW * 32) {
+                const int copy = i / (heads * kBiasRow), j = i - copy * heads * kBiasRow;
                 const int hh_ = j / kBiasRow, kk = j - hh_ * kBiasRow - kBiasPad + copy;
-                bias_tab[i] = (kk >= 0 && kk < win && (kk & dmask) == 0) ? __ldg(rpb + hh_ * gm.win + (kk >> dshift)) * kLog2e : 0.f;
+                const bool nb = kk >= 0 && kk < win && (kk & dmask) == 0;
+                bias_tab[i] = !nb ? -INFINITY : rpb ? __ldg(rpb + hh_ * gm.win + (kk >> dshift)) * kLog2e : 0.f;
             }
             asm volatile("bar.sync 1, %0;" ::"n"(NSW * 32) : "memory");
         }
@@ -373,7 +380,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 for (int k = 0; k < 2 * NB; ++k) {
                     const int tq = scur.i * kTileM + rb + fr + 8 * k;
                     const int vlr = tq < Trow ? vl_seq : 0;
-                    brow[k >> 1][k & 1] = bias_tab + ((fa & 1) ? gm.H * kBiasRow - 1 : 0) + scur.h * kBiasRow + kBiasPad + fa;
+                    brow[k >> 1][k & 1] = bias_tab + ((fa & 1) ? heads * kBiasRow - 1 : 0) + (rpb ? scur.h : 0) * kBiasRow + kBiasPad + fa;
                     jb[k >> 1][k & 1] = tq - left + fa;
                     vle[k >> 1][k & 1] = tq >= vlr ? 0 : vlr;
                     need_mask |= tq < left || tq + (win - 1 - left) >= vlr;
@@ -385,7 +392,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 for (int k = 0; k < 2 * NB; ++k) {
                     const bool live = g0 + rb + fr + 8 * k < rows_total;
                     const int vlr = !live ? 0 : valid_len ? min(T, __ldg(valid_len + min(bq, batch - 1))) : T;
-                    brow[k >> 1][k & 1] = bias_tab + ((fa & 1) ? gm.H * kBiasRow - 1 : 0) + hq * kBiasRow + kBiasPad + fa;
+                    brow[k >> 1][k & 1] = bias_tab + ((fa & 1) ? heads * kBiasRow - 1 : 0) + (rpb ? hq : 0) * kBiasRow + kBiasPad + fa;
                     jb[k >> 1][k & 1] = tq - left + fa;
                     vle[k >> 1][k & 1] = tq >= vlr ? 0 : vlr;
                     need_mask |= tq < left || tq + (win - 1 - left) >= vlr;
@@ -479,13 +486,12 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
 #pragma unroll
                             for (int hh = 0; hh < 2; ++hh) {
                                 if (tc::dead_slot(g, hh, NG)) { s[b][4 * g + 2 * hh] = s[b][4 * g + 2 * hh + 1] = -INFINITY; continue; }
-                                float2 bias2 = make_float2(0.f, 0.f);  // biases of the thread's two adjacent columns of this group
-                                if (rpb) bias2 = *reinterpret_cast<const float2*>(brow[b][hh] + 8 * (g - hh));
+                                // additive terms of the thread's two adjacent columns of this group (-inf outside the band)
+                                const float2 bias2 = *reinterpret_cast<const float2*>(brow[b][hh] + 8 * (g - hh));
 #pragma unroll
                                 for (int e = 0; e < 2; ++e) {
                                     const int idx = 4 * g + 2 * hh + e;
                                     const int kc = 8 * (g - hh) + e;  // window offset minus the lane constant fa
-                                    const bool inband = (band_bits >> (2 * (g - hh + 1) + e)) & 1u;
                                     float bias = e ? bias2.y : bias2.x;
                                     float dot = s[b][idx];
                                     if constexpr (kMasked) {
@@ -493,7 +499,7 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                         if (j >= (unsigned)Trow) dot = 0.f;  // key outside the query's own sequence: the reference's zero row
                                         if (j >= (unsigned)vle[b][hh]) bias += mask2;
                                     }
-                                    const float x = inband ? fmaf(dot, sc, bias) : -INFINITY;
+                                    const float x = fmaf(dot, sc, bias);
                                     s[b][idx] = x;
                                     mx[b][hh] = fmaxf(mx[b][hh], x);
                                 }
@@ -627,7 +633,7 @@ template <typename E, int C, int WB, bool SEG, int MODE, bool DROP>
 cudaError_t launch_fwd(const FwdMaps<SEG ? 2 : 1>& maps, float* lse, float* band, const float* rpb, const int* valid_len,
                        const Geometry& gm, const SegGeom& sg, int KT, int total, int sm_count, bool pdl, const DropoutCfg& drop,
                        cudaStream_t st) {
-    const int smem = fwd_layout(C, KT, rpb ? gm.H : 0, (MODE == kBandOut && softmax_warps(C, MODE) == 8) ? gm.win : 0).total;
+    const int smem = fwd_layout(C, KT, table_heads(rpb != nullptr, gm.H, MODE), (MODE == kBandOut && softmax_warps(C, MODE) == 8) ? gm.win : 0).total;
     auto kern = tc_fwd_kernel<E, C, WB, SEG, MODE, DROP>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
