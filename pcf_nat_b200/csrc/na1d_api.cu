@@ -121,6 +121,7 @@ static int pick_family(const na1d::Geometry& g, int backward, bool has_bias = fa
     const bool seg_ok = backward ? na1d::tc_bwd_seg_supports(g, has_bias, wants_bias_grad) : na1d::tc_seg_supports(g);
     if (forced == 0) return 0;
     if (forced == 2) return seg_ok ? 2 : NA1D_ERR_UNSUPPORTED;
+    if (forced == 1 && flat_ok) return 1;   // forced: the flat tiling wherever it can run (the choice below is for the automatic mode)
     int pick = 0;
     if (flat_ok && seg_ok && g.dil > 1) {
         // relative cost of a tile row in the window buckets 9 / 17 / 33 (measured at 64 utterances x 4 heads, 200 to 1000
