@@ -637,7 +637,11 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                         if ((int)j >= vle[hh] || (int)j < 0) bias += mask2;
                                     }
                                     const float x = fmaf(dot, sc, bias) - lse2[hh];   // lse2 = +inf for rows outside the tensor
-                                    const float p = tc::fast_exp2(x);
+                                    float p = tc::fast_exp2(x);
+                                    // A neighbour outside the query's sequence is a zero K/V row in the reference: its logit still
+                                    // has a bias gradient, but neither P nor dS of it may reach the operand matrices. Without a
+                                    // bias gradient nothing needs its probability: zero it here and the packing needs no masks.
+                                    if constexpr (kMasked) if (!d_rpb && (unsigned)(jb[hh] + kc) >= (unsigned)Trow) p = 0.f;
                                     if constexpr (DROP)
                                         dpv = drop_hash(drow[hh], (uint32_t)(kk >> dshift), drop.seed) >= drop.threshold ? dpv * drop.scale : 0.f;
                                     s1[idx] = p;
@@ -664,7 +668,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             float p0 = s1[idx], p1 = s1[idx + 1];
                             uint32_t dsp = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
                             if constexpr (kBiasCopy) pk_b[2 * g + hh] = dsp;   // the bias gradient sees every entry of the band
-                            if (need_mask) {
+                            if (need_mask && d_rpb) {
                                 const int kc = 8 * (g - hh), kk0 = kc + fa;
                                 const int j0 = jb[hh] + kc;
                                 const int row = cw * 32 + 16 * b + 8 * hh + fr;
@@ -772,7 +776,10 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                         if ((int)j >= vle[b][hh] || (int)j < 0) bias += mask2;
                                     }
                                     const float x = fmaf(dot, sc, bias) - lse2[b][hh];   // lse2 = +inf for rows outside the tensor
-                                    const float p = tc::fast_exp2(x);
+                                    float p = tc::fast_exp2(x);
+                                    // without a bias gradient nothing needs the probability of a neighbour outside the query's
+                                    // sequence: zero it here and the packing needs no masks
+                                    if constexpr (kMasked) if (!d_rpb && (unsigned)(jb[b][hh] + kc) >= (unsigned)Trow) p = 0.f;
                                     if constexpr (DROP)
                                         dpv = drop_hash(drow[b][hh], (uint32_t)(kk >> dshift), drop.seed) >= drop.threshold ? dpv * drop.scale : 0.f;
                                     s[b][idx] = p;
@@ -797,7 +804,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             float ds0 = s[b][idx] * (d[b][idx] - delta[b][hh]);
                             float ds1 = s[b][idx + 1] * (d[b][idx + 1] - delta[b][hh]);
                             float p0 = s[b][idx], p1 = s[b][idx + 1];
-                            if (need_mask) {
+                            if (need_mask && d_rpb) {   // (without a bias gradient these probabilities are already zero)
                                 // a neighbour outside the query's sequence is a zero K/V row in the reference: its logit still has a
                                 // bias gradient, but it must not reach the other sequence's dK/dV nor this query's dQ
                                 const int kc = 8 * (g - hh), kk0 = kc + fa;
