@@ -173,9 +173,64 @@ __device__ __noinline__ void bias_grad_tile(const uint8_t* ds, int lboq, int r0,
     }
 }
 
+// Bias gradient of one tile from a warp's private copy of its block's dS band (8 compute warps): 16 rows of PITCH 16-bit
+// values, entry (row q, window offset kk) at q * PITCH + 8 + kk + (q & 1) -- the shift by the row's parity makes every
+// thread's pair of adjacent offsets a 4-byte aligned store, the 8 leading cells and the overlap into the next row's
+// leading cells take the fragment slots left and right of the band (always 0). Rows the tile does not own were stored as
+// zeros, so lane i just adds up column i; only a warp whose rows span two sequences (in_b != 0) separates the heads.
+// hr: head of row `lane` (-1: not owned, and lanes >= 16). One shared atomic per lane and head.
+template <typename E, int PITCH>
+__device__ __noinline__ void bias_grad_rows(const uint8_t* copy, int lane, int hr, int win, int ref_win, int dmask, int dshift,
+                                            float inv_scale, float* acc) {
+    const unsigned owned = __ballot_sync(0xffffffffu, hr >= 0);
+    if (owned == 0) return;
+    const int head_a = __shfl_sync(0xffffffffu, hr, __ffs(owned) - 1);
+    const unsigned in_b = owned & ~__ballot_sync(0xffffffffu, hr == head_a);
+    const int head_b = __shfl_sync(0xffffffffu, hr, in_b ? __ffs(in_b) - 1 : 0);
+    const uint32_t base = ptx::smem_u32(copy) + (uint32_t)(8 + lane) * 2u;
+    float v[16];
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {
+        unsigned short raw;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(raw) : "r"(base + (uint32_t)((q * PITCH + (q & 1)) * 2)));
+        v[q] = Cvt<E>::from_bits(raw);
+    }
+    float t = 0.f, b = 0.f;
+#pragma unroll
+    for (int q = 0; q < 16; ++q) t += v[q];
+    if (in_b) {
+#pragma unroll
+        for (int q = 0; q < 16; ++q) b += ((in_b >> q) & 1u) ? v[q] : 0.f;
+    }
+    if (lane < win && (lane & dmask) == 0) {
+        atomicAdd(acc + head_a * ref_win + (lane >> dshift), (t - b) * inv_scale);
+        if (in_b) atomicAdd(acc + head_b * ref_win + (lane >> dshift), b * inv_scale);
+    }
+    if (win > 32) {  // offset 32 (a window of 33): one row per lane, then a sum over the lanes
+        constexpr int NV = 32;
+        float x = 0.f;
+        if (lane < 16) {
+            unsigned short raw;
+            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(raw) : "r"(ptx::smem_u32(copy) + (uint32_t)((lane * PITCH + 8 + NV + (lane & 1)) * 2)));
+            x = Cvt<E>::from_bits(raw);
+        }
+        float b2 = ((in_b >> lane) & 1u) ? x : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            x += __shfl_xor_sync(0xffffffffu, x, o);
+            b2 += __shfl_xor_sync(0xffffffffu, b2, o);
+        }
+        if (lane == 0) {
+            atomicAdd(acc + head_a * ref_win + (NV >> dshift), (x - b2) * inv_scale);
+            if (in_b) atomicAdd(acc + head_b * ref_win + (NV >> dshift), b2 * inv_scale);
+        }
+    }
+}
+
 // The layout as both the launcher and the kernel compute it (one function, so they cannot disagree): bias table for every
 // head when there is a bias, four per-warp (H, win) accumulators when its gradient is wanted.
-__host__ __device__ constexpr int bias_copy_bytes(int KT) { return 2 * (KT > 144 ? 6 : 4) * 128; }
+// a warp's private copy of its block's dS band: 16 rows of (8 + window bucket + 1) 16-bit cells and the last row's overlap
+__host__ __device__ constexpr int bias_copy_bytes(int KT) { return KT > 144 ? 1408 : 896; }
 __host__ __device__ inline BwdSmemLayout bwd_layout_for(int C, int KT, const Geometry& gm, bool has_bias, bool wants_bias_grad,
                                                         int ncw = 0) {
     if (ncw == 0) ncw = compute_warps(C, 0);
@@ -242,7 +297,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
     // the operand matrices) and is read back by its own warp right after the tile's stores, while batch 2 runs: the
     // read-back from the operand had to sit between "batch 2 retired" and "the next tile's stores", on the critical loop.
     constexpr bool kBiasCopy = NCW == 8;
-    constexpr int kCopyLbo = NG * 128;   // bytes between the two 8-row groups of a copy
+    constexpr int kCopyPitch = 8 + WB + 1;   // 16-bit cells per row of a copy (even: WB is odd)
     uint8_t* bias_copy = reinterpret_cast<uint8_t*>(bias_acc + round_up(n_bias, 32));
     const int rows_total = gm.N * gm.T;
 
@@ -574,6 +629,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 // the two rows of block b this thread sees (row half hh): see the comments of the unrolled path below
                 float lse2[2];
                 int jb[2], vle[2], hrow[2];
+                bool ownr[2];                  // the tile owns the row (its band is complete here) and the row is in the tensor
                 const float* btab[2];          // the rows' bias table entries of window offset fa
                 uint32_t drow[2] = {0u, 0u};   // dense row index n*T + t of the two rows (dropout mask key)
                 bool need_mask = false;
@@ -589,6 +645,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             const bool live = gq >= 0 && gq < (SEG ? Trow : rows_total);
                             const int vlr = !live ? 0 : SEG ? vl_seq : valid_len ? min(T, __ldg(valid_len + min(max(bq, 0), batch - 1))) : T;
                             hrow[hh] = hq;
+                            ownr[hh] = live && cw * 32 + 16 * b + 8 * hh + fr >= right && cw * 32 + 16 * b + 8 * hh + fr < kTileM - left;
                             jb[hh] = tq - left + fa;
                             vle[hh] = !live ? -1 : tq >= vlr ? 0 : vlr;
                             need_mask |= tq < left || tq + right >= vlr;
@@ -667,7 +724,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                             float ds1 = s1[idx + 1] * (d1[idx + 1] - delta[hh]);
                             float p0 = s1[idx], p1 = s1[idx + 1];
                             uint32_t dsp = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
-                            if constexpr (kBiasCopy) pk_b[2 * g + hh] = dsp;   // the bias gradient sees every entry of the band
+                            if constexpr (kBiasCopy) pk_b[2 * g + hh] = ownr[hh] ? dsp : 0u;   // the bias gradient sees every band entry of an owned row
                             if (need_mask && d_rpb) {
                                 const int kc = 8 * (g - hh), kk0 = kc + fa;
                                 const int j0 = jb[hh] + kc;
@@ -704,7 +761,19 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     tc::store_block_operand<NG>(ds_a + blk, (uint32_t)lboq, pk_d, lane);
                     tc::store_block_operand<NG>(p_a + blk, (uint32_t)lboq, pk_p, lane);
                     if constexpr (kBiasCopy)
-                        if (d_rpb) tc::store_block_operand<NG>(ptx::smem_u32(bias_copy) + (uint32_t)(warp * bias_copy_bytes(KT)), (uint32_t)kCopyLbo, pk_b, lane);
+                        if (d_rpb) {
+                            // entry (row q, offset kk) at cell q * pitch + 8 + kk + (q & 1): the thread's pair (kk0, kk0 + 1), kk0
+                            // of the row's parity, is one aligned 4-byte store
+                            const uint32_t cp = ptx::smem_u32(bias_copy) + (uint32_t)(warp * bias_copy_bytes(KT)) +
+                                                (uint32_t)((fr * kCopyPitch + 8 + fa + (fr & 1)) * 2);
+#pragma unroll
+                            for (int g = 0; g < NG; ++g)
+#pragma unroll
+                                for (int hh = 0; hh < 2; ++hh) {
+                                    if (tc::dead_slot(g, hh, NG)) continue;
+                                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(cp + (uint32_t)((8 * hh * kCopyPitch + 8 * (g - hh)) * 2)), "r"(pk_b[2 * g + hh]) : "memory");
+                                }
+                        }
                 }
                 if (failed) { atomicExch(&g_tc_bwd_status, 16); *abort_flag = 1; break; }
             } else {
@@ -865,8 +934,8 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     // this tile's share, from the warp's own copy (written by this warp just above: a warp-level barrier is
                     // all the ordering it needs), while the tensor pipe works on batch 2
                     __syncwarp();
-                    bias_grad_tile<E, WB - 1, 16, true>(bias_copy + warp * bias_copy_bytes(KT), kCopyLbo, 0, lane, prev_hr, win, gm.win, dmask,
-                                                        dshift, 1.f / gm.scale, bias_acc);
+                    bias_grad_rows<E, kCopyPitch>(bias_copy + warp * bias_copy_bytes(KT), lane, prev_hr, win, gm.win, dmask, dshift,
+                                                          1.f / gm.scale, bias_acc);
                 }
             }
             if constexpr (SEG) scur.advance(); else cur.advance();
