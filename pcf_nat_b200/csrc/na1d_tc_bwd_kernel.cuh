@@ -698,7 +698,10 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                     // A neighbour outside the query's sequence is a zero K/V row in the reference: its logit still
                                     // has a bias gradient, but neither P nor dS of it may reach the operand matrices. Without a
                                     // bias gradient nothing needs its probability: zero it here and the packing needs no masks.
-                                    if constexpr (kMasked) if (!d_rpb && (unsigned)(jb[hh] + kc) >= (unsigned)Trow) p = 0.f;
+                                    // With one (and 8 compute warps) the probability goes on NEGATED: its sign tells the packing
+                                    // which entries go to the bias-gradient copy only (dpv is 0 there, so delta does not see it).
+                                    if constexpr (kMasked)
+                                        if ((unsigned)(jb[hh] + kc) >= (unsigned)Trow) p = !d_rpb ? 0.f : kBiasCopy ? -p : p;
                                     if constexpr (DROP)
                                         dpv = drop_hash(drow[hh], (uint32_t)(kk >> dshift), drop.seed) >= drop.threshold ? dpv * drop.scale : 0.f;
                                     s1[idx] = p;
@@ -720,23 +723,31 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                                 if constexpr (kBiasCopy) pk_b[2 * g + hh] = 0u;
                                 continue;
                             }
-                            float ds0 = s1[idx] * (d1[idx] - delta[hh]);
-                            float ds1 = s1[idx + 1] * (d1[idx + 1] - delta[hh]);
                             float p0 = s1[idx], p1 = s1[idx + 1];
-                            uint32_t dsp = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
-                            if constexpr (kBiasCopy) pk_b[2 * g + hh] = ownr[hh] ? dsp : 0u;   // the bias gradient sees every band entry of an owned row
-                            if (need_mask && d_rpb) {
+                            const float t0 = (d1[idx] - delta[hh]) * gm.scale, t1 = (d1[idx + 1] - delta[hh]) * gm.scale;
+                            if (kBiasCopy && need_mask && d_rpb) {
+                                // negative = a neighbour outside the query's sequence: its dS goes to the bias-gradient copy, zeros
+                                // go to the operand matrices
+                                if constexpr (kBiasCopy) pk_b[2 * g + hh] = ownr[hh] ? Cvt<E>::pack2(fabsf(p0) * t0, fabsf(p1) * t1) : 0u;
+                                p0 = fmaxf(p0, 0.f);
+                                p1 = fmaxf(p1, 0.f);
+                            }
+                            float ds0 = p0 * t0, ds1 = p1 * t1;   // (scaled)
+                            uint32_t dsp = Cvt<E>::pack2(ds0, ds1);
+                            if constexpr (kBiasCopy)
+                                if (!(need_mask && d_rpb)) pk_b[2 * g + hh] = ownr[hh] ? dsp : 0u;   // the bias gradient sees every band entry of an owned row
+                            if (!kBiasCopy && need_mask && d_rpb) {
                                 const int kc = 8 * (g - hh), kk0 = kc + fa;
                                 const int j0 = jb[hh] + kc;
                                 const int row = cw * 32 + 16 * b + 8 * hh + fr;
                                 const bool own = d_rpb && row >= right && row < kTileM - left;
                                 const bool out0 = (unsigned)j0 >= (unsigned)Trow, out1 = (unsigned)(j0 + 1) >= (unsigned)Trow;
                                 if (out0 | out1) {
-                                    if constexpr (!kBiasCopy)
-                                        if (own) bias_grad_outside(bias_acc + warp * n_bias + hrow[hh] * gm.win, kk0, dshift, out0 ? ds0 : 0.f, out1 ? ds1 : 0.f);
+                                    // (ds is scaled here; the accumulators hold unscaled sums)
+                                    if (own) bias_grad_outside(bias_acc + warp * n_bias + hrow[hh] * gm.win, kk0, dshift, out0 ? ds0 / gm.scale : 0.f, out1 ? ds1 / gm.scale : 0.f);
                                     if (out0) { ds0 = 0.f; p0 = 0.f; }
                                     if (out1) { ds1 = 0.f; p1 = 0.f; }
-                                    dsp = Cvt<E>::pack2(ds0 * gm.scale, ds1 * gm.scale);
+                                    dsp = Cvt<E>::pack2(ds0, ds1);
                                 }
                             }
                             pk_d[2 * g + hh] = dsp;
