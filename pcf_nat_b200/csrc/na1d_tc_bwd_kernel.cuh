@@ -1146,6 +1146,16 @@ cudaError_t launch_bwd(const BwdMaps<SEG ? 2 : 1>& maps, float* d_rpb, float* sc
                                                              : tc_bwd_kernel<E, C, WB, true, SEG, MODE, DROP>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
+    if constexpr (compute_warps(C, MODE) == 8) {
+        // The warp groups of this variant trade registers among themselves (2 x 176 + 104 + 56 per thread): the CTA's pool
+        // must hold 4 x 128, i.e. the kernel must have been compiled to 128 registers, or the compute warps would wait
+        // for registers that never come. Checked once per variant; a build that breaks it fails here, not on the GPU.
+        static const int regs = [] {
+            cudaFuncAttributes fa;
+            return cudaFuncGetAttributes(&fa, tc_bwd_kernel<E, C, WB, true, SEG, MODE, DROP>) == cudaSuccess ? fa.numRegs : 0;
+        }();
+        if (regs < 128) return cudaErrorLaunchOutOfResources;
+    }
     const int grid = total < sm_count ? total : sm_count;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);

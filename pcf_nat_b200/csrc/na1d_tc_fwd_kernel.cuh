@@ -637,6 +637,16 @@ cudaError_t launch_fwd(const FwdMaps<SEG ? 2 : 1>& maps, float* lse, float* band
     auto kern = tc_fwd_kernel<E, C, WB, SEG, MODE, DROP>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
+    if constexpr (softmax_warps(C, MODE) == 8) {
+        // The warp groups of this variant trade registers among themselves (2 x 104 + 32 per thread): the CTA's pool must
+        // hold 3 x 80, i.e. the kernel must have been compiled to 80 registers, or the softmax warps would wait for
+        // registers that never come. Checked once per variant; a build that breaks it fails here, not on the GPU.
+        static const int regs = [] {
+            cudaFuncAttributes fa;
+            return cudaFuncGetAttributes(&fa, tc_fwd_kernel<E, C, WB, SEG, MODE, DROP>) == cudaSuccess ? fa.numRegs : 0;
+        }();
+        if (regs < 80) return cudaErrorLaunchOutOfResources;
+    }
     const int per_sm = (2 * (smem + 1024) <= 227 * 1024) ? 2 : 1;
     const int slots = sm_count * per_sm;
     const int grid = total < slots ? total : slots;
