@@ -673,6 +673,52 @@ def run_layer_cost(args):
     print(json.dumps(out), flush=True)
 
 
+def run_bias_cost(args):
+    """What the layer's relative-position bias, its gradient and the padding masks cost in the fused kernels
+    (models/PCF_NATransformer.py:141-150 adds all three; the operator workloads above time the bare kernels, as the
+    reference's own kernels know none of them): forward and backward microseconds over rotating buffer sets, plain launches,
+    CUDA events, at the training shape and at the reference's own shape."""
+    import ctypes
+    from pcf_nat_b200 import _lib, ops
+    lib = _lib.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    ptr = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
+    out = {"what": "fused forward / backward us per launch (bf16): bare, + rpb, + rpb and d_rpb, + rpb, d_rpb and valid_len"}
+    for name in ("cfg2_train_B128_H4_L200_D64_w7", "real_B512_H16_L150_D16_w27"):
+        w = WORKLOADS[name]
+        N, H, T, C, win = w["B"] * w["H"], w["H"], w["T"], w["C"], w["win"]
+        left = win // 2
+        g = torch.Generator(device=dev).manual_seed(0)
+        sets = []
+        for _ in range(4):
+            q, k, v, do = (torch.randn(N, T, C, device=dev, generator=g).to(torch.bfloat16) for _ in range(4))
+            sets.append((q, k, v, do) + tuple(torch.empty_like(q) for _ in range(4)) + (torch.empty(N, T, device=dev), torch.empty(N, T, device=dev)))
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        rows = {}
+        for label, use_rpb, use_drpb, use_vl in (("bare", 0, 0, 0), ("rpb", 1, 0, 0), ("rpb_drpb", 1, 1, 0), ("rpb_drpb_valid_len", 1, 1, 1)):
+            rpb = 0.1 * torch.randn(H, win, device=dev, generator=g) if use_rpb else None
+            drpb = torch.zeros(H, win, device=dev) if use_drpb else None
+            vl = torch.full((N // H,), T - 5, dtype=torch.int32, device=dev) if use_vl else None
+            i = [0]
+
+            def fwd():
+                q, k, v, do, o, dq, dk, dv, lse, ws = sets[i[0] % 4]
+                assert lib.na1d_fused_forward(ptr(o), ptr(lse), ptr(q), ptr(k), ptr(v), ptr(rpb), ptr(vl), N, H, T, C, win, left, 1, C ** -0.5, 0, st) == 0
+
+            def bwd():
+                q, k, v, do, o, dq, dk, dv, lse, ws = sets[i[0] % 4]
+                i[0] += 1
+                assert lib.na1d_fused_backward(ptr(dq), ptr(dk), ptr(dv), ptr(drpb), ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(rpb), ptr(vl),
+                                               ptr(ws), N, H, T, C, win, left, 1, C ** -0.5, 0, st) == 0
+            for _ in range(4):
+                fwd(); bwd()
+            rows[label] = {"fwd_us": round(_time_fn(fwd, 20), 1), "bwd_us": round(_time_fn(bwd, 20), 1)}
+        out[name] = rows
+    ops.device_status()
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -693,9 +739,12 @@ def main():
                     help="cfg5_embed: cut every length-sorted batch to its own longest utterance (the reference's length-bucketed loader)")
     ap.add_argument("--layer-cost", action="store_true", help="whole attention layer, strided route against the copying route")
     ap.add_argument("--host-cost", action="store_true", help="host microseconds per forward+backward C-ABI call pair at a small shape")
+    ap.add_argument("--bias-cost", action="store_true", help="fused kernels with the layer's bias, its gradient and padding masks")
     args = ap.parse_args()
     if args.host_cost:
         return run_host_cost(args)
+    if args.bias_cost:
+        return run_bias_cost(args)
     if args.layer_cost:
         return run_layer_cost(args)
     if args.sweep:

@@ -106,8 +106,9 @@ int na1d_fused_forward(void* o, float* lse, const void* q, const void* k, const 
 /* Gradients of na1d_fused_forward. dq,dk,dv: (N,T,C) 16-bit. d_rpb: (heads,win) fp32, ACCUMULATED
  * into (caller zeroes it), or NULL. delta_ws: caller-provided scratch of N*T fp32. The CUDA-core
  * kernels keep the row sums of d_o*o there (written by a pre-pass, read by the main kernel); the
- * tcgen05 kernels need no such pre-pass and use it only for one partial row of d_rpb per CTA, summed
- * by a second small kernel (when it is too small for that they add to d_rpb with atomics).
+ * tcgen05 kernels need no such pre-pass: every CTA adds its partial d_rpb to the result with atomics at
+ * its end (with NA1D_BIAS_GRAD_ROWS=1 in the environment: one partial row per CTA in delta_ws, summed in
+ * a fixed order by a second small kernel).
  * Replaces the autograd chain AV.backward -> softmax backward -> QK.backward,
  * na1d_tensorcore/nattn.py:46-54 and :69-78. */
 int na1d_fused_backward(void* dq, void* dk, void* dv, float* d_rpb, const void* d_o, const void* q,

@@ -1167,9 +1167,9 @@ cudaError_t launch_bwd(const BwdMaps<SEG ? 2 : 1>& maps, float* d_rpb, float* sc
     attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    // bias gradient: one partial row per CTA in the caller's scratch, summed by a second tiny kernel; if the scratch cannot
-    // hold grid rows the CTAs add their row to the result with atomics instead
-    const bool partial_rows = d_rpb && scratch && scratch_floats >= (size_t)grid * n_bias;
+    // bias gradient: every CTA adds its partial sums to the result with atomics at its end; on request (and if the caller's
+    // scratch holds one row per CTA) one partial row per CTA instead, summed in a fixed order by a second tiny kernel
+    const bool partial_rows = bias_grad_partial_rows() && d_rpb && scratch && scratch_floats >= (size_t)grid * n_bias;
     float* bias_out = !d_rpb ? nullptr : partial_rows ? scratch : d_rpb;
     e = cudaLaunchKernelEx(&cfg, kern, maps, bias_out, partial_rows ? 0 : 1, lse, rpb, valid_len, gm, sg, stride, KT, total, drop);
     if (e != cudaSuccess || !partial_rows) return e;

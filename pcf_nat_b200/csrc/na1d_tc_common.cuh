@@ -265,5 +265,6 @@ int device_sm_count();
 void bind_primary_context();
 bool pdl_enabled();
 int pdl_mode();
+bool bias_grad_partial_rows();
 
 }  // namespace na1d

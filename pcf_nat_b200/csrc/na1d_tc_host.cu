@@ -130,6 +130,18 @@ int pdl_mode() {  // 0 off, 1 both kernels, 2 forward only, 3 backward only; any
 }
 bool pdl_enabled() { return pdl_mode() != 0; }
 
+// How a backward launch hands over its CTAs' partial bias gradients. Default: every CTA adds its (heads, win) partial sum to
+// d_rpb with atomics, once, at its end (148 adds per entry; 4 us cheaper than a second kernel, which is 15 % of a backward at
+// the training shape). NA1D_BIAS_GRAD_ROWS=1 (read once): one row per CTA in the caller's scratch and a second small kernel
+// that sums the rows in a fixed order -- the same bits from run to run for 64-channel rows.
+bool bias_grad_partial_rows() {
+    static const bool m = []() {
+        const char* e = getenv("NA1D_BIAS_GRAD_ROWS");
+        return e && e[0] == '1' && e[1] == '\0';
+    }();
+    return m;
+}
+
 // The tensor-map encoder is a DRIVER call and needs the device's primary context current on the calling thread. A thread that
 // has made no runtime call yet (an autograd worker whose first CUDA work is this library) has none: bind it explicitly.
 void bind_primary_context() {
