@@ -202,3 +202,38 @@ def test_unfused_entry_points_many_tiles_per_cta(N, T, C, win, left, dil, dtype)
     ref = res[ops.FAMILY_CUDA_CORE][0]
     assert float((got - ref).abs().max()) < 1e-4 * max(1.0, float(ref.abs().max()))
     assert torch.isnan(buf[0]) and torch.isnan(buf[1 + N * T * win:]).all()
+
+
+def test_bias_gradient_partial_rows_mode_in_a_fresh_process():
+    """NA1D_BIAS_GRAD_ROWS=1 (read once per process): one partial row of d_rpb per CTA in the caller's scratch, summed by the
+    second kernel in a fixed order -- same values as the oracle, and the same bits when the call is repeated (64-channel
+    rows: per-warp accumulators, no atomics anywhere on the way)."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import sys, torch
+sys.path[:0] = ["tests", "tests/golden"]
+from gpu_util import assert_close
+from oracle import na1d_oracle as orc
+from pcf_nat_b200 import ops
+N, H, T, C, win, left = 1200, 4, 200, 64, 7, 3
+g = torch.Generator().manual_seed(5)
+q, k, v, d_o = ((torch.randn(N, T, C, generator=g) * C ** -0.25).to(torch.bfloat16) for _ in range(4))
+rpb = 0.3 * torch.randn(H, win, generator=g)
+vl = [T - (i % 7) for i in range(N // H)]
+sc = C ** -0.5
+o, lse = ops.fused_forward(q.cuda(), k.cuda(), v.cuda(), win, left, 1, sc, rpb.cuda(), vl, H)
+args = (d_o.cuda(), q.cuda(), k.cuda(), v.cuda(), o, lse, win, left, 1, sc, rpb.cuda(), vl, H)
+a = ops.fused_backward(*args, need_d_rpb=True)[3]
+b = ops.fused_backward(*args, need_d_rpb=True)[3]
+ops.device_status()
+assert torch.equal(a, b), "partial rows summed in a fixed order must repeat bit for bit"
+ref = orc.na1d_fused_with_grads(q.float(), k.float(), v.float(), d_o.float(), win, left, 1, sc, rpb, vl, H)[4]
+assert_close(a, ref, torch.bfloat16, "drpb", factor=2.0)
+print("ok")
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NA1D_BIAS_GRAD_ROWS="1", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
