@@ -230,8 +230,9 @@ int na1d_fused_kernel_tiling(int64_t N, int64_t T, int64_t C, int64_t win, int64
                              int dtype, int backward);
 
 /* Force a kernel family for the fused entry points: -1 = automatic (default), 0 = CUDA-core,
- * 1 = tcgen05/TMA (either tiling), 2 = tcgen05/TMA on the segmented tiling. Process-wide; meant for tests and
- * benchmarks. Returns the previous setting. */
+ * 1 = tcgen05/TMA (the flat tiling wherever it can run, else the segmented one; for the unfused entry points: also
+ * where the automatic choice would take a CUDA-core kernel), 2 = tcgen05/TMA on the segmented tiling. Process-wide;
+ * meant for tests and benchmarks. Returns the previous setting. */
 int na1d_set_kernel_family(int family);
 
 /* Hits and misses of the library's cache of encoded TMA tensor maps since the process started (the cache is keyed by
