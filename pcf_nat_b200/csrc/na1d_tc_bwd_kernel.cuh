@@ -177,16 +177,12 @@ __device__ __noinline__ void bias_grad_tile(const uint8_t* ds, int lboq, int r0,
 // values, entry (row q, window offset kk) at q * PITCH + 8 + kk + (q & 1) -- the shift by the row's parity makes every
 // thread's pair of adjacent offsets a 4-byte aligned store, the 8 leading cells and the overlap into the next row's
 // leading cells take the fragment slots left and right of the band (always 0). Rows the tile does not own were stored as
-// zeros, so lane i just adds up column i; only a warp whose rows span two sequences (in_b != 0) separates the heads.
-// hr: head of row `lane` (-1: not owned, and lanes >= 16). One shared atomic per lane and head.
+// zeros, so lane i just adds up column i. The caller says (warp-uniform, from its row cursor -- no votes here) which rows
+// [lo, hi) are owned and from which row `split` on they belong to the next sequence (head_b instead of head_a); only a
+// warp whose owned rows do span two sequences separates the two sums. One shared reduction per lane and head.
 template <typename E, int PITCH>
-__device__ __noinline__ void bias_grad_rows(const uint8_t* copy, int lane, int hr, int win, int ref_win, int dmask, int dshift,
-                                            float inv_scale, float* acc) {
-    const unsigned owned = __ballot_sync(0xffffffffu, hr >= 0);
-    if (owned == 0) return;
-    const int head_a = __shfl_sync(0xffffffffu, hr, __ffs(owned) - 1);
-    const unsigned in_b = owned & ~__ballot_sync(0xffffffffu, hr == head_a);
-    const int head_b = __shfl_sync(0xffffffffu, hr, in_b ? __ffs(in_b) - 1 : 0);
+__device__ __noinline__ void bias_grad_rows(const uint8_t* copy, int lane, int lo, int hi, int split, int head_a, int head_b,
+                                            int win, int ref_win, int dmask, int dshift, float inv_scale, float* acc) {
     const uint32_t base = ptx::smem_u32(copy) + (uint32_t)(8 + lane) * 2u;
     float v[16];
 #pragma unroll
@@ -195,34 +191,37 @@ __device__ __noinline__ void bias_grad_rows(const uint8_t* copy, int lane, int h
         asm volatile("ld.shared.u16 %0, [%1];" : "=h"(raw) : "r"(base + (uint32_t)((q * PITCH + (q & 1)) * 2)));
         v[q] = Cvt<E>::from_bits(raw);
     }
-    float t = 0.f, b = 0.f;
+    auto red = [&](int head, int off, float x) {
+        asm volatile("red.shared.add.f32 [%0], %1;" ::"r"(ptx::smem_u32(acc + head * ref_win + (off >> dshift))), "f"(x * inv_scale) : "memory");
+    };
+    const float t = (((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]))) +
+                    (((v[8] + v[9]) + (v[10] + v[11])) + ((v[12] + v[13]) + (v[14] + v[15])));
+    const bool two = split > lo && split < hi;      // owned rows on both sides of a sequence end
+    float b = 0.f;
+    if (two) {
 #pragma unroll
-    for (int q = 0; q < 16; ++q) t += v[q];
-    if (in_b) {
-#pragma unroll
-        for (int q = 0; q < 16; ++q) b += ((in_b >> q) & 1u) ? v[q] : 0.f;
+        for (int q = 0; q < 16; ++q) b += q >= split ? v[q] : 0.f;
     }
     if (lane < win && (lane & dmask) == 0) {
-        atomicAdd(acc + head_a * ref_win + (lane >> dshift), (t - b) * inv_scale);
-        if (in_b) atomicAdd(acc + head_b * ref_win + (lane >> dshift), b * inv_scale);
+        red(split > lo ? head_a : head_b, lane, t - b);
+        if (two) red(head_b, lane, b);
     }
     if (win > 32) {  // offset 32 (a window of 33): one row per lane, then a sum over the lanes
-        constexpr int NV = 32;
         float x = 0.f;
         if (lane < 16) {
             unsigned short raw;
-            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(raw) : "r"(ptx::smem_u32(copy) + (uint32_t)((lane * PITCH + 8 + NV + (lane & 1)) * 2)));
+            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(raw) : "r"(ptx::smem_u32(copy) + (uint32_t)((lane * PITCH + 8 + 32 + (lane & 1)) * 2)));
             x = Cvt<E>::from_bits(raw);
         }
-        float b2 = ((in_b >> lane) & 1u) ? x : 0.f;
+        float b2 = (two && lane >= split) ? x : 0.f;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             x += __shfl_xor_sync(0xffffffffu, x, o);
             b2 += __shfl_xor_sync(0xffffffffu, b2, o);
         }
         if (lane == 0) {
-            atomicAdd(acc + head_a * ref_win + (NV >> dshift), (x - b2) * inv_scale);
-            if (in_b) atomicAdd(acc + head_b * ref_win + (NV >> dshift), b2 * inv_scale);
+            red(split > lo ? head_a : head_b, 32, x - b2);
+            if (two) red(head_b, 32, b2);
         }
     }
 }
@@ -926,7 +925,24 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(&misc->p_ready);
-            if (d_rpb) {
+            if constexpr (kBiasCopy) {
+                if (d_rpb) {
+                    // This tile's share, from the warp's own copy (written by this warp just above: a warp-level barrier is all
+                    // the ordering it needs), while the tensor pipe works on batch 2. Which of the warp's 16 rows the tile owns
+                    // ([lo, hi): the same test as for the stored zeros) and where the next sequence starts (split) follow from
+                    // the row cursor; the rows cross at most one sequence end.
+                    int t0 = 0, h0 = SEG ? scur.h : 0;
+                    if constexpr (kOwnCursor) { t0 = __shfl_sync(0xffffffffu, mine.t, 0); h0 = __shfl_sync(0xffffffffu, mine.h, 0); }
+                    const int first = g0 + r0w;
+                    const int lo = max(max(right - r0w, 0), -first);
+                    const int hi = min(min(16, kTileM - left - r0w), (SEG ? Trow : rows_total) - first);
+                    const int split = kOwnCursor ? T - t0 : 16;
+                    __syncwarp();
+                    if (hi > lo)
+                        bias_grad_rows<E, kCopyPitch>(bias_copy + warp * bias_copy_bytes(KT), lane, lo, hi, split, h0, h0 + 1 == gm.H ? 0 : h0 + 1, win,
+                                                      gm.win, dmask, dshift, 1.f / gm.scale, bias_acc);
+                }
+            } else if (d_rpb) {
                 // head of the row this lane will read back (-1: a row this tile does not own)
                 const int gr = g0 + r;
                 prev_hr = -1;
@@ -940,13 +956,6 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                         int tr, br;
                         cur.row_at(r - right, inv_T, inv_H, tr, prev_hr, br);
                     }
-                }
-                if constexpr (kBiasCopy) {
-                    // this tile's share, from the warp's own copy (written by this warp just above: a warp-level barrier is
-                    // all the ordering it needs), while the tensor pipe works on batch 2
-                    __syncwarp();
-                    bias_grad_rows<E, kCopyPitch>(bias_copy + warp * bias_copy_bytes(KT), lane, prev_hr, win, gm.win, dmask, dshift,
-                                                          1.f / gm.scale, bias_acc);
                 }
             }
             if constexpr (SEG) scur.advance(); else cur.advance();
