@@ -181,7 +181,7 @@ __device__ __noinline__ void bias_grad_tile(const uint8_t* ds, int lboq, int r0,
 // [lo, hi) are owned and from which row `split` on they belong to the next sequence (head_b instead of head_a); only a
 // warp whose owned rows do span two sequences separates the two sums. One shared reduction per lane and head.
 template <typename E, int PITCH>
-__device__ __noinline__ void bias_grad_rows(const uint8_t* copy, int lane, int lo, int hi, int split, int head_a, int head_b,
+__device__ __forceinline__ void bias_grad_rows(const uint8_t* copy, int lane, int lo, int hi, int split, int head_a, int head_b,
                                             int win, int ref_win, int dmask, int dshift, float inv_scale, float* acc) {
     const uint32_t base = ptx::smem_u32(copy) + (uint32_t)(8 + lane) * 2u;
     float v[16];
