@@ -941,6 +941,7 @@ tc_bwd_kernel(const __grid_constant__ BwdMaps<SEG ? 2 : 1> tm, float* __restrict
                     if (hi > lo)
                         bias_grad_rows<E, kCopyPitch>(bias_copy + warp * bias_copy_bytes(KT), lane, lo, hi, split, h0, h0 + 1 == gm.H ? 0 : h0 + 1, win,
                                                       gm.win, dmask, dshift, 1.f / gm.scale, bias_acc);
+                    __syncwarp();   // every lane has read the copy before any lane rewrites it in the next tile
                 }
             } else if (d_rpb) {
                 // head of the row this lane will read back (-1: a row this tile does not own)
