@@ -423,8 +423,8 @@ tc_fwd_kernel(const __grid_constant__ FwdMaps<SEG ? 2 : 1> tm, float* __restrict
                 for (int b = 0; b < NB; ++b)
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) {
-                        // (4 softmax warps, 128-byte rows: straight to global memory -- the staging costs registers the two
-                        // blocks per warp do not have, and the band is the smaller part of the traffic there)
+                        // (the 4-warp form of the kernel, two blocks per warp, writes straight to global memory: the staging
+                        // costs registers it does not have)
                         const int gq = g0 + rb + 16 * b + 8 * hh + fr;
                         if (!kStageBand && gq >= rows_total) continue;
                         float* dst = kStageBand ? stg + (16 * b + 8 * hh + fr) * gm.win : band + (size_t)gq * gm.win;
